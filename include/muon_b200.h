@@ -1,0 +1,148 @@
+/*
+ * muon_b200 — C ABI of the B200 (sm_100a) Muon optimizer-step library.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream; nothing here
+ * depends on PyTorch. All work is enqueued on the given stream and no entry point
+ * synchronises, except muon_b200_device_status. Unless stated otherwise the library
+ * neither allocates nor frees device memory: buffers, workspaces included, belong to
+ * the caller.
+ *
+ * Return value: 0 on success, a negative code on failure (see MUON_B200_ERR_*); the
+ * text of the last failure on the calling thread is available from
+ * muon_b200_last_error(). There is no CPU fallback: on a device that is not sm_100
+ * every compute entry point fails with MUON_B200_ERR_UNSUPPORTED.
+ *
+ * "Reference" citations are file:line of thib-s/Muon's muon.py, the module whose
+ * functions these entry points replace.
+ */
+#ifndef MUON_B200_H_
+#define MUON_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MUON_B200_OK 0
+#define MUON_B200_ERR_INVALID_ARG (-1)
+#define MUON_B200_ERR_ALIGNMENT (-2)
+#define MUON_B200_ERR_CUDA (-3)
+#define MUON_B200_ERR_UNSUPPORTED (-4)
+#define MUON_B200_ERR_DEVICE_TIMEOUT (-5)
+
+/* Element types of parameters, gradients and optimizer state. */
+#define MUON_B200_F32 0
+#define MUON_B200_BF16 1
+
+/* Newton-Schulz variants. AOL4 is what the reference executes (muon.py:748-799);
+ * CLASSIC5 is the Frobenius-normalised quintic iteration the reference documents in
+ * its commented block (muon.py:263-291). */
+#define MUON_B200_NS_AOL4 0
+#define MUON_B200_NS_CLASSIC5 1
+
+/* Upper bound on tensors per call of the multi-tensor entry points is unlimited;
+ * internally they are processed in launches of this many. */
+#define MUON_B200_TENSORS_PER_LAUNCH 32
+
+typedef void* muon_b200_stream_t; /* a cudaStream_t */
+
+/* Library version as major*10000 + minor*100 + patch. */
+int muon_b200_version(void);
+
+/* Message of the last error raised on the calling thread ("" if none). */
+const char* muon_b200_last_error(void);
+
+/* Synchronises the current device and reads the device-side status word that kernels
+ * set when a bounded wait inside them runs out (0 = healthy). If reset != 0 the word
+ * is cleared afterwards. Returns MUON_B200_ERR_DEVICE_TIMEOUT when the word is set. */
+int muon_b200_device_status(int* status_out, int reset);
+
+/* ---- Newton-Schulz GEMM lines ---------------------------------------------------
+ * All matrices are bf16, row-major with a pitch (ld*, in elements, multiple of 8) and a
+ * batch pitch (*_bs, in elements, multiple of 8; ignored when batch == 1). Pointers
+ * must be 16-byte aligned. */
+
+/* A[b] = X[b] · X[b]ᵀ, X is m x k, A is m x m, exactly symmetric.
+ * Replaces ns_line_1 (muon.py:420-456) and its kernel (muon.py:349-417). */
+int muon_b200_ns_line1(const void* x, int64_t ldx, int64_t x_bs, void* a_out, int64_t lda,
+                       int64_t a_bs, int batch, int64_t m, int64_t k, muon_b200_stream_t stream);
+
+/* B[b] = alpha · A[b] · A[b]ᵀ + beta · A[b], A is m x m. The lower triangle is computed
+ * and mirrored. Replaces ns_line_2 (muon.py:547-588, kernel :464-544). */
+int muon_b200_ns_line2(const void* a, int64_t lda, int64_t a_bs, void* b_out, int64_t ldb,
+                       int64_t b_bs, int batch, int64_t m, float alpha, float beta,
+                       muon_b200_stream_t stream);
+
+/* OUT[b] = a · X[b] + B[b] · X[b], B is m x m, X and OUT are m x n. OUT must not alias X.
+ * Replaces ns_line_3 (muon.py:705-746, kernel :639-702). */
+int muon_b200_ns_line3(const void* b, int64_t ldb, int64_t b_bs, const void* x, int64_t ldx,
+                       int64_t x_bs, void* out, int64_t ldo, int64_t o_bs, int batch, int64_t m,
+                       int64_t n, float a, muon_b200_stream_t stream);
+
+/* ---- Newton-Schulz driver ---------------------------------------------------------
+ * The workspace of a batch of `batch` matrices of m x n (m <= n) holds, in this order,
+ * X and C ([batch, m, ldn] bf16), A and B ([batch, m, ldm] bf16) and a small fp32
+ * reduction area. Layout query (all outputs in bytes / elements as named): */
+typedef struct muon_b200_ns_layout {
+  int64_t total_bytes;
+  int64_t x_offset_bytes, c_offset_bytes, a_offset_bytes, b_offset_bytes, partials_offset_bytes;
+  int64_t ldn, x_bs; /* pitch and batch pitch of X and C, in elements */
+  int64_t ldm, a_bs; /* pitch and batch pitch of A and B, in elements */
+} muon_b200_ns_layout;
+
+int muon_b200_ns_workspace_layout(int batch, int64_t m, int64_t n, muon_b200_ns_layout* out);
+
+/* Orthogonalises the `batch` matrices already stored (bf16, m x n, m <= n) in slot X of
+ * `workspace`. mode is MUON_B200_NS_AOL4 or MUON_B200_NS_CLASSIC5; steps = 0 picks the
+ * mode's default (4 / 5); coeffs is NULL or steps triples (a, b, c); eps is the clamp
+ * (AOL) or the additive term (classic). On return *result_slot is 0 if the result is in
+ * slot X and 1 if it is in slot C. `workspace` must be 256-byte aligned.
+ * Replaces zeropower_via_newtonschulz5 (muon.py:748-799) from line 778 on. */
+int muon_b200_ns_run(void* workspace, int batch, int64_t m, int64_t n, int mode, int steps,
+                     const float* coeffs, float eps, int* result_slot, muon_b200_stream_t stream);
+
+/* ---- Elementwise stages, multi-tensor ------------------------------------------------
+ * `count` tensors of identical shape rows x cols (a 4-D conv filter is passed as
+ * rows = size(0), cols = numel / size(0), muon.py:11-12) and identical dtype. */
+
+/* Momentum prologue, in place on grads and moms (muon.py:9-10) and bf16 cast into the NS
+ * input X (muon.py:760-764): X of tensor i starts at x + i*x_bs elements, pitch ldx; with
+ * transpose_out != 0 it is written transposed ([cols, rows]), which is how tall
+ * parameters enter the iteration. */
+int muon_b200_prologue(void* const* grads, void* const* moms, int count, int64_t rows,
+                       int64_t cols, int dtype, double beta, int nesterov, void* x, int64_t ldx,
+                       int64_t x_bs, int transpose_out, muon_b200_stream_t stream);
+
+/* Update epilogue, in place on params (muon.py:14 and :66-67):
+ * p = p*(1 - lr*wd) - lr * bf16(U*scale). U of tensor i is at u + i*u_bs, pitch ldu, and is
+ * [rows, cols], or [cols, rows] when u_transposed != 0. */
+int muon_b200_epilogue(void* const* params, int count, int64_t rows, int64_t cols, int dtype,
+                       const void* u, int64_t ldu, int64_t u_bs, int u_transposed, double lr,
+                       double weight_decay, double scale, muon_b200_stream_t stream);
+
+/* Whole Muon update of `count` same-shape parameters: prologue -> NS -> epilogue, using
+ * `workspace` (>= muon_b200_ns_workspace_layout(count, min(rows,cols), max(rows,cols))
+ * bytes). scale is the factor of muon.py:14, evaluated by the caller on the original
+ * gradient shape. Replaces the body of the per-parameter loop of SingleDeviceMuon.step
+ * (muon.py:94-99) for a group of parameters. */
+int muon_b200_muon_step(void* const* params, void* const* grads, void* const* moms, int count,
+                        int64_t rows, int64_t cols, int dtype, double lr, double weight_decay,
+                        double beta, int nesterov, double scale, int ns_mode, int ns_steps,
+                        const float* ns_coeffs, float ns_eps, void* workspace,
+                        int64_t workspace_bytes, muon_b200_stream_t stream);
+
+/* Fused Adam step on `count` tensors of any sizes (numel[i] elements each), in place on
+ * params, exp_avg and exp_avg_sq; steps[i] is the 1-based step count of tensor i after
+ * the increment. Replaces adam_update and the two parameter ops that follow it
+ * (muon.py:104-109, :193-197). */
+int muon_b200_adam(void* const* params, void* const* grads, void* const* exp_avg,
+                   void* const* exp_avg_sq, const int64_t* numel, const int64_t* steps, int count,
+                   int dtype, double lr, double weight_decay, double beta1, double beta2,
+                   double eps, muon_b200_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* MUON_B200_H_ */

@@ -1,0 +1,351 @@
+// C-ABI layer of libmuon_b200: argument checking, the Newton-Schulz driver and the
+// composition prologue -> NS -> epilogue. Declarations and the reference lines each
+// entry point replaces are in include/muon_b200.h.
+#include "../../include/muon_b200.h"
+
+#include "common.cuh"
+#include "elementwise.h"
+#include "ns_gemm.h"
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+namespace mb {
+
+namespace {
+thread_local char t_err[512] = "";
+}
+
+int set_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(t_err, sizeof(t_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+const char* last_error() { return t_err; }
+
+namespace {
+
+inline int64_t round_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+inline cudaStream_t as_stream(muon_b200_stream_t s) { return static_cast<cudaStream_t>(s); }
+inline __nv_bfloat16* bf(void* p) { return static_cast<__nv_bfloat16*>(p); }
+inline const __nv_bfloat16* bf(const void* p) { return static_cast<const __nv_bfloat16*>(p); }
+
+constexpr int kFroChunksMax = 296;
+
+int fro_chunks(int64_t m) { return (int)(m < kFroChunksMax ? m : kFroChunksMax); }
+
+// Coefficient tables (a, b, c) per iteration.
+const float kAol4[4][3] = {{4.0098f, -7.0585f, 2.4635f},   // muon.py:754-759
+                           {3.4585f, -5.5479f, 2.5959f},
+                           {2.7573f, -3.2939f, 1.4254f},
+                           {2.7215f, -3.0494f, 1.3169f}};
+const float kClassic[3] = {3.4445f, -4.7750f, 2.0315f};    // muon.py:276
+
+int check_dtype(int dtype) {
+  if (dtype != DT_F32 && dtype != DT_BF16)
+    return set_error(ERR_INVALID_ARG, "dtype must be MUON_B200_F32 or MUON_B200_BF16 (got %d)",
+                     dtype);
+  return OK;
+}
+
+bool all_aligned16(void* const* ptrs, int n) {
+  for (int i = 0; i < n; ++i)
+    if (reinterpret_cast<uintptr_t>(ptrs[i]) & 15) return false;
+  return true;
+}
+
+}  // namespace
+}  // namespace mb
+
+using namespace mb;
+
+extern "C" {
+
+int muon_b200_version(void) { return 100; }
+
+const char* muon_b200_last_error(void) { return last_error(); }
+
+int muon_b200_device_status(int* status_out, int reset) {
+  int st = 0;
+  int rc = read_device_status(&st);
+  if (rc != OK) return rc;
+  if (status_out) *status_out = st;
+  if (reset && st != 0 && (rc = clear_device_status()) != OK) return rc;
+  if (st != 0)
+    return set_error(ERR_DEVICE_TIMEOUT, "a kernel gave up on a bounded wait (device status %d)",
+                     st);
+  return OK;
+}
+
+int muon_b200_ns_line1(const void* x, int64_t ldx, int64_t x_bs, void* a_out, int64_t lda,
+                       int64_t a_bs, int batch, int64_t m, int64_t k, muon_b200_stream_t stream) {
+  return launch_ns_gemm(MODE_SYRK, bf(x), ldx, x_bs, bf(x), ldx, x_bs, bf(a_out), lda, a_bs, batch,
+                        m, m, k, 1.f, 0.f, as_stream(stream));
+}
+
+int muon_b200_ns_line2(const void* a, int64_t lda, int64_t a_bs, void* b_out, int64_t ldb,
+                       int64_t b_bs, int batch, int64_t m, float alpha, float beta,
+                       muon_b200_stream_t stream) {
+  if (a == b_out) return set_error(ERR_INVALID_ARG, "ns_line2 output must not alias its input");
+  return launch_ns_gemm(MODE_AXPBY, bf(a), lda, a_bs, bf(a), lda, a_bs, bf(b_out), ldb, b_bs, batch,
+                        m, m, m, alpha, beta, as_stream(stream));
+}
+
+int muon_b200_ns_line3(const void* b, int64_t ldb, int64_t b_bs, const void* x, int64_t ldx,
+                       int64_t x_bs, void* out, int64_t ldo, int64_t o_bs, int batch, int64_t m,
+                       int64_t n, float a, muon_b200_stream_t stream) {
+  if (x == out) return set_error(ERR_INVALID_ARG, "ns_line3 output must not alias X");
+  return launch_ns_gemm(MODE_BX, bf(b), ldb, b_bs, bf(x), ldx, x_bs, bf(out), ldo, o_bs, batch, m,
+                        n, m, a, 0.f, as_stream(stream));
+}
+
+int muon_b200_ns_workspace_layout(int batch, int64_t m, int64_t n, muon_b200_ns_layout* out) {
+  if (!out) return set_error(ERR_INVALID_ARG, "layout output is NULL");
+  if (batch < 1 || m < 1 || n < 1)
+    return set_error(ERR_INVALID_ARG, "workspace layout needs batch, m, n >= 1");
+  if (m > n) return set_error(ERR_INVALID_ARG, "NS works on m x n with m <= n (got %lld x %lld)",
+                              (long long)m, (long long)n);
+  muon_b200_ns_layout l;
+  l.ldn = round_up(n, 8);
+  l.ldm = round_up(m, 8);
+  l.x_bs = m * l.ldn;
+  l.a_bs = m * l.ldm;
+  const int64_t xb = round_up(batch * l.x_bs * 2, 256);
+  const int64_t ab = round_up(batch * l.a_bs * 2, 256);
+  l.x_offset_bytes = 0;
+  l.c_offset_bytes = xb;
+  l.a_offset_bytes = 2 * xb;
+  l.b_offset_bytes = 2 * xb + ab;
+  l.partials_offset_bytes = 2 * xb + 2 * ab;
+  l.total_bytes = l.partials_offset_bytes + round_up((int64_t)batch * kFroChunksMax * 4, 256);
+  *out = l;
+  return OK;
+}
+
+int muon_b200_ns_run(void* workspace, int batch, int64_t m, int64_t n, int mode, int steps,
+                     const float* coeffs, float eps, int* result_slot, muon_b200_stream_t stream) {
+  if (!workspace) return set_error(ERR_INVALID_ARG, "workspace is NULL");
+  if (reinterpret_cast<uintptr_t>(workspace) & 255)
+    return set_error(ERR_ALIGNMENT, "NS workspace must be 256-byte aligned");
+  if (mode != MUON_B200_NS_AOL4 && mode != MUON_B200_NS_CLASSIC5)
+    return set_error(ERR_INVALID_ARG, "unknown NS mode %d", mode);
+  if (steps < 0 || steps > 64) return set_error(ERR_INVALID_ARG, "NS steps out of range: %d", steps);
+  if (steps == 0) steps = (mode == MUON_B200_NS_AOL4) ? 4 : 5;
+  if (!coeffs && mode == MUON_B200_NS_AOL4 && steps > 4)
+    return set_error(ERR_INVALID_ARG, "the AOL table has 4 iterations; pass coeffs for %d", steps);
+  muon_b200_ns_layout l;
+  int rc = muon_b200_ns_workspace_layout(batch, m, n, &l);
+  if (rc != OK) return rc;
+  char* ws = static_cast<char*>(workspace);
+  __nv_bfloat16* X = bf(static_cast<void*>(ws + l.x_offset_bytes));
+  __nv_bfloat16* C = bf(static_cast<void*>(ws + l.c_offset_bytes));
+  __nv_bfloat16* A = bf(static_cast<void*>(ws + l.a_offset_bytes));
+  __nv_bfloat16* B = bf(static_cast<void*>(ws + l.b_offset_bytes));
+  float* partials = reinterpret_cast<float*>(ws + l.partials_offset_bytes);
+  cudaStream_t st = as_stream(stream);
+
+  int slot = 0;
+  bool have_gram = false;
+  if (mode == MUON_B200_NS_AOL4) {
+    // Gram matrix once, shared by the rescale and the first iteration (muon.py:778-785).
+    rc = launch_ns_gemm(MODE_SYRK, X, l.ldn, l.x_bs, X, l.ldn, l.x_bs, A, l.ldm, l.a_bs, batch, m,
+                        m, n, 1.f, 0.f, st);
+    if (rc != OK) return rc;
+    rc = launch_aol_rescale(X, l.ldn, l.x_bs, A, l.ldm, l.a_bs, (int)m, (int)n, batch, eps, st);
+    if (rc != OK) return rc;
+    have_gram = true;
+  } else {
+    rc = launch_fro_normalize(X, l.ldn, l.x_bs, (int)m, (int)n, batch, eps, partials,
+                              fro_chunks(m), st);
+    if (rc != OK) return rc;
+  }
+  for (int k = 0; k < steps; ++k) {
+    float a, b, c;
+    if (coeffs) {
+      a = coeffs[3 * k]; b = coeffs[3 * k + 1]; c = coeffs[3 * k + 2];
+    } else if (mode == MUON_B200_NS_AOL4) {
+      a = kAol4[k][0]; b = kAol4[k][1]; c = kAol4[k][2];
+    } else {
+      a = kClassic[0]; b = kClassic[1]; c = kClassic[2];
+    }
+    if (!have_gram) {
+      rc = launch_ns_gemm(MODE_SYRK, X, l.ldn, l.x_bs, X, l.ldn, l.x_bs, A, l.ldm, l.a_bs, batch,
+                          m, m, n, 1.f, 0.f, st);
+      if (rc != OK) return rc;
+    }
+    have_gram = false;
+    rc = launch_ns_gemm(MODE_AXPBY, A, l.ldm, l.a_bs, A, l.ldm, l.a_bs, B, l.ldm, l.a_bs, batch, m,
+                        m, m, c, b, st);
+    if (rc != OK) return rc;
+    rc = launch_ns_gemm(MODE_BX, B, l.ldm, l.a_bs, X, l.ldn, l.x_bs, C, l.ldn, l.x_bs, batch, m, n,
+                        m, a, 0.f, st);
+    if (rc != OK) return rc;
+    __nv_bfloat16* t = X; X = C; C = t;
+    slot ^= 1;
+  }
+  if (result_slot) *result_slot = slot;
+  return OK;
+}
+
+int muon_b200_prologue(void* const* grads, void* const* moms, int count, int64_t rows,
+                       int64_t cols, int dtype, double beta, int nesterov, void* x, int64_t ldx,
+                       int64_t x_bs, int transpose_out, muon_b200_stream_t stream) {
+  int rc = check_dtype(dtype);
+  if (rc != OK) return rc;
+  if (!grads || !moms || !x) return set_error(ERR_INVALID_ARG, "null pointer passed to prologue");
+  if (count < 1 || rows < 1 || cols < 1 || rows > INT32_MAX || cols > INT32_MAX)
+    return set_error(ERR_INVALID_ARG, "prologue needs count, rows, cols >= 1");
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (ldx % 8) || (x_bs % 8))
+    return set_error(ERR_ALIGNMENT, "prologue X must be 16-byte aligned with pitches %% 8 == 0");
+  if (ldx < (transpose_out ? rows : cols))
+    return set_error(ERR_INVALID_ARG, "prologue X pitch %lld is shorter than a row", (long long)ldx);
+  const int vec = dtype == DT_F32 ? 4 : 8;
+  for (int base = 0; base < count; base += kMaxTensors) {
+    const int n = count - base < kMaxTensors ? count - base : kMaxTensors;
+    PrologueArgs a{};
+    for (int i = 0; i < n; ++i) {
+      if (!grads[base + i] || !moms[base + i])
+        return set_error(ERR_INVALID_ARG, "prologue tensor %d has a null pointer", base + i);
+      a.grad[i] = grads[base + i];
+      a.mom[i] = moms[base + i];
+    }
+    a.x = bf(x) + (int64_t)base * x_bs;
+    a.x_bs = x_bs;
+    a.ldx = ldx;
+    a.count = n;
+    a.rows = (int)rows;
+    a.cols = (int)cols;
+    a.nesterov = nesterov ? 1 : 0;
+    a.vec_ok = (cols % vec == 0) && all_aligned16(grads + base, n) && all_aligned16(moms + base, n);
+    a.w_mom = (float)(1.0 - beta);
+    a.beta = (float)beta;
+    rc = launch_prologue(a, dtype, transpose_out ? 1 : 0, as_stream(stream));
+    if (rc != OK) return rc;
+  }
+  return OK;
+}
+
+int muon_b200_epilogue(void* const* params, int count, int64_t rows, int64_t cols, int dtype,
+                       const void* u, int64_t ldu, int64_t u_bs, int u_transposed, double lr,
+                       double weight_decay, double scale, muon_b200_stream_t stream) {
+  int rc = check_dtype(dtype);
+  if (rc != OK) return rc;
+  if (!params || !u) return set_error(ERR_INVALID_ARG, "null pointer passed to epilogue");
+  if (count < 1 || rows < 1 || cols < 1 || rows > INT32_MAX || cols > INT32_MAX)
+    return set_error(ERR_INVALID_ARG, "epilogue needs count, rows, cols >= 1");
+  if ((reinterpret_cast<uintptr_t>(u) & 15) || (ldu % 8) || (u_bs % 8))
+    return set_error(ERR_ALIGNMENT, "epilogue U must be 16-byte aligned with pitches %% 8 == 0");
+  const int vec = dtype == DT_F32 ? 4 : 8;
+  for (int base = 0; base < count; base += kMaxTensors) {
+    const int n = count - base < kMaxTensors ? count - base : kMaxTensors;
+    EpilogueArgs a{};
+    for (int i = 0; i < n; ++i) {
+      if (!params[base + i])
+        return set_error(ERR_INVALID_ARG, "epilogue tensor %d has a null pointer", base + i);
+      a.param[i] = params[base + i];
+    }
+    a.u = bf(u) + (int64_t)base * u_bs;
+    a.u_bs = u_bs;
+    a.ldu = ldu;
+    a.count = n;
+    a.rows = (int)rows;
+    a.cols = (int)cols;
+    a.vec_ok = (cols % vec == 0) && all_aligned16(params + base, n);
+    a.scale = (float)scale;
+    a.decay = (float)(1.0 - lr * weight_decay);
+    a.neg_lr = (float)(-lr);
+    rc = launch_epilogue(a, dtype, u_transposed ? 1 : 0, as_stream(stream));
+    if (rc != OK) return rc;
+  }
+  return OK;
+}
+
+int muon_b200_muon_step(void* const* params, void* const* grads, void* const* moms, int count,
+                        int64_t rows, int64_t cols, int dtype, double lr, double weight_decay,
+                        double beta, int nesterov, double scale, int ns_mode, int ns_steps,
+                        const float* ns_coeffs, float ns_eps, void* workspace,
+                        int64_t workspace_bytes, muon_b200_stream_t stream) {
+  if (count < 1 || rows < 1 || cols < 1)
+    return set_error(ERR_INVALID_ARG, "muon_step needs count, rows, cols >= 1");
+  if (!workspace) return set_error(ERR_INVALID_ARG, "workspace is NULL");
+  const bool tall = rows > cols;  // the iteration runs on the transposed matrix (muon.py:761-762)
+  const int64_t m = tall ? cols : rows;
+  const int64_t n = tall ? rows : cols;
+  muon_b200_ns_layout l;
+  int rc = muon_b200_ns_workspace_layout(count, m, n, &l);
+  if (rc != OK) return rc;
+  if (workspace_bytes < l.total_bytes)
+    return set_error(ERR_INVALID_ARG, "workspace too small: %lld bytes given, %lld needed",
+                     (long long)workspace_bytes, (long long)l.total_bytes);
+  if (reinterpret_cast<uintptr_t>(workspace) & 255)
+    return set_error(ERR_ALIGNMENT, "NS workspace must be 256-byte aligned");
+  char* ws = static_cast<char*>(workspace);
+  rc = muon_b200_prologue(grads, moms, count, rows, cols, dtype, beta, nesterov,
+                          ws + l.x_offset_bytes, l.ldn, l.x_bs, tall ? 1 : 0, stream);
+  if (rc != OK) return rc;
+  int slot = 0;
+  rc = muon_b200_ns_run(workspace, count, m, n, ns_mode, ns_steps, ns_coeffs, ns_eps, &slot, stream);
+  if (rc != OK) return rc;
+  const void* u = ws + (slot == 0 ? l.x_offset_bytes : l.c_offset_bytes);
+  return muon_b200_epilogue(params, count, rows, cols, dtype, u, l.ldn, l.x_bs, tall ? 1 : 0, lr,
+                            weight_decay, scale, stream);
+}
+
+int muon_b200_adam(void* const* params, void* const* grads, void* const* exp_avg,
+                   void* const* exp_avg_sq, const int64_t* numel, const int64_t* steps, int count,
+                   int dtype, double lr, double weight_decay, double beta1, double beta2,
+                   double eps, muon_b200_stream_t stream) {
+  int rc = check_dtype(dtype);
+  if (rc != OK) return rc;
+  if (!params || !grads || !exp_avg || !exp_avg_sq || !numel || !steps)
+    return set_error(ERR_INVALID_ARG, "null pointer passed to adam");
+  if (count < 0) return set_error(ERR_INVALID_ARG, "adam count is negative");
+  int sms = 0;
+  if ((rc = device_sm_count(&sms)) != OK) return rc;
+  const int per_block = adam_elems_per_block(dtype);
+  const int vec = dtype == DT_F32 ? 4 : 8;
+  (void)vec;
+  for (int base = 0; base < count; base += kMaxTensors) {
+    const int n = count - base < kMaxTensors ? count - base : kMaxTensors;
+    AdamArgs a{};
+    a.count = n;
+    a.block_start[0] = 0;
+    for (int i = 0; i < n; ++i) {
+      const int k = base + i;
+      if (!params[k] || !grads[k] || !exp_avg[k] || !exp_avg_sq[k])
+        return set_error(ERR_INVALID_ARG, "adam tensor %d has a null pointer", k);
+      if (numel[k] < 0 || steps[k] < 1)
+        return set_error(ERR_INVALID_ARG, "adam tensor %d: numel must be >= 0 and step >= 1", k);
+      a.param[i] = params[k];
+      a.grad[i] = grads[k];
+      a.exp_avg[i] = exp_avg[k];
+      a.exp_avg_sq[i] = exp_avg_sq[k];
+      a.numel[i] = numel[k];
+      a.bc1[i] = (float)(1.0 - std::pow(beta1, (double)steps[k]));
+      a.bc2[i] = (float)(1.0 - std::pow(beta2, (double)steps[k]));
+      const uintptr_t bits = reinterpret_cast<uintptr_t>(params[k]) |
+                             reinterpret_cast<uintptr_t>(grads[k]) |
+                             reinterpret_cast<uintptr_t>(exp_avg[k]) |
+                             reinterpret_cast<uintptr_t>(exp_avg_sq[k]);
+      a.vec_ok[i] = (bits & 15) == 0;
+      const int64_t blocks = (numel[k] + per_block - 1) / per_block;
+      if (blocks + a.block_start[i] > INT32_MAX)
+        return set_error(ERR_UNSUPPORTED, "adam tensor %d is too large for one launch", k);
+      a.block_start[i + 1] = a.block_start[i] + (int)blocks;
+    }
+    a.w1 = (float)(1.0 - beta1);
+    a.w2 = (float)(1.0 - beta2);
+    a.eps = (float)eps;
+    a.decay = (float)(1.0 - lr * weight_decay);
+    a.neg_lr = (float)(-lr);
+    rc = launch_adam(a, dtype, as_stream(stream));
+    if (rc != OK) return rc;
+  }
+  return OK;
+}
+
+}  // extern "C"

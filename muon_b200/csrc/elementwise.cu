@@ -1,0 +1,598 @@
+// HBM-bound kernels of the Muon step: momentum prologue, AOL / Frobenius rescale,
+// update epilogue and the fused Adam step. All of them move 128 bits per thread per
+// access where alignment allows, are grid-stride over tiles, and take up to
+// kMaxTensors same-shape tensors per launch so that a group of parameters costs one
+// launch instead of one per parameter.
+#include "common.cuh"
+#include "elementwise.h"
+#include "ns_gemm.h"
+
+namespace mb {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kTileRows = 64;
+
+template <typename T>
+struct Vec;
+template <>
+struct Vec<float> {
+  static constexpr int N = 4;
+  using Raw = float4;
+  __device__ static void load(const float* p, float (&v)[4]) {
+    float4 r = *reinterpret_cast<const float4*>(p);
+    v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+  }
+  __device__ static void store(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <>
+struct Vec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static void load(const __nv_bfloat16* p, float (&v)[8]) {
+    uint4 r = *reinterpret_cast<const uint4*>(p);
+    uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[2 * j] = bf16_bits_to_float(w[j] & 0xffffu);
+      v[2 * j + 1] = bf16_bits_to_float(w[j] >> 16);
+    }
+  }
+  __device__ static void store(__nv_bfloat16* p, const float (&v)[8]) {
+    *reinterpret_cast<uint4*>(p) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
+                                              pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+  }
+};
+
+template <typename T>
+__device__ __forceinline__ float to_f(T v);
+template <>
+__device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// Round an fp32 intermediate to the storage type and back, i.e. what an eager
+// elementwise op leaves in a tensor of type T.
+template <typename T>
+__device__ __forceinline__ float round_to(float v);
+template <>
+__device__ __forceinline__ float round_to<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float round_to<__nv_bfloat16>(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+template <typename T>
+__device__ __forceinline__ T from_f(float v);
+template <>
+__device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float bf16_round(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+
+// torch.lerp(self, end, weight) in opmath precision: two algebraically equal forms,
+// picked by |weight| < 0.5 (ATen/native/Lerp.h).
+__device__ __forceinline__ float torch_lerp(float self, float end, float w) {
+  const float d = end - self;
+  return (fabsf(w) < 0.5f) ? fmaf(w, d, self) : fmaf(-d, 1.0f - w, end);
+}
+
+// ---------------------------------------------------------------------------
+// Prologue (reference muon_update, muon.py:9-12 and the cast/transposition of
+// zeropower_via_newtonschulz5, muon.py:760-764):
+//   mom  <- lerp(mom, grad, 1 - beta)
+//   grad <- lerp(grad, mom, beta)            (Nesterov; written back like lerp_ does)
+//   X    <- bf16(nesterov ? grad : mom), stored [rows, cols] or transposed [cols, rows]
+// A tile is kTileRows x (16 * Vec<T>::N) elements.
+// ---------------------------------------------------------------------------
+template <typename T, bool TRANSPOSE>
+__global__ void __launch_bounds__(kThreads)
+prologue_kernel(const PrologueArgs a) {
+  constexpr int V = Vec<T>::N;
+  constexpr int kTileCols = 16 * V;
+  // Transposition staging: [col][row] with one pad column of 2 bf16 to skew banks.
+  __shared__ __nv_bfloat16 tile[TRANSPOSE ? kTileCols : 1][TRANSPOSE ? kTileRows + 2 : 1];
+
+  const int tiles_c = (a.cols + kTileCols - 1) / kTileCols;
+  const int tiles_r = (a.rows + kTileRows - 1) / kTileRows;
+  const long long tiles_per = (long long)tiles_c * tiles_r;
+  const long long total = tiles_per * a.count;
+  const int tx = threadIdx.x & 15;
+  const int ty = threadIdx.x >> 4;
+  const float w1 = a.w_mom;  // float(1 - beta)
+  const float w2 = a.beta;   // float(beta)
+
+  for (long long t = blockIdx.x; t < total; t += gridDim.x) {
+    const int ti = (int)(t / tiles_per);
+    const long long rem = t - (long long)ti * tiles_per;
+    const int tr = (int)(rem / tiles_c);
+    const int tcn = (int)(rem - (long long)tr * tiles_c);
+    T* g = static_cast<T*>(a.grad[ti]);
+    T* m = static_cast<T*>(a.mom[ti]);
+    __nv_bfloat16* x = a.x + (long long)ti * a.x_bs;
+    const int c0 = tcn * kTileCols + tx * V;
+
+#pragma unroll
+    for (int it = 0; it < kTileRows / 16; ++it) {
+      const int rl = it * 16 + ty;
+      const int r = tr * kTileRows + rl;
+      float xv[V];
+#pragma unroll
+      for (int j = 0; j < V; ++j) xv[j] = 0.f;
+      if (r < a.rows && c0 < a.cols) {
+        const long long off = (long long)r * a.cols + c0;
+        float gv[V], mv[V];
+        const bool full = a.vec_ok && (c0 + V <= a.cols);
+        if (full) {
+          Vec<T>::load(g + off, gv);
+          Vec<T>::load(m + off, mv);
+        } else {
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            const bool in = c0 + j < a.cols;
+            gv[j] = in ? to_f<T>(g[off + j]) : 0.f;
+            mv[j] = in ? to_f<T>(m[off + j]) : 0.f;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          mv[j] = round_to<T>(torch_lerp(mv[j], gv[j], w1));
+          if (a.nesterov) {
+            gv[j] = round_to<T>(torch_lerp(gv[j], mv[j], w2));
+            xv[j] = bf16_round(gv[j]);
+          } else {
+            xv[j] = bf16_round(mv[j]);
+          }
+        }
+        if (full) {
+          Vec<T>::store(m + off, mv);
+          if (a.nesterov) Vec<T>::store(g + off, gv);
+        } else {
+#pragma unroll
+          for (int j = 0; j < V; ++j)
+            if (c0 + j < a.cols) {
+              m[off + j] = from_f<T>(mv[j]);
+              if (a.nesterov) g[off + j] = from_f<T>(gv[j]);
+            }
+        }
+        if (!TRANSPOSE) {
+          __nv_bfloat16* xr = x + (long long)r * a.ldx + c0;
+          if (c0 + V <= a.cols) {
+            if (V == 8) {
+              *reinterpret_cast<uint4*>(xr) =
+                  make_uint4(pack_bf16x2(xv[0], xv[1]), pack_bf16x2(xv[2], xv[3]),
+                             pack_bf16x2(xv[V - 4], xv[V - 3]), pack_bf16x2(xv[V - 2], xv[V - 1]));
+            } else {
+              *reinterpret_cast<uint2*>(xr) =
+                  make_uint2(pack_bf16x2(xv[0], xv[1]), pack_bf16x2(xv[2], xv[3]));
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < V; ++j)
+              if (c0 + j < a.cols) xr[j] = __float2bfloat16_rn(xv[j]);
+          }
+        }
+      }
+      if (TRANSPOSE) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) tile[tx * V + j][rl] = __float2bfloat16_rn(xv[j]);
+      }
+    }
+    if (TRANSPOSE) {
+      __syncthreads();
+      // Output rows are input columns. 8 threads cover one output row of 64 elements.
+      const int seg = threadIdx.x & 7;
+      for (int cl = threadIdx.x >> 3; cl < kTileCols; cl += kThreads / 8) {
+        const int c = tcn * kTileCols + cl;
+        const int r0 = tr * kTileRows + seg * 8;
+        if (c < a.cols && r0 < a.rows) {
+          __nv_bfloat16* xr = x + (long long)c * a.ldx + r0;
+          if (r0 + 8 <= a.rows) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              w[j] = *reinterpret_cast<const uint32_t*>(&tile[cl][seg * 8 + 2 * j]);
+            *reinterpret_cast<uint4*>(xr) = make_uint4(w[0], w[1], w[2], w[3]);
+          } else {
+            for (int j = 0; j < 8 && r0 + j < a.rows; ++j) xr[j] = tile[cl][seg * 8 + j];
+          }
+        }
+      }
+      __syncthreads();
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Epilogue (reference muon.py:14 and :66-67): with U the bf16 NS output
+//   U' = bf16(U * scale)            (update *= max(1, rows/cols)**0.5)
+//   p  = T(p * (1 - lr*wd))         (p.mul_)
+//   p  = T(p - lr * U')             (p.add_(update, alpha=-lr))
+// U is [rows, cols] or, for tall parameters, stored transposed as [cols, rows].
+// ---------------------------------------------------------------------------
+template <typename T, bool TRANSPOSE>
+__global__ void __launch_bounds__(kThreads)
+epilogue_kernel(const EpilogueArgs a) {
+  constexpr int V = Vec<T>::N;
+  constexpr int kTileCols = 16 * V;
+  __shared__ __nv_bfloat16 tile[TRANSPOSE ? kTileCols : 1][TRANSPOSE ? kTileRows + 2 : 1];
+
+  const int tiles_c = (a.cols + kTileCols - 1) / kTileCols;
+  const int tiles_r = (a.rows + kTileRows - 1) / kTileRows;
+  const long long tiles_per = (long long)tiles_c * tiles_r;
+  const long long total = tiles_per * a.count;
+  const int tx = threadIdx.x & 15;
+  const int ty = threadIdx.x >> 4;
+
+  for (long long t = blockIdx.x; t < total; t += gridDim.x) {
+    const int ti = (int)(t / tiles_per);
+    const long long rem = t - (long long)ti * tiles_per;
+    const int tr = (int)(rem / tiles_c);
+    const int tcn = (int)(rem - (long long)tr * tiles_c);
+    T* p = static_cast<T*>(a.param[ti]);
+    const __nv_bfloat16* u = a.u + (long long)ti * a.u_bs;
+
+    if (TRANSPOSE) {
+      // Stage U[c, r0..r0+63] rows into tile[c][r].
+      const int seg = threadIdx.x & 7;
+      for (int cl = threadIdx.x >> 3; cl < kTileCols; cl += kThreads / 8) {
+        const int c = tcn * kTileCols + cl;
+        const int r0 = tr * kTileRows + seg * 8;
+        if (c < a.cols && r0 < a.rows) {
+          const __nv_bfloat16* ur = u + (long long)c * a.ldu + r0;
+          if (r0 + 8 <= a.rows) {
+            uint4 q = *reinterpret_cast<const uint4*>(ur);
+            uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<uint32_t*>(&tile[cl][seg * 8 + 2 * j]) = w[j];
+          } else {
+            for (int j = 0; j < 8 && r0 + j < a.rows; ++j) tile[cl][seg * 8 + j] = ur[j];
+          }
+        }
+      }
+      __syncthreads();
+    }
+
+    const int c0 = tcn * kTileCols + tx * V;
+#pragma unroll
+    for (int it = 0; it < kTileRows / 16; ++it) {
+      const int rl = it * 16 + ty;
+      const int r = tr * kTileRows + rl;
+      if (r < a.rows && c0 < a.cols) {
+        const long long off = (long long)r * a.cols + c0;
+        const bool full = a.vec_ok && (c0 + V <= a.cols);
+        float pv[V], uv[V];
+        if (full) {
+          Vec<T>::load(p + off, pv);
+        } else {
+#pragma unroll
+          for (int j = 0; j < V; ++j) pv[j] = (c0 + j < a.cols) ? to_f<T>(p[off + j]) : 0.f;
+        }
+        if (TRANSPOSE) {
+#pragma unroll
+          for (int j = 0; j < V; ++j) uv[j] = __bfloat162float(tile[tx * V + j][rl]);
+        } else {
+          const __nv_bfloat16* ur = u + (long long)r * a.ldu + c0;
+          if (c0 + V <= a.cols) {
+            if (V == 8) {
+              float tmp[8];
+              Vec<__nv_bfloat16>::load(ur, tmp);
+#pragma unroll
+              for (int j = 0; j < V; ++j) uv[j] = tmp[j];
+            } else {
+              uint2 q = *reinterpret_cast<const uint2*>(ur);
+              uv[0] = bf16_bits_to_float(q.x & 0xffffu);
+              uv[1] = bf16_bits_to_float(q.x >> 16);
+              uv[2] = bf16_bits_to_float(q.y & 0xffffu);
+              uv[3] = bf16_bits_to_float(q.y >> 16);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < V; ++j) uv[j] = (c0 + j < a.cols) ? __bfloat162float(ur[j]) : 0.f;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float us = bf16_round(uv[j] * a.scale);
+          const float p1 = round_to<T>(pv[j] * a.decay);
+          pv[j] = round_to<T>(fmaf(a.neg_lr, us, p1));
+        }
+        if (full) {
+          Vec<T>::store(p + off, pv);
+        } else {
+#pragma unroll
+          for (int j = 0; j < V; ++j)
+            if (c0 + j < a.cols) p[off + j] = from_f<T>(pv[j]);
+        }
+      }
+    }
+    if (TRANSPOSE) __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------
+// AOL rescale (reference muon.py:779-785), one CTA per matrix row i:
+//   s_i  = bf16( max( sum_j |A_ij|, eps ) )
+//   X_i: = bf16( X_i: * rsqrt(s_i) )
+//   A_i: = bf16( A_i: / s_i )          (rows only, exactly as the reference does)
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+aol_rescale_kernel(__nv_bfloat16* X, long long ldx, long long x_bs, __nv_bfloat16* A, long long lda,
+                   long long a_bs, int m, int n, int batch, float eps) {
+  __shared__ float warp_sums[kThreads / 32];
+  __shared__ float s_bcast;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long rows_total = (long long)m * batch;
+  for (long long row = blockIdx.x; row < rows_total; row += gridDim.x) {
+    const int b = (int)(row / m);
+    const int i = (int)(row - (long long)b * m);
+    __nv_bfloat16* arow = A + (long long)b * a_bs + (long long)i * lda;
+    __nv_bfloat16* xrow = X + (long long)b * x_bs + (long long)i * ldx;
+    float acc = 0.f;
+    const int mv = m & ~7;
+    for (int j = threadIdx.x * 8; j < mv; j += kThreads * 8) {
+      float v[8];
+      Vec<__nv_bfloat16>::load(arow + j, v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc += fabsf(v[k]);
+    }
+    for (int j = mv + threadIdx.x; j < m; j += kThreads) acc += fabsf(__bfloat162float(arow[j]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) warp_sums[warp] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float s = 0.f;
+      for (int w = 0; w < kThreads / 32; ++w) s += warp_sums[w];
+      s_bcast = bf16_round(fmaxf(s, eps));
+    }
+    __syncthreads();
+    const float s = s_bcast;
+    const float rs = rsqrtf(s);
+    for (int j = threadIdx.x * 8; j < mv; j += kThreads * 8) {
+      float v[8];
+      Vec<__nv_bfloat16>::load(arow + j, v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = __fdiv_rn(v[k], s);
+      Vec<__nv_bfloat16>::store(arow + j, v);
+    }
+    for (int j = mv + threadIdx.x; j < m; j += kThreads)
+      arow[j] = __float2bfloat16_rn(__fdiv_rn(__bfloat162float(arow[j]), s));
+    const int nv = n & ~7;
+    for (int j = threadIdx.x * 8; j < nv; j += kThreads * 8) {
+      float v[8];
+      Vec<__nv_bfloat16>::load(xrow + j, v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] *= rs;
+      Vec<__nv_bfloat16>::store(xrow + j, v);
+    }
+    for (int j = nv + threadIdx.x; j < n; j += kThreads)
+      xrow[j] = __float2bfloat16_rn(__bfloat162float(xrow[j]) * rs);
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Frobenius normalisation of the classic iteration (commented block, muon.py:282):
+//   X = X / (||X||_F + 1e-7), bf16 eager semantics: the norm and the sum are each
+//   rounded to bf16 before the division.
+// Pass 1 writes one partial sum of squares per (matrix, chunk); pass 2 re-adds the
+// partials in a fixed order, so the result does not depend on scheduling.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+sumsq_partial_kernel(const __nv_bfloat16* X, long long ldx, long long x_bs, int m, int n, int chunks,
+                     float* partials) {
+  __shared__ float warp_sums[kThreads / 32];
+  const int b = blockIdx.y, ch = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float acc = 0.f;
+  for (int i = ch; i < m; i += chunks) {
+    const __nv_bfloat16* xrow = X + (long long)b * x_bs + (long long)i * ldx;
+    const int nv = n & ~7;
+    for (int j = threadIdx.x * 8; j < nv; j += kThreads * 8) {
+      float v[8];
+      Vec<__nv_bfloat16>::load(xrow + j, v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc = fmaf(v[k], v[k], acc);
+    }
+    for (int j = nv + threadIdx.x; j < n; j += kThreads) {
+      float v = __bfloat162float(xrow[j]);
+      acc = fmaf(v, v, acc);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) warp_sums[warp] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int w = 0; w < kThreads / 32; ++w) s += warp_sums[w];
+    partials[(long long)b * chunks + ch] = s;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+fro_scale_kernel(__nv_bfloat16* X, long long ldx, long long x_bs, int m, int n, int chunks,
+                 const float* partials, float eps) {
+  __shared__ float s_den;
+  const int b = blockIdx.y, ch = blockIdx.x;
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int c = 0; c < chunks; ++c) s += partials[(long long)b * chunks + c];
+    s_den = bf16_round(bf16_round(sqrtf(s)) + eps);
+  }
+  __syncthreads();
+  const float den = s_den;
+  for (int i = ch; i < m; i += chunks) {
+    __nv_bfloat16* xrow = X + (long long)b * x_bs + (long long)i * ldx;
+    const int nv = n & ~7;
+    for (int j = threadIdx.x * 8; j < nv; j += kThreads * 8) {
+      float v[8];
+      Vec<__nv_bfloat16>::load(xrow + j, v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = __fdiv_rn(v[k], den);
+      Vec<__nv_bfloat16>::store(xrow + j, v);
+    }
+    for (int j = nv + threadIdx.x; j < n; j += kThreads)
+      xrow[j] = __float2bfloat16_rn(__fdiv_rn(__bfloat162float(xrow[j]), den));
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Fused Adam step (reference adam_update + the two in-place parameter ops,
+// muon.py:104-109 and :196-197), every intermediate rounded to the tensor dtype as
+// the eager ops do:
+//   m  = lerp(m, g, 1-b1) ; v = lerp(v, g*g, 1-b2)
+//   u  = (m / bc1) / (sqrt(v / bc2) + eps)
+//   p  = p * (1 - lr*wd) ; p = p - lr * u
+// Blocks are assigned to tensors through block_start (prefix sums of per-tensor
+// block counts), so tensors of different sizes share a launch.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+adam_kernel(const AdamArgs a) {
+  constexpr int V = Vec<T>::N;
+  constexpr int kPerBlock = kThreads * V * 4;
+  int ti = 0;
+  while (ti + 1 < a.count && (int)blockIdx.x >= a.block_start[ti + 1]) ++ti;
+  const long long base = (long long)((int)blockIdx.x - a.block_start[ti]) * kPerBlock;
+  T* p = static_cast<T*>(a.param[ti]);
+  const T* g = static_cast<const T*>(a.grad[ti]);
+  T* m = static_cast<T*>(a.exp_avg[ti]);
+  T* v = static_cast<T*>(a.exp_avg_sq[ti]);
+  const long long numel = a.numel[ti];
+  const float bc1 = a.bc1[ti], bc2 = a.bc2[ti];
+  const bool vec_ok = a.vec_ok[ti] != 0;
+
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const long long off = base + ((long long)it * kThreads + threadIdx.x) * V;
+    if (off >= numel) break;
+    const bool full = vec_ok && (off + V <= numel);
+    float pv[V], gv[V], mv[V], vv[V];
+    if (full) {
+      Vec<T>::load(p + off, pv);
+      Vec<T>::load(g + off, gv);
+      Vec<T>::load(m + off, mv);
+      Vec<T>::load(v + off, vv);
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const bool in = off + j < numel;
+        pv[j] = in ? to_f<T>(p[off + j]) : 0.f;
+        gv[j] = in ? to_f<T>(g[off + j]) : 0.f;
+        mv[j] = in ? to_f<T>(m[off + j]) : 0.f;
+        vv[j] = in ? to_f<T>(v[off + j]) : 1.f;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      mv[j] = round_to<T>(torch_lerp(mv[j], gv[j], a.w1));
+      const float g2 = round_to<T>(gv[j] * gv[j]);
+      vv[j] = round_to<T>(torch_lerp(vv[j], g2, a.w2));
+      const float mh = round_to<T>(__fdiv_rn(mv[j], bc1));
+      const float vh = round_to<T>(__fdiv_rn(vv[j], bc2));
+      const float den = round_to<T>(round_to<T>(__fsqrt_rn(vh)) + a.eps);
+      const float u = round_to<T>(__fdiv_rn(mh, den));
+      const float p1 = round_to<T>(pv[j] * a.decay);
+      pv[j] = round_to<T>(fmaf(a.neg_lr, u, p1));
+    }
+    if (full) {
+      Vec<T>::store(p + off, pv);
+      Vec<T>::store(m + off, mv);
+      Vec<T>::store(v + off, vv);
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; ++j)
+        if (off + j < numel) {
+          p[off + j] = from_f<T>(pv[j]);
+          m[off + j] = from_f<T>(mv[j]);
+          v[off + j] = from_f<T>(vv[j]);
+        }
+    }
+  }
+}
+
+int grid_for(long long work_items, int per_sm) {
+  int sms = 0;
+  if (device_sm_count(&sms) != OK) return -1;
+  long long cap = (long long)sms * per_sm;
+  long long g = work_items < cap ? work_items : cap;
+  return (int)(g < 1 ? 1 : g);
+}
+
+}  // namespace
+
+int adam_elems_per_block(int dtype) {
+  return kThreads * (dtype == DT_F32 ? 4 : 8) * 4;
+}
+
+int launch_prologue(const PrologueArgs& a, int dtype, int transpose, cudaStream_t stream) {
+  const int tile_cols = 16 * (dtype == DT_F32 ? 4 : 8);
+  long long tiles = (long long)((a.cols + tile_cols - 1) / tile_cols) *
+                    ((a.rows + kTileRows - 1) / kTileRows) * a.count;
+  int grid = grid_for(tiles, 8);
+  if (grid < 0) return ERR_UNSUPPORTED;
+  if (dtype == DT_F32) {
+    if (transpose) prologue_kernel<float, true><<<grid, kThreads, 0, stream>>>(a);
+    else prologue_kernel<float, false><<<grid, kThreads, 0, stream>>>(a);
+  } else {
+    if (transpose) prologue_kernel<__nv_bfloat16, true><<<grid, kThreads, 0, stream>>>(a);
+    else prologue_kernel<__nv_bfloat16, false><<<grid, kThreads, 0, stream>>>(a);
+  }
+  MB_CUDA_CHECK(cudaGetLastError());
+  return OK;
+}
+
+int launch_epilogue(const EpilogueArgs& a, int dtype, int transpose, cudaStream_t stream) {
+  const int tile_cols = 16 * (dtype == DT_F32 ? 4 : 8);
+  long long tiles = (long long)((a.cols + tile_cols - 1) / tile_cols) *
+                    ((a.rows + kTileRows - 1) / kTileRows) * a.count;
+  int grid = grid_for(tiles, 8);
+  if (grid < 0) return ERR_UNSUPPORTED;
+  if (dtype == DT_F32) {
+    if (transpose) epilogue_kernel<float, true><<<grid, kThreads, 0, stream>>>(a);
+    else epilogue_kernel<float, false><<<grid, kThreads, 0, stream>>>(a);
+  } else {
+    if (transpose) epilogue_kernel<__nv_bfloat16, true><<<grid, kThreads, 0, stream>>>(a);
+    else epilogue_kernel<__nv_bfloat16, false><<<grid, kThreads, 0, stream>>>(a);
+  }
+  MB_CUDA_CHECK(cudaGetLastError());
+  return OK;
+}
+
+int launch_aol_rescale(__nv_bfloat16* X, long long ldx, long long x_bs, __nv_bfloat16* A,
+                       long long lda, long long a_bs, int m, int n, int batch, float eps,
+                       cudaStream_t stream) {
+  int grid = grid_for((long long)m * batch, 16);
+  if (grid < 0) return ERR_UNSUPPORTED;
+  aol_rescale_kernel<<<grid, kThreads, 0, stream>>>(X, ldx, x_bs, A, lda, a_bs, m, n, batch, eps);
+  MB_CUDA_CHECK(cudaGetLastError());
+  return OK;
+}
+
+int launch_fro_normalize(__nv_bfloat16* X, long long ldx, long long x_bs, int m, int n, int batch,
+                         float eps, float* partials, int chunks, cudaStream_t stream) {
+  dim3 grid(chunks, batch);
+  sumsq_partial_kernel<<<grid, kThreads, 0, stream>>>(X, ldx, x_bs, m, n, chunks, partials);
+  MB_CUDA_CHECK(cudaGetLastError());
+  fro_scale_kernel<<<grid, kThreads, 0, stream>>>(X, ldx, x_bs, m, n, chunks, partials, eps);
+  MB_CUDA_CHECK(cudaGetLastError());
+  return OK;
+}
+
+int launch_adam(const AdamArgs& a, int dtype, cudaStream_t stream) {
+  int blocks = a.block_start[a.count];
+  if (blocks <= 0) return OK;
+  if (dtype == DT_F32) adam_kernel<float><<<blocks, kThreads, 0, stream>>>(a);
+  else adam_kernel<__nv_bfloat16><<<blocks, kThreads, 0, stream>>>(a);
+  MB_CUDA_CHECK(cudaGetLastError());
+  return OK;
+}
+
+}  // namespace mb

@@ -1,0 +1,68 @@
+// Internal interface between the elementwise kernels and the C-ABI layer.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace mb {
+
+enum DType : int { DT_F32 = 0, DT_BF16 = 1 };
+
+constexpr int kMaxTensors = 32;  // tensors per multi-tensor launch
+
+struct PrologueArgs {
+  void* grad[kMaxTensors];
+  void* mom[kMaxTensors];
+  __nv_bfloat16* x;   // X of tensor i starts at x + i * x_bs
+  long long x_bs;
+  long long ldx;      // pitch of X in elements
+  int count;
+  int rows, cols;     // 2-D view of each parameter
+  int nesterov;
+  int vec_ok;         // all grad/mom pointers 16-byte aligned and cols % vector == 0
+  float w_mom;        // float(1 - beta)
+  float beta;         // float(beta)
+};
+
+struct EpilogueArgs {
+  void* param[kMaxTensors];
+  const __nv_bfloat16* u;  // NS output of tensor i at u + i * u_bs
+  long long u_bs;
+  long long ldu;
+  int count;
+  int rows, cols;
+  int vec_ok;
+  float scale;   // max(1, rows/cols)^0.5 as the reference evaluates it
+  float decay;   // float(1 - lr*wd)
+  float neg_lr;  // float(-lr)
+};
+
+struct AdamArgs {
+  void* param[kMaxTensors];
+  void* grad[kMaxTensors];
+  void* exp_avg[kMaxTensors];
+  void* exp_avg_sq[kMaxTensors];
+  long long numel[kMaxTensors];
+  float bc1[kMaxTensors];  // 1 - beta1^step
+  float bc2[kMaxTensors];  // 1 - beta2^step
+  int block_start[kMaxTensors + 1];
+  unsigned char vec_ok[kMaxTensors];
+  int count;
+  float w1, w2;  // float(1 - beta1), float(1 - beta2)
+  float eps;
+  float decay;
+  float neg_lr;
+};
+
+int adam_elems_per_block(int dtype);
+int launch_prologue(const PrologueArgs& a, int dtype, int transpose, cudaStream_t stream);
+int launch_epilogue(const EpilogueArgs& a, int dtype, int transpose, cudaStream_t stream);
+int launch_aol_rescale(__nv_bfloat16* X, long long ldx, long long x_bs, __nv_bfloat16* A,
+                       long long lda, long long a_bs, int m, int n, int batch, float eps,
+                       cudaStream_t stream);
+int launch_fro_normalize(__nv_bfloat16* X, long long ldx, long long x_bs, int m, int n, int batch,
+                         float eps, float* partials, int chunks, cudaStream_t stream);
+int launch_adam(const AdamArgs& a, int dtype, cudaStream_t stream);
+
+}  // namespace mb

@@ -1,0 +1,553 @@
+// Newton-Schulz GEMMs for sm_100a: one persistent, warp-specialised tcgen05 kernel
+// family covering the three products of an iteration.
+//
+//   line 1  A  = X · Xᵀ                       (reference ns_line_1_kernel, muon.py:349-417)
+//   line 2  B  = alpha · A · Aᵀ + beta · A     (reference ns_line_2_kernel, muon.py:464-544)
+//   line 3  X' = a · X + B · X                 (reference ns_line_3_kernel, muon.py:639-702)
+//
+// All operands are bf16, accumulation is fp32 in tensor memory, and every output
+// element is rounded to bf16 exactly once, after the fused epilogue arithmetic
+// (muon.py:404-405, :528-532, :696-697).
+//
+// Lines 1 and 2 only visit output tiles that touch the lower triangle. Inside such a
+// tile the elements with row >= col are authoritative: they are stored directly and
+// mirrored to (col, row). Elements above the diagonal are never stored from their
+// own position, so the result is exactly symmetric and deterministic. (The reference
+// stores every computed tile and its transpose, muon.py:408-417, which makes
+// diagonal-straddling tiles depend on store order.)
+//
+// Roles inside a CTA (192 threads):
+//   warp 0      TMA producer: fills a 4-stage ring of {A tile, B tile} in shared memory
+//   warp 1      MMA issuer: tcgen05.mma 128x256x16, accumulators double-buffered in TMEM
+//   warps 2..5  epilogue: tcgen05.ld -> fp32 epilogue -> bf16 stores (+ mirrored stores)
+// The grid is persistent: each CTA walks tiles blockIdx.x, +gridDim.x, ...
+#include "common.cuh"
+#include "ns_gemm.h"
+
+#include <cuda.h>
+#include <mutex>
+
+namespace mb {
+
+__device__ int g_device_status = 0;
+
+int read_device_status(int* status_out) {
+  MB_CUDA_CHECK(cudaDeviceSynchronize());
+  MB_CUDA_CHECK(cudaMemcpyFromSymbol(status_out, g_device_status, sizeof(int)));
+  return OK;
+}
+int clear_device_status() {
+  int zero = 0;
+  MB_CUDA_CHECK(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
+  return OK;
+}
+
+namespace {
+
+constexpr int BM = 128;  // UMMA M
+constexpr int BN = 256;  // UMMA N
+constexpr int BK = 64;   // one 128-byte swizzle span of bf16
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int TMEM_COLS = 512;  // two 128x256 fp32 accumulators
+constexpr int NUM_THREADS = 192;
+constexpr int SMEM_BARRIER_BYTES = 256;
+constexpr int SMEM_TOTAL = STAGES * STAGE_BYTES + SMEM_BARRIER_BYTES + 1024;  // + align slack
+
+struct TileCoord {
+  int batch, tm, tn;
+};
+
+// Linear tile index -> (batch, tile row, tile col). For the triangular schedule row
+// tile i owns the column tiles j with j*BN <= i*BM + BM - 1.
+__device__ __forceinline__ int tri_row_count(int i, int tiles_n) {
+  int c = (i * BM + BM - 1) / BN + 1;
+  return c < tiles_n ? c : tiles_n;
+}
+
+__device__ __forceinline__ TileCoord decode_tile(int t, const GemmParams& p) {
+  TileCoord tc;
+  tc.batch = t / p.tiles_per_batch;
+  int r = t - tc.batch * p.tiles_per_batch;
+  if (!p.triangular) {
+    tc.tm = r / p.tiles_n;
+    tc.tn = r - tc.tm * p.tiles_n;
+    return tc;
+  }
+  int i = 0;
+  for (; i < p.tiles_m; ++i) {
+    int c = tri_row_count(i, p.tiles_n);
+    if (r < c) break;
+    r -= c;
+  }
+  tc.tm = i;
+  tc.tn = r;
+  return tc;
+}
+
+// Instruction descriptor: bf16 x bf16 -> fp32, M=128, N=256, A K-major, B as templated.
+__host__ __device__ constexpr uint32_t make_idesc(bool b_mn_major) {
+  return (1u << 4)                      // D format: f32
+         | (1u << 7)                    // A format: bf16
+         | (1u << 10)                   // B format: bf16
+         | ((b_mn_major ? 1u : 0u) << 16)  // B major: 0 = K, 1 = MN
+         | (uint32_t(BN >> 3) << 17)    // N
+         | (uint32_t(BM >> 4) << 24);   // M
+}
+
+// ---------------------------------------------------------------------------
+// Epilogue helpers. Thread owns one output row `r` and 32 consecutive columns.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void load_row32(const __nv_bfloat16* src, int col0, int ncols,
+                                           float (&dst)[32]) {
+  // src points at (r, 0). Vector path when the whole span is in range (16-byte aligned
+  // because leading dimensions and col0 are multiples of 8).
+  if (col0 + 32 <= ncols) {
+    const uint4* v = reinterpret_cast<const uint4*>(src + col0);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 q = __ldg(v + i);
+      uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        dst[i * 8 + j * 2] = bf16_bits_to_float(w[j] & 0xffffu);
+        dst[i * 8 + j * 2 + 1] = bf16_bits_to_float(w[j] >> 16);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      int c = col0 + j;
+      dst[j] = (c < ncols) ? __bfloat162float(src[c]) : 0.f;
+    }
+  }
+}
+
+__device__ __forceinline__ void store_row32(__nv_bfloat16* dst, int col0, int col_end,
+                                            const uint32_t (&packed)[16]) {
+  // Stores columns [col0, min(col0+32, col_end)) of one row.
+  if (col0 + 32 <= col_end) {
+    uint4* v = reinterpret_cast<uint4*>(dst + col0);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      v[i] = make_uint4(packed[i * 4], packed[i * 4 + 1], packed[i * 4 + 2], packed[i * 4 + 3]);
+  } else {
+    unsigned short* s = reinterpret_cast<unsigned short*>(dst);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      int c = col0 + j;
+      if (c < col_end) {
+        uint32_t w = packed[j >> 1];
+        s[c] = static_cast<unsigned short>((j & 1) ? (w >> 16) : (w & 0xffffu));
+      }
+    }
+  }
+}
+
+template <int MODE, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ int s_abort;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  // barrier layout (8 bytes each): full[STAGES], empty[STAGES], tfull[2], tempty[2], tmem slot
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(smem_gen + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  const int k_blocks = (p.K + BK - 1) / BK;
+  const int total_tiles = p.tiles_per_batch * p.batch;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const TileCoord tc = decode_tile(t, p);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, &s_abort)) {
+            atomicCAS(&g_device_status, 0, 1);
+            s_abort = 1;
+            ok = false;
+            break;
+          }
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_STAGE_BYTES;
+          mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+          tma_load_3d(sa, &tmap_a, full_bar(stage), kb * BK, tc.tm * BM, tc.batch);
+          if (!B_MN) {
+            // B operand rows are output columns; K contiguous.
+            tma_load_3d(sb, &tmap_b, full_bar(stage), kb * BK, tc.tn * BN, tc.batch);
+          } else {
+            // B operand is [K, N] with N contiguous: four 64-column slabs of 64 k-rows.
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_3d(sb + c * (BK * 128), &tmap_b, full_bar(stage), tc.tn * BN + c * 64,
+                          kb * BK, tc.batch);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // Let copies that are still in flight land before shared memory goes away.
+        for (int i = 0; i < 100; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1u;
+        if (!mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, &s_abort)) {
+          atomicCAS(&g_device_status, 0, 3);
+          s_abort = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait_bounded(full_bar(stage), phase, &s_abort)) {
+            atomicCAS(&g_device_status, 0, 2);
+            s_abort = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_STAGE_BYTES;
+          // K-major tiles: rows of 128 bytes, 8-row groups 1024 bytes apart.
+          const uint64_t a_desc = make_smem_desc_sw128(sa, 16, 1024);
+          // MN-major B: 64-column slabs BK*128 bytes apart, 8-k groups 1024 bytes apart.
+          const uint64_t b_desc =
+              B_MN ? make_smem_desc_sw128(sb, BK * 128, 1024) : make_smem_desc_sw128(sb, 16, 1024);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t a_adv = static_cast<uint64_t>((kk * UMMA_K * 2) >> 4);
+            const uint64_t b_adv = B_MN ? static_cast<uint64_t>((kk * UMMA_K * 128) >> 4)
+                                        : static_cast<uint64_t>((kk * UMMA_K * 2) >> 4);
+            umma_bf16_ss(d_tmem, a_desc + a_adv, b_desc + b_adv, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit(tfull_bar(acc));  // accumulator complete
+      }
+    }
+  } else {
+    // -------------------------------- epilogue --------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    int local = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
+      const TileCoord tc = decode_tile(t, p);
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1u;
+      int ok = mbar_wait_bounded(tfull_bar(acc), acc_phase, &s_abort) ? 1 : 0;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) {
+          atomicCAS(&g_device_status, 0, 4);
+          s_abort = 1;
+        }
+        break;
+      }
+      tc_fence_after();
+
+      const int r = tc.tm * BM + q * 32 + lane;  // output row of this thread
+      const int r_warp_max = tc.tm * BM + q * 32 + 31;
+      const bool row_ok = r < p.M;
+      __nv_bfloat16* out_b = p.out + static_cast<long long>(tc.batch) * p.out_bs;
+      const __nv_bfloat16* add_b =
+          (MODE == MODE_SYRK) ? nullptr : p.add + static_cast<long long>(tc.batch) * p.add_bs;
+      __nv_bfloat16* out_row = out_b + static_cast<long long>(r) * p.ldo;
+      const __nv_bfloat16* add_row =
+          (MODE == MODE_SYRK) ? nullptr : add_b + static_cast<long long>(r) * p.ldadd;
+
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = tc.tn * BN + c * 32;
+        if (col0 >= p.N) break;                               // uniform: past the right edge
+        if (MODE != MODE_BX && col0 > r_warp_max) break;      // uniform: strictly above diagonal
+        uint32_t v[32];
+        __syncwarp();  // tcgen05.ld is warp-collective: reconverge after the predicated stores
+        tmem_ld_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, v);
+        tmem_ld_wait();
+        if (!row_ok) continue;
+
+        float f[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+
+        if (MODE == MODE_AXPBY) {
+          float a[32];
+          load_row32(add_row, col0, p.N, a);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = fmaf(a[j], p.beta, f[j] * p.alpha);
+        } else if (MODE == MODE_BX) {
+          float a[32];
+          load_row32(add_row, col0, p.N, a);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = fmaf(a[j], p.alpha, f[j]);
+        }
+
+        uint32_t packed[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) packed[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
+
+        if (MODE == MODE_BX) {
+          store_row32(out_row, col0, p.N, packed);
+        } else {
+          // Lower triangle (col <= r) is authoritative.
+          int col_end = r + 1 < p.N ? r + 1 : p.N;
+          store_row32(out_row, col0, col_end, packed);
+          // Mirror: element (r, col) with col < r also lands at (col, r). Lanes hold
+          // consecutive r, so each of these stores is a contiguous run across the warp.
+          unsigned short* out_s = reinterpret_cast<unsigned short*>(out_b);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = col0 + j;
+            if (col < r && col < p.N) {
+              const uint32_t w = packed[j >> 1];
+              out_s[static_cast<long long>(col) * p.ldo + r] =
+                  static_cast<unsigned short>((j & 1) ? (w >> 16) : (w & 0xffffu));
+            }
+          }
+        }
+      }
+      // Accumulator drained: hand it back to the MMA warp.
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+// bf16 tensor [batch, rows, cols] with row pitch `ld` and batch pitch `bs` (elements).
+// Box = box_rows x 64 columns, 128-byte swizzle, zero fill outside the tensor.
+int encode_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld,
+               int64_t bs, int batch, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return set_error(ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0)
+    return set_error(ERR_ALIGNMENT, "GEMM operand base %p is not 16-byte aligned", base);
+  if ((ld * 2) % 16 != 0 || (batch > 1 && (bs * 2) % 16 != 0))
+    return set_error(ERR_ALIGNMENT,
+                     "GEMM operand pitch must be a multiple of 8 bf16 elements (ld=%lld bs=%lld)",
+                     (long long)ld, (long long)bs);
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)(batch > 1 ? bs : rows * ld) * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return set_error(ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return OK;
+}
+
+struct DeviceInfo {
+  int sm_count = 0;
+  int cc_major = 0;
+  bool attr_set[6] = {false, false, false, false, false, false};
+};
+DeviceInfo g_dev[64];
+std::mutex g_dev_mu;
+
+template <int MODE, bool B_MN>
+int launch_instance(int dev, int slot, const CUtensorMap& ta, const CUtensorMap& tb,
+                    const GemmParams& p, int grid, cudaStream_t stream) {
+  auto kern = ns_gemm_kernel<MODE, B_MN>;
+  {
+    std::lock_guard<std::mutex> lk(g_dev_mu);
+    if (!g_dev[dev].attr_set[slot]) {
+      MB_CUDA_CHECK(
+          cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
+      g_dev[dev].attr_set[slot] = true;
+    }
+  }
+  kern<<<grid, NUM_THREADS, SMEM_TOTAL, stream>>>(ta, tb, p);
+  MB_CUDA_CHECK(cudaGetLastError());
+  return OK;
+}
+
+}  // namespace
+
+int device_sm_count(int* sm_count_out) {
+  int dev = 0;
+  MB_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return set_error(ERR_UNSUPPORTED, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lk(g_dev_mu);
+  if (g_dev[dev].sm_count == 0) {
+    int major = 0, sms = 0;
+    MB_CUDA_CHECK(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    MB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    g_dev[dev].cc_major = major;
+    g_dev[dev].sm_count = sms;
+  }
+  if (g_dev[dev].cc_major != 10)
+    return set_error(ERR_UNSUPPORTED, "muon_b200 kernels need an sm_100 device (found sm_%d0)",
+                     g_dev[dev].cc_major);
+  *sm_count_out = g_dev[dev].sm_count;
+  return OK;
+}
+
+// out[batch, M, N] = epilogue( opA[batch, M, K] · opB ), see GemmMode.
+//   MODE_SYRK / MODE_AXPBY: opB = opA (K contiguous), N = M, triangular schedule + mirror.
+//   MODE_BX: opA = Bmat [M, M], opB = X [M(K), N] with N contiguous, add = X.
+int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs,
+                   const __nv_bfloat16* opb, int64_t ldb, int64_t b_bs, __nv_bfloat16* out,
+                   int64_t ldo, int64_t out_bs, int batch, int64_t M, int64_t N, int64_t K,
+                   float alpha, float beta, cudaStream_t stream) {
+  if (!opa || !opb || !out) return set_error(ERR_INVALID_ARG, "null pointer passed to NS GEMM");
+  if (batch < 1 || M < 1 || N < 1 || K < 1)
+    return set_error(ERR_INVALID_ARG, "NS GEMM needs batch, M, N, K >= 1 (got %d, %lld, %lld, %lld)",
+                     batch, (long long)M, (long long)N, (long long)K);
+  if (M > (1 << 24) || N > (1 << 24) || K > (1 << 24))
+    return set_error(ERR_UNSUPPORTED, "NS GEMM dimension beyond 2^24");
+  if ((reinterpret_cast<uintptr_t>(out) & 15) != 0 || (ldo % 8) != 0 || (out_bs % 8) != 0)
+    return set_error(ERR_ALIGNMENT, "NS GEMM output must be 16-byte aligned with pitch %% 8 == 0");
+  int sms = 0;
+  int rc = device_sm_count(&sms);
+  if (rc != OK) return rc;
+  int dev = 0;
+  MB_CUDA_CHECK(cudaGetDevice(&dev));
+
+  GemmParams p{};
+  p.M = (int)M;
+  p.N = (int)N;
+  p.K = (int)K;
+  p.batch = batch;
+  p.tiles_m = (int)((M + BM - 1) / BM);
+  p.tiles_n = (int)((N + BN - 1) / BN);
+  p.alpha = alpha;
+  p.beta = beta;
+  p.out = out;
+  p.ldo = ldo;
+  p.out_bs = out_bs;
+
+  CUtensorMap ta, tb;
+  if (mode == MODE_SYRK || mode == MODE_AXPBY) {
+    if (M != N) return set_error(ERR_INVALID_ARG, "symmetric product needs a square output");
+    p.triangular = 1;
+    int cnt = 0;
+    for (int i = 0; i < p.tiles_m; ++i) {
+      int c = (i * BM + BM - 1) / BN + 1;
+      cnt += c < p.tiles_n ? c : p.tiles_n;
+    }
+    p.tiles_per_batch = cnt;
+    p.add = opa;  // line 2 adds beta * A, where A is the operand itself
+    p.ldadd = lda;
+    p.add_bs = a_bs;
+    if (mode == MODE_AXPBY && K != M)
+      return set_error(ERR_INVALID_ARG, "line 2 needs a square operand (got %lld x %lld)",
+                       (long long)M, (long long)K);
+    if ((rc = encode_map(&ta, opa, M, K, lda, a_bs, batch, BM)) != OK) return rc;
+    if ((rc = encode_map(&tb, opb, M, K, ldb, b_bs, batch, BN)) != OK) return rc;
+  } else if (mode == MODE_BX) {
+    if (K != M) return set_error(ERR_INVALID_ARG, "line 3 needs a square left operand");
+    p.triangular = 0;
+    p.tiles_per_batch = p.tiles_m * p.tiles_n;
+    p.add = opb;  // a * X
+    p.ldadd = ldb;
+    p.add_bs = b_bs;
+    if ((rc = encode_map(&ta, opa, M, K, lda, a_bs, batch, BM)) != OK) return rc;
+    if ((rc = encode_map(&tb, opb, K, N, ldb, b_bs, batch, BK)) != OK) return rc;
+  } else {
+    return set_error(ERR_INVALID_ARG, "unknown NS GEMM mode %d", mode);
+  }
+  if ((reinterpret_cast<uintptr_t>(p.add) & 15) != 0 || (p.ldadd % 8) != 0)
+    return set_error(ERR_ALIGNMENT, "NS GEMM addend must be 16-byte aligned with pitch %% 8 == 0");
+
+  long long total = (long long)p.tiles_per_batch * batch;
+  if (total > (1ll << 30)) return set_error(ERR_UNSUPPORTED, "too many output tiles");
+  int grid = (int)(total < sms ? total : sms);
+
+  switch (mode) {
+    case MODE_SYRK:
+      return launch_instance<MODE_SYRK, false>(dev, 0, ta, tb, p, grid, stream);
+    case MODE_AXPBY:
+      return launch_instance<MODE_AXPBY, false>(dev, 1, ta, tb, p, grid, stream);
+    default:
+      return launch_instance<MODE_BX, true>(dev, 2, ta, tb, p, grid, stream);
+  }
+}
+
+}  // namespace mb

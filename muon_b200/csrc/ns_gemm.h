@@ -1,0 +1,36 @@
+// Internal interface between the NS GEMM kernels and the C-ABI layer.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace mb {
+
+enum GemmMode : int {
+  MODE_SYRK = 0,   // out = opA · opAᵀ                       (lower tiles + mirror)
+  MODE_AXPBY = 1,  // out = alpha · opA · opAᵀ + beta · opA   (lower tiles + mirror)
+  MODE_BX = 2,     // out = opA · opB + alpha · opB           (full)
+};
+
+struct GemmParams {
+  int M, N, K;  // output rows, output cols, contraction length
+  int batch;
+  int tiles_m, tiles_n;
+  int tiles_per_batch;
+  int triangular;
+  float alpha, beta;
+  __nv_bfloat16* out;
+  long long ldo, out_bs;
+  const __nv_bfloat16* add;
+  long long ldadd, add_bs;
+};
+
+int device_sm_count(int* sm_count_out);
+
+int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs,
+                   const __nv_bfloat16* opb, int64_t ldb, int64_t b_bs, __nv_bfloat16* out,
+                   int64_t ldo, int64_t out_bs, int batch, int64_t M, int64_t N, int64_t K,
+                   float alpha, float beta, cudaStream_t stream);
+
+}  // namespace mb
