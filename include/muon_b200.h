@@ -58,6 +58,21 @@ const char* muon_b200_last_error(void);
  * is cleared afterwards. Returns MUON_B200_ERR_DEVICE_TIMEOUT when the word is set. */
 int muon_b200_device_status(int* status_out, int reset);
 
+/* ---- Accounting and per-kernel timing -----------------------------------------------
+ * Kernel kinds, in the order of every array below:
+ *   0 NS line 1, 1 NS line 2, 2 NS line 3 (work unit: algorithmic FLOPs, symmetric products
+ *   counted once), 3 prologue, 4 epilogue, 5 AOL rescale, 6 Frobenius normalise, 7 Adam
+ *   (work unit: algorithmic HBM bytes). No counterpart in the reference. */
+int muon_b200_kernel_kinds(void);
+/* Kernel launches issued by this process since load, per kind. */
+int muon_b200_launch_counts(int64_t* counts, int n_kinds);
+/* While enabled, every launch is bracketed by two CUDA events recorded on the launching
+ * stream. Meant for measurement runs: creating the events costs host time. */
+int muon_b200_timing_enable(int on);
+/* Waits for the recorded intervals; returns per kind the summed device time (ms), summed
+ * work units and number of launches since the last collect, and forgets them. */
+int muon_b200_timing_collect(double* ms, double* work, int64_t* launches, int n_kinds);
+
 /* ---- Newton-Schulz GEMM lines ---------------------------------------------------
  * All matrices are bf16, row-major with a pitch (ld*, in elements, multiple of 8) and a
  * batch pitch (*_bs, in elements, multiple of 8; ignored when batch == 1). Pointers
@@ -68,11 +83,14 @@ int muon_b200_device_status(int* status_out, int reset);
 int muon_b200_ns_line1(const void* x, int64_t ldx, int64_t x_bs, void* a_out, int64_t lda,
                        int64_t a_bs, int batch, int64_t m, int64_t k, muon_b200_stream_t stream);
 
-/* B[b] = alpha · A[b] · A[b]ᵀ + beta · A[b], A is m x m. The lower triangle is computed
- * and mirrored. Replaces ns_line_2 (muon.py:547-588, kernel :464-544). */
+/* B[b] = alpha · A[b] · A[b]ᵀ + beta · A[b], A is m x m. Only the lower triangle of the
+ * product is computed and it is mirrored; the addend beta·A is taken per element, so A
+ * may be non-symmetric. With a_is_symmetric != 0 the caller asserts A == Aᵀ bit for bit
+ * and the kernel mirrors finished values instead of re-reading A.
+ * Replaces ns_line_2 (muon.py:547-588, kernel :464-544). */
 int muon_b200_ns_line2(const void* a, int64_t lda, int64_t a_bs, void* b_out, int64_t ldb,
                        int64_t b_bs, int batch, int64_t m, float alpha, float beta,
-                       muon_b200_stream_t stream);
+                       int a_is_symmetric, muon_b200_stream_t stream);
 
 /* OUT[b] = a · X[b] + B[b] · X[b], B is m x m, X and OUT are m x n. OUT must not alias X.
  * Replaces ns_line_3 (muon.py:705-746, kernel :639-702). */

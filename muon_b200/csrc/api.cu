@@ -6,6 +6,7 @@
 #include "common.cuh"
 #include "elementwise.h"
 #include "ns_gemm.h"
+#include "profiling.h"
 
 #include <cmath>
 #include <cstdarg>
@@ -81,18 +82,37 @@ int muon_b200_device_status(int* status_out, int reset) {
   return OK;
 }
 
+int muon_b200_kernel_kinds(void) { return K_KIND_COUNT; }
+
+int muon_b200_launch_counts(int64_t* counts, int n_kinds) {
+  if (!counts || n_kinds < 0) return set_error(ERR_INVALID_ARG, "launch_counts: bad arguments");
+  launch_counts(counts, n_kinds);
+  return OK;
+}
+
+int muon_b200_timing_enable(int on) {
+  timing_enable(on != 0);
+  return OK;
+}
+
+int muon_b200_timing_collect(double* ms, double* work, int64_t* launches, int n_kinds) {
+  if (!ms || !work || !launches || n_kinds < 0)
+    return set_error(ERR_INVALID_ARG, "timing_collect: bad arguments");
+  return timing_collect(ms, work, launches, n_kinds);
+}
+
 int muon_b200_ns_line1(const void* x, int64_t ldx, int64_t x_bs, void* a_out, int64_t lda,
                        int64_t a_bs, int batch, int64_t m, int64_t k, muon_b200_stream_t stream) {
   return launch_ns_gemm(MODE_SYRK, bf(x), ldx, x_bs, bf(x), ldx, x_bs, bf(a_out), lda, a_bs, batch,
-                        m, m, k, 1.f, 0.f, as_stream(stream));
+                        m, m, k, 1.f, 0.f, 1, as_stream(stream));
 }
 
 int muon_b200_ns_line2(const void* a, int64_t lda, int64_t a_bs, void* b_out, int64_t ldb,
                        int64_t b_bs, int batch, int64_t m, float alpha, float beta,
-                       muon_b200_stream_t stream) {
+                       int a_is_symmetric, muon_b200_stream_t stream) {
   if (a == b_out) return set_error(ERR_INVALID_ARG, "ns_line2 output must not alias its input");
   return launch_ns_gemm(MODE_AXPBY, bf(a), lda, a_bs, bf(a), lda, a_bs, bf(b_out), ldb, b_bs, batch,
-                        m, m, m, alpha, beta, as_stream(stream));
+                        m, m, m, alpha, beta, a_is_symmetric ? 1 : 0, as_stream(stream));
 }
 
 int muon_b200_ns_line3(const void* b, int64_t ldb, int64_t b_bs, const void* x, int64_t ldx,
@@ -100,7 +120,7 @@ int muon_b200_ns_line3(const void* b, int64_t ldb, int64_t b_bs, const void* x, 
                        int64_t n, float a, muon_b200_stream_t stream) {
   if (x == out) return set_error(ERR_INVALID_ARG, "ns_line3 output must not alias X");
   return launch_ns_gemm(MODE_BX, bf(b), ldb, b_bs, bf(x), ldx, x_bs, bf(out), ldo, o_bs, batch, m,
-                        n, m, a, 0.f, as_stream(stream));
+                        n, m, a, 0.f, 0, as_stream(stream));
 }
 
 int muon_b200_ns_workspace_layout(int batch, int64_t m, int64_t n, muon_b200_ns_layout* out) {
@@ -153,7 +173,7 @@ int muon_b200_ns_run(void* workspace, int batch, int64_t m, int64_t n, int mode,
   if (mode == MUON_B200_NS_AOL4) {
     // Gram matrix once, shared by the rescale and the first iteration (muon.py:778-785).
     rc = launch_ns_gemm(MODE_SYRK, X, l.ldn, l.x_bs, X, l.ldn, l.x_bs, A, l.ldm, l.a_bs, batch, m,
-                        m, n, 1.f, 0.f, st);
+                        m, n, 1.f, 0.f, 1, st);
     if (rc != OK) return rc;
     rc = launch_aol_rescale(X, l.ldn, l.x_bs, A, l.ldm, l.a_bs, (int)m, (int)n, batch, eps, st);
     if (rc != OK) return rc;
@@ -174,15 +194,18 @@ int muon_b200_ns_run(void* workspace, int batch, int64_t m, int64_t n, int mode,
     }
     if (!have_gram) {
       rc = launch_ns_gemm(MODE_SYRK, X, l.ldn, l.x_bs, X, l.ldn, l.x_bs, A, l.ldm, l.a_bs, batch,
-                          m, m, n, 1.f, 0.f, st);
+                          m, m, n, 1.f, 0.f, 1, st);
       if (rc != OK) return rc;
     }
+    // A is exactly symmetric when it comes straight from line 1; after the AOL row
+    // scaling (first iteration) it is not.
+    const int a_symmetric = have_gram ? 0 : 1;
     have_gram = false;
     rc = launch_ns_gemm(MODE_AXPBY, A, l.ldm, l.a_bs, A, l.ldm, l.a_bs, B, l.ldm, l.a_bs, batch, m,
-                        m, m, c, b, st);
+                        m, m, c, b, a_symmetric, st);
     if (rc != OK) return rc;
     rc = launch_ns_gemm(MODE_BX, B, l.ldm, l.a_bs, X, l.ldn, l.x_bs, C, l.ldn, l.x_bs, batch, m, n,
-                        m, a, 0.f, st);
+                        m, a, 0.f, 0, st);
     if (rc != OK) return rc;
     __nv_bfloat16* t = X; X = C; C = t;
     slot ^= 1;

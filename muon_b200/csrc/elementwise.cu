@@ -6,6 +6,7 @@
 #include "common.cuh"
 #include "elementwise.h"
 #include "ns_gemm.h"
+#include "profiling.h"
 
 namespace mb {
 
@@ -538,6 +539,9 @@ int launch_prologue(const PrologueArgs& a, int dtype, int transpose, cudaStream_
                     ((a.rows + kTileRows - 1) / kTileRows) * a.count;
   int grid = grid_for(tiles, 8);
   if (grid < 0) return ERR_UNSUPPORTED;
+  const double b = dtype == DT_F32 ? 4 : 2;  // read g, m; write m (+ g with Nesterov); write bf16 X
+  LaunchScope scope(K_PROLOGUE, (double)a.rows * a.cols * a.count * (3 * b + 2 + (a.nesterov ? b : 0)),
+                    stream);
   if (dtype == DT_F32) {
     if (transpose) prologue_kernel<float, true><<<grid, kThreads, 0, stream>>>(a);
     else prologue_kernel<float, false><<<grid, kThreads, 0, stream>>>(a);
@@ -555,6 +559,8 @@ int launch_epilogue(const EpilogueArgs& a, int dtype, int transpose, cudaStream_
                     ((a.rows + kTileRows - 1) / kTileRows) * a.count;
   int grid = grid_for(tiles, 8);
   if (grid < 0) return ERR_UNSUPPORTED;
+  const double b = dtype == DT_F32 ? 4 : 2;  // read bf16 U; read and write p
+  LaunchScope scope(K_EPILOGUE, (double)a.rows * a.cols * a.count * (2 * b + 2), stream);
   if (dtype == DT_F32) {
     if (transpose) epilogue_kernel<float, true><<<grid, kThreads, 0, stream>>>(a);
     else epilogue_kernel<float, false><<<grid, kThreads, 0, stream>>>(a);
@@ -571,6 +577,8 @@ int launch_aol_rescale(__nv_bfloat16* X, long long ldx, long long x_bs, __nv_bfl
                        cudaStream_t stream) {
   int grid = grid_for((long long)m * batch, 16);
   if (grid < 0) return ERR_UNSUPPORTED;
+  // read + write A (m x m) and X (m x n), bf16
+  LaunchScope scope(K_AOL_RESCALE, 4.0 * m * ((double)m + n) * batch, stream);
   aol_rescale_kernel<<<grid, kThreads, 0, stream>>>(X, ldx, x_bs, A, lda, a_bs, m, n, batch, eps);
   MB_CUDA_CHECK(cudaGetLastError());
   return OK;
@@ -579,6 +587,8 @@ int launch_aol_rescale(__nv_bfloat16* X, long long ldx, long long x_bs, __nv_bfl
 int launch_fro_normalize(__nv_bfloat16* X, long long ldx, long long x_bs, int m, int n, int batch,
                          float eps, float* partials, int chunks, cudaStream_t stream) {
   dim3 grid(chunks, batch);
+  // pass 1 reads X, pass 2 reads and writes it (bf16); accounted as one unit of two launches
+  LaunchScope scope(K_FRO_NORMALIZE, 6.0 * m * (double)n * batch, stream);
   sumsq_partial_kernel<<<grid, kThreads, 0, stream>>>(X, ldx, x_bs, m, n, chunks, partials);
   MB_CUDA_CHECK(cudaGetLastError());
   fro_scale_kernel<<<grid, kThreads, 0, stream>>>(X, ldx, x_bs, m, n, chunks, partials, eps);
@@ -589,6 +599,9 @@ int launch_fro_normalize(__nv_bfloat16* X, long long ldx, long long x_bs, int m,
 int launch_adam(const AdamArgs& a, int dtype, cudaStream_t stream) {
   int blocks = a.block_start[a.count];
   if (blocks <= 0) return OK;
+  double elems = 0;
+  for (int i = 0; i < a.count; ++i) elems += (double)a.numel[i];
+  LaunchScope scope(K_ADAM, elems * 7 * (dtype == DT_F32 ? 4 : 2), stream);  // read p,g,m,v; write p,m,v
   if (dtype == DT_F32) adam_kernel<float><<<blocks, kThreads, 0, stream>>>(a);
   else adam_kernel<__nv_bfloat16><<<blocks, kThreads, 0, stream>>>(a);
   MB_CUDA_CHECK(cudaGetLastError());

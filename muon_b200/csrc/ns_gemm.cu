@@ -10,11 +10,15 @@
 // (muon.py:404-405, :528-532, :696-697).
 //
 // Lines 1 and 2 only visit output tiles that touch the lower triangle. Inside such a
-// tile the elements with row >= col are authoritative: they are stored directly and
-// mirrored to (col, row). Elements above the diagonal are never stored from their
-// own position, so the result is exactly symmetric and deterministic. (The reference
-// stores every computed tile and its transpose, muon.py:408-417, which makes
-// diagonal-straddling tiles depend on store order.)
+// tile the products with row >= col are computed once, stored at (row, col) and
+// mirrored to (col, row); nothing above the diagonal is stored from its own position,
+// so the result is deterministic. The product part is therefore exactly symmetric.
+// Line 2's addend beta*A is taken per position (A[row, col] below the diagonal,
+// A[col, row] for the mirrored element), so the kernel computes alpha*A*A^T + beta*A as
+// the reference documents it (muon.py:483-486) even when A is not symmetric, which
+// happens in the first iteration (A/s scales rows only, muon.py:785). The reference
+// instead stores every computed tile and then its transpose (muon.py:534-544): its
+// output for a non-symmetric A depends on tile shape and store order.
 //
 // Roles inside a CTA (192 threads):
 //   warp 0      TMA producer: fills a 4-stage ring of {A tile, B tile} in shared memory
@@ -23,6 +27,7 @@
 // The grid is persistent: each CTA walks tiles blockIdx.x, +gridDim.x, ...
 #include "common.cuh"
 #include "ns_gemm.h"
+#include "profiling.h"
 
 #include <cuda.h>
 #include <mutex>
@@ -328,11 +333,29 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
         for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
 
+        // mirror[j]: value for position (col, r) when it differs from the direct one.
+        float mirror[MODE == MODE_AXPBY ? 32 : 1];
         if (MODE == MODE_AXPBY) {
           float a[32];
           load_row32(add_row, col0, p.N, a);
+          if (p.sym_add) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) f[j] = fmaf(a[j], p.beta, f[j] * p.alpha);
+            for (int j = 0; j < 32; ++j) f[j] = fmaf(a[j], p.beta, f[j] * p.alpha);
+          } else {
+            // The product alpha*A*A^T is symmetric, the addend beta*A need not be: the
+            // mirrored position takes its own addend A[col, r].
+            const unsigned short* add_s = reinterpret_cast<const unsigned short*>(add_b);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = col0 + j;
+              const float prod = f[j] * p.alpha;
+              f[j] = fmaf(a[j], p.beta, prod);
+              float at = 0.f;
+              if (col < r && col < p.N)
+                at = bf16_bits_to_float(__ldg(add_s + static_cast<long long>(col) * p.ldadd + r));
+              mirror[j] = fmaf(at, p.beta, prod);
+            }
+          }
         } else if (MODE == MODE_BX) {
           float a[32];
           load_row32(add_row, col0, p.N, a);
@@ -347,19 +370,25 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (MODE == MODE_BX) {
           store_row32(out_row, col0, p.N, packed);
         } else {
-          // Lower triangle (col <= r) is authoritative.
+          // Lower triangle (col <= r) is stored from here.
           int col_end = r + 1 < p.N ? r + 1 : p.N;
           store_row32(out_row, col0, col_end, packed);
           // Mirror: element (r, col) with col < r also lands at (col, r). Lanes hold
           // consecutive r, so each of these stores is a contiguous run across the warp.
           unsigned short* out_s = reinterpret_cast<unsigned short*>(out_b);
+          const bool own_mirror = (MODE == MODE_AXPBY) && !p.sym_add;
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const int col = col0 + j;
             if (col < r && col < p.N) {
-              const uint32_t w = packed[j >> 1];
-              out_s[static_cast<long long>(col) * p.ldo + r] =
-                  static_cast<unsigned short>((j & 1) ? (w >> 16) : (w & 0xffffu));
+              unsigned short bits;
+              if (own_mirror) {
+                bits = __bfloat16_as_ushort(__float2bfloat16_rn(mirror[MODE == MODE_AXPBY ? j : 0]));
+              } else {
+                const uint32_t w = packed[j >> 1];
+                bits = static_cast<unsigned short>((j & 1) ? (w >> 16) : (w & 0xffffu));
+              }
+              out_s[static_cast<long long>(col) * p.ldo + r] = bits;
             }
           }
         }
@@ -443,7 +472,13 @@ int launch_instance(int dev, int slot, const CUtensorMap& ta, const CUtensorMap&
       g_dev[dev].attr_set[slot] = true;
     }
   }
-  kern<<<grid, NUM_THREADS, SMEM_TOTAL, stream>>>(ta, tb, p);
+  {
+    const double m = p.M, n = p.N, k = p.K, b = p.batch;
+    const double flops = MODE == MODE_BX ? 2.0 * m * k * n * b : m * (m + 1.0) * k * b;
+    LaunchScope scope(MODE == MODE_SYRK ? K_NS_LINE1 : MODE == MODE_AXPBY ? K_NS_LINE2 : K_NS_LINE3,
+                      flops, stream);
+    kern<<<grid, NUM_THREADS, SMEM_TOTAL, stream>>>(ta, tb, p);
+  }
   MB_CUDA_CHECK(cudaGetLastError());
   return OK;
 }
@@ -475,7 +510,7 @@ int device_sm_count(int* sm_count_out) {
 int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs,
                    const __nv_bfloat16* opb, int64_t ldb, int64_t b_bs, __nv_bfloat16* out,
                    int64_t ldo, int64_t out_bs, int batch, int64_t M, int64_t N, int64_t K,
-                   float alpha, float beta, cudaStream_t stream) {
+                   float alpha, float beta, int sym_add, cudaStream_t stream) {
   if (!opa || !opb || !out) return set_error(ERR_INVALID_ARG, "null pointer passed to NS GEMM");
   if (batch < 1 || M < 1 || N < 1 || K < 1)
     return set_error(ERR_INVALID_ARG, "NS GEMM needs batch, M, N, K >= 1 (got %d, %lld, %lld, %lld)",
@@ -513,6 +548,7 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
       cnt += c < p.tiles_n ? c : p.tiles_n;
     }
     p.tiles_per_batch = cnt;
+    p.sym_add = sym_add;
     p.add = opa;  // line 2 adds beta * A, where A is the operand itself
     p.ldadd = lda;
     p.add_bs = a_bs;

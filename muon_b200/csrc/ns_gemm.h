@@ -19,6 +19,7 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int tiles_per_batch;
   int triangular;
+  int sym_add;  // line 2: the addend is known symmetric, mirror the finished value
   float alpha, beta;
   __nv_bfloat16* out;
   long long ldo, out_bs;
@@ -31,6 +32,6 @@ int device_sm_count(int* sm_count_out);
 int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs,
                    const __nv_bfloat16* opb, int64_t ldb, int64_t b_bs, __nv_bfloat16* out,
                    int64_t ldo, int64_t out_bs, int batch, int64_t M, int64_t N, int64_t K,
-                   float alpha, float beta, cudaStream_t stream);
+                   float alpha, float beta, int sym_add, cudaStream_t stream);
 
 }  // namespace mb

@@ -1,0 +1,79 @@
+#include "profiling.h"
+
+#include "common.cuh"
+
+#include <atomic>
+#include <mutex>
+#include <vector>
+
+namespace mb {
+
+namespace {
+std::atomic<int64_t> g_counts[K_KIND_COUNT];
+std::atomic<bool> g_timing{false};
+struct Interval {
+  int kind;
+  double work;
+  cudaEvent_t start, stop;
+};
+std::vector<Interval> g_intervals;
+std::mutex g_mu;
+}  // namespace
+
+LaunchScope::LaunchScope(int kind, double work, cudaStream_t stream)
+    : kind_(kind), work_(work), stream_(stream) {
+  g_counts[kind].fetch_add(1, std::memory_order_relaxed);
+  if (g_timing.load(std::memory_order_relaxed)) {
+    if (cudaEventCreate(&start_) == cudaSuccess) cudaEventRecord(start_, stream_);
+    else start_ = nullptr;
+  }
+}
+
+LaunchScope::~LaunchScope() {
+  if (!start_) return;
+  cudaEvent_t stop = nullptr;
+  if (cudaEventCreate(&stop) != cudaSuccess) {
+    cudaEventDestroy(start_);
+    return;
+  }
+  cudaEventRecord(stop, stream_);
+  std::lock_guard<std::mutex> lk(g_mu);
+  g_intervals.push_back({kind_, work_, start_, stop});
+}
+
+void timing_enable(bool on) { g_timing.store(on); }
+
+int timing_collect(double* ms, double* work, int64_t* launches, int n_kinds) {
+  std::vector<Interval> taken;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    taken.swap(g_intervals);
+  }
+  for (int k = 0; k < n_kinds; ++k) {
+    ms[k] = 0.0;
+    work[k] = 0.0;
+    launches[k] = 0;
+  }
+  int rc = OK;
+  for (const Interval& iv : taken) {
+    float t = 0.f;
+    cudaError_t e = cudaEventSynchronize(iv.stop);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&t, iv.start, iv.stop);
+    if (e != cudaSuccess && rc == OK)
+      rc = set_error(ERR_CUDA, "timing_collect: %s", cudaGetErrorString(e));
+    if (e == cudaSuccess && iv.kind < n_kinds) {
+      ms[iv.kind] += t;
+      work[iv.kind] += iv.work;
+      launches[iv.kind] += 1;
+    }
+    cudaEventDestroy(iv.start);
+    cudaEventDestroy(iv.stop);
+  }
+  return rc;
+}
+
+void launch_counts(int64_t* counts, int n_kinds) {
+  for (int k = 0; k < n_kinds && k < K_KIND_COUNT; ++k) counts[k] = g_counts[k].load();
+}
+
+}  // namespace mb

@@ -1,0 +1,40 @@
+// Launch accounting and optional per-kernel CUDA-event timing for the library's kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mb {
+
+enum KernelKind : int {
+  K_NS_LINE1 = 0,   // work unit: algorithmic FLOPs, m(m+1)k per matrix
+  K_NS_LINE2 = 1,   // m*m*(m+1)
+  K_NS_LINE3 = 2,   // 2*m*m*n
+  K_PROLOGUE = 3,   // work unit: algorithmic HBM bytes
+  K_EPILOGUE = 4,
+  K_AOL_RESCALE = 5,
+  K_FRO_NORMALIZE = 6,
+  K_ADAM = 7,
+  K_KIND_COUNT = 8,
+};
+
+// Counts the launch; when timing is enabled also brackets it with two events recorded on
+// `stream` (the launching stream), so the interval covers exactly this kernel.
+class LaunchScope {
+ public:
+  LaunchScope(int kind, double work, cudaStream_t stream);
+  ~LaunchScope();
+
+ private:
+  int kind_;
+  double work_;
+  cudaStream_t stream_;
+  cudaEvent_t start_ = nullptr;
+};
+
+void timing_enable(bool on);
+// Waits for all recorded intervals, adds them up per kind and forgets them.
+int timing_collect(double* ms, double* work, int64_t* launches, int n_kinds);
+void launch_counts(int64_t* counts, int n_kinds);
+
+}  // namespace mb

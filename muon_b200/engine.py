@@ -1,0 +1,240 @@
+"""Host-side engine: turns lists of torch tensors into grouped calls of the C ABI.
+
+``CudaBackend`` is the product path. It hands raw device pointers of the callers'
+tensors to ``libmuon_b200.so`` on the current CUDA stream; PyTorch is used only to own
+memory (the Newton-Schulz workspace is a cached ``torch.uint8`` buffer) and for streams.
+
+Tensors that are not on an sm_100 CUDA device are rejected: there is no CPU path.
+The optimizer classes talk to whatever ``get_backend()`` returns, so that their
+ownership / windowing logic can be unit-tested on CPU ranks with a stand-in backend
+installed by the tests; the package itself never installs anything but ``CudaBackend``.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Sequence
+
+import torch
+from torch import Tensor
+
+from . import _lib
+from ._lib import BF16, F32, NS_AOL4, NS_CLASSIC5, check, i64_array, lib, ptr_array
+
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+_NS_MODES = {"aol4": NS_AOL4, "classic5": NS_CLASSIC5}
+
+# Module-level Newton-Schulz setting. It cannot be a param-group key: the reference's
+# group key sets are asserted exactly (muon.py:148, :155).
+_ns_mode = "aol4"
+_ns_steps = 0  # 0 = the mode's default (4 for aol4, 5 for classic5)
+
+
+def set_ns_mode(mode: str = "aol4", steps: int = 0) -> None:
+    """Select the Newton-Schulz variant used by every optimizer and by ``muon_update``.
+
+    ``"aol4"`` (default) is the algorithm the reference executes (muon.py:748-799);
+    ``"classic5"`` is the Frobenius-normalised quintic iteration of its commented block
+    (muon.py:265-291).
+    """
+    global _ns_mode, _ns_steps
+    if mode not in _NS_MODES:
+        raise ValueError(f"unknown NS mode {mode!r}; expected one of {sorted(_NS_MODES)}")
+    if steps < 0:
+        raise ValueError("steps must be >= 0")
+    _ns_mode, _ns_steps = mode, int(steps)
+
+
+def get_ns_mode() -> tuple[str, int]:
+    return _ns_mode, _ns_steps
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _require_cuda(t: Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(
+            f"muon_b200: {what} must live on a CUDA (sm_100) device, got device={t.device}; "
+            "there is no CPU implementation")
+
+
+def dtype_code(t: Tensor) -> int:
+    try:
+        return _DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise ValueError(f"muon_b200 supports float32 and bfloat16 tensors, got {t.dtype}") from None
+
+
+def view_2d(shape: Sequence[int]) -> tuple[int, int]:
+    """Rows/cols of the matrix the iteration sees: 4-D filters collapse their last three
+    dimensions (muon.py:11-12); 2-D tensors are taken as they are."""
+    if len(shape) == 2:
+        return int(shape[0]), int(shape[1])
+    if len(shape) == 4:
+        return int(shape[0]), int(shape[1] * shape[2] * shape[3])
+    raise ValueError(f"Muon parameters must be 2-D or 4-D, got shape {tuple(shape)}")
+
+
+def aspect_scale(shape: Sequence[int]) -> float:
+    """max(1, size(-2)/size(-1))**0.5 on the gradient's ORIGINAL shape (muon.py:14); for a
+    4-D filter that is kH/kW, not rows/cols of the collapsed matrix."""
+    return max(1, shape[-2] / shape[-1]) ** 0.5
+
+
+def tri_tiles(m: int) -> int:
+    """Output tiles of the triangular schedule for an m x m product (128 x 256 tiles)."""
+    tiles_n = (m + 255) // 256
+    return sum(min(tiles_n, (i * 128 + 127) // 256 + 1) for i in range((m + 127) // 128))
+
+
+def batch_size_for(m: int, n: int, count: int, workspace_cap_bytes: int) -> int:
+    """How many same-shape matrices share one grouped launch: enough for about four waves
+    of tiles on the smallest product (line 2), within the workspace cap."""
+    want = max(1, math.ceil(592 / max(1, tri_tiles(m))))
+    per_matrix = 2 * (2 * m * ((n + 7) // 8 * 8) + 2 * m * ((m + 7) // 8 * 8)) + 2048
+    fit = max(1, workspace_cap_bytes // per_matrix)
+    return max(1, min(count, want, fit))
+
+
+class CudaBackend:
+    """Calls the sm_100a library. One instance per process; workspaces cached per device."""
+
+    name = "cuda"
+
+    def __init__(self, workspace_cap_bytes: int = 4 << 30):
+        self.workspace_cap_bytes = workspace_cap_bytes
+        self._workspaces: dict[tuple[int, int], Tensor] = {}
+        self.launch_groups = 0  # grouped C-ABI calls issued (for accounting)
+
+    # -- memory ------------------------------------------------------------------------
+    def workspace(self, device: torch.device, nbytes: int) -> Tensor:
+        """uint8 buffer >= nbytes, private to (device, current stream)."""
+        key = (device.index if device.index is not None else torch.cuda.current_device(),
+               _stream_ptr(device))
+        buf = self._workspaces.get(key)
+        if buf is None or buf.numel() < nbytes:
+            buf = torch.empty(nbytes + 256, dtype=torch.uint8, device=device)
+            self._workspaces[key] = buf
+        return buf
+
+    @staticmethod
+    def _aligned_ptr(buf: Tensor) -> int:
+        return (buf.data_ptr() + 255) & ~255
+
+    def release_workspaces(self) -> None:
+        self._workspaces.clear()
+
+    # -- Muon --------------------------------------------------------------------------
+    def muon_step(self, params: Sequence[Tensor], grads: Sequence[Tensor], moms: Sequence[Tensor],
+                  lr: float, weight_decay: float, beta: float, nesterov: bool = True) -> None:
+        """prologue -> Newton-Schulz -> epilogue for same-shape, same-dtype parameters."""
+        p0 = params[0]
+        rows, cols = view_2d(p0.shape)
+        code = dtype_code(p0)
+        for p, g, m in zip(params, grads, moms):
+            _require_cuda(p, "parameter")
+            if p.shape != p0.shape or p.dtype != p0.dtype or g.dtype != p0.dtype or m.dtype != p0.dtype:
+                raise ValueError("muon_step needs tensors of one shape and one dtype")
+            if not (p.is_contiguous() and g.is_contiguous() and m.is_contiguous()):
+                raise ValueError("muon_step needs contiguous parameter, gradient and momentum")
+        m_, n_ = min(rows, cols), max(rows, cols)
+        scale = aspect_scale(p0.shape)
+        mode, steps = _ns_mode, _ns_steps
+        eps = 1e-7
+        bsz = batch_size_for(m_, n_, len(params), self.workspace_cap_bytes)
+        dev = p0.device
+        with torch.cuda.device(dev):
+            stream = _stream_ptr(dev)
+            for s in range(0, len(params), bsz):
+                e = min(s + bsz, len(params))
+                layout = _lib.ns_layout(e - s, m_, n_)
+                ws = self.workspace(dev, layout.total_bytes)
+                check(lib.muon_b200_muon_step(
+                    ptr_array([p.data_ptr() for p in params[s:e]]),
+                    ptr_array([g.data_ptr() for g in grads[s:e]]),
+                    ptr_array([m.data_ptr() for m in moms[s:e]]),
+                    e - s, rows, cols, code, lr, weight_decay, beta, 1 if nesterov else 0, scale,
+                    _NS_MODES[mode], steps, None, eps, self._aligned_ptr(ws), layout.total_bytes,
+                    stream))
+                self.launch_groups += 1
+
+    # -- Adam --------------------------------------------------------------------------
+    def adam_step(self, params: Sequence[Tensor], grads: Sequence[Tensor], exp_avgs: Sequence[Tensor],
+                  exp_avg_sqs: Sequence[Tensor], steps: Sequence[int], lr: float, weight_decay: float,
+                  betas: tuple[float, float], eps: float) -> None:
+        """Fused Adam on tensors of any sizes; one dtype per call."""
+        if not params:
+            return
+        code = dtype_code(params[0])
+        for p, g, m, v in zip(params, grads, exp_avgs, exp_avg_sqs):
+            _require_cuda(p, "parameter")
+            if not (p.dtype == g.dtype == m.dtype == v.dtype == params[0].dtype):
+                raise ValueError("adam_step needs one dtype across parameter, gradient and state")
+            if not (p.is_contiguous() and g.is_contiguous() and m.is_contiguous() and v.is_contiguous()):
+                raise ValueError("adam_step needs contiguous tensors")
+        dev = params[0].device
+        with torch.cuda.device(dev):
+            check(lib.muon_b200_adam(
+                ptr_array([p.data_ptr() for p in params]), ptr_array([g.data_ptr() for g in grads]),
+                ptr_array([m.data_ptr() for m in exp_avgs]), ptr_array([v.data_ptr() for v in exp_avg_sqs]),
+                i64_array([p.numel() for p in params]), i64_array(list(steps)), len(params), code,
+                lr, weight_decay, betas[0], betas[1], eps, _stream_ptr(dev)))
+            self.launch_groups += 1
+
+    # -- functional pieces -------------------------------------------------------------
+    def newton_schulz(self, G: Tensor, epsilon: float = 1e-7, mode: str | None = None,
+                      steps: int | None = None) -> Tensor:
+        """Orthogonalise G ([r, c] or [b, r, c], any float dtype). Returns bf16 of G's
+        logical shape: a transposed view of a contiguous buffer when r > c, like the
+        reference (muon.py:797-798)."""
+        _require_cuda(G, "G")
+        if G.ndim not in (2, 3):
+            raise ValueError(f"Input tensor must be 2D or 3D, but got {G.ndim}D tensor.")
+        mode = _ns_mode if mode is None else mode
+        steps = _ns_steps if steps is None else steps
+        batch = G.shape[0] if G.ndim == 3 else 1
+        r, c = int(G.shape[-2]), int(G.shape[-1])
+        tall = r > c
+        m_, n_ = (c, r) if tall else (r, c)
+        layout = _lib.ns_layout(batch, m_, n_)
+        dev = G.device
+        with torch.cuda.device(dev):
+            # Private buffer: the result is returned as a view into it.
+            ws = torch.empty(layout.total_bytes + 256, dtype=torch.uint8, device=dev)
+            base = self._aligned_ptr(ws) - ws.data_ptr()
+
+            def slot(offset: int) -> Tensor:
+                flat = ws[base + offset: base + offset + batch * layout.x_bs * 2].view(torch.bfloat16)
+                return flat.view(batch, m_, layout.ldn)[:, :, :n_]
+
+            src = G.reshape(batch, r, c)
+            slot(layout.x_offset_bytes).copy_(src.mT if tall else src)  # cast (+ transposition)
+            res = ctypes.c_int(0)
+            check(lib.muon_b200_ns_run(self._aligned_ptr(ws), batch, m_, n_, _NS_MODES[mode], steps,
+                                       None, epsilon, ctypes.byref(res), _stream_ptr(dev)))
+            self.launch_groups += 1
+            out = slot(layout.x_offset_bytes if res.value == 0 else layout.c_offset_bytes)
+        if tall:
+            out = out.mT
+        return out if G.ndim == 3 else out[0]
+
+
+_backend = None
+
+
+def get_backend():
+    """The active backend; created on first use."""
+    global _backend
+    if _backend is None:
+        _backend = CudaBackend()
+    return _backend
+
+
+def _set_backend_for_testing(backend):
+    """Test seam: swap the backend object (pass None to restore the CUDA one). Returns the
+    previous backend. Product code never calls this."""
+    global _backend
+    prev, _backend = _backend, backend
+    return prev

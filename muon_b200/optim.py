@@ -1,0 +1,222 @@
+"""The four optimizer classes of the reference (muon.py:18-260), same constructors, same
+param-group keys, same state keys, same ownership rule — with the per-parameter torch ops
+replaced by grouped calls into the sm_100a library.
+
+What differs on purpose, and only in scheduling:
+
+* same-shape parameters are orthogonalised together in one grouped launch sequence
+  instead of one at a time;
+* in the distributed classes each window's ``all_gather`` is issued asynchronously and
+  overlaps the next windows' Newton-Schulz work; all of them are waited for before
+  ``step`` returns, so callers observe the reference's post-condition (every rank holds
+  every updated parameter).
+"""
+from __future__ import annotations
+
+from collections import OrderedDict
+
+import torch
+import torch.distributed as dist
+
+from .engine import batch_size_for, get_backend, view_2d
+
+
+def _ensure_grad_and_state(optimizer, p) -> None:
+    """muon.py:59-64: a missing gradient becomes zeros, so that every rank reaches every
+    collective; the momentum buffer is created on first use."""
+    if p.grad is None:
+        p.grad = torch.zeros_like(p)
+    elif not p.grad.is_contiguous():
+        p.grad = p.grad.contiguous()
+    state = optimizer.state[p]
+    if len(state) == 0:
+        state["momentum_buffer"] = torch.zeros_like(p)
+
+
+def _bucket_by_shape(params):
+    """Stable buckets of same-shape, same-dtype, same-device parameters."""
+    buckets: "OrderedDict[tuple, list]" = OrderedDict()
+    for p in params:
+        buckets.setdefault((tuple(p.shape), p.dtype, p.device), []).append(p)
+    return buckets
+
+
+def _muon_update_params(optimizer, params, group) -> None:
+    """Body of the reference's per-parameter loop (muon.py:91-99) for a list of parameters."""
+    backend = get_backend()
+    for p in params:
+        _ensure_grad_and_state(optimizer, p)
+    for plist in _bucket_by_shape(params).values():
+        backend.muon_step(plist, [p.grad for p in plist],
+                          [optimizer.state[p]["momentum_buffer"] for p in plist],
+                          group["lr"], group["weight_decay"], group["momentum"])
+
+
+def _adam_update_params(optimizer, group) -> None:
+    """Adam branch (muon.py:184-197): replicated on every rank, no collective."""
+    backend = get_backend()
+    params = group["params"]
+    for p in params:
+        if p.grad is None:
+            p.grad = torch.zeros_like(p)
+        elif not p.grad.is_contiguous():
+            p.grad = p.grad.contiguous()
+        state = optimizer.state[p]
+        if len(state) == 0:
+            state["exp_avg"] = torch.zeros_like(p)
+            state["exp_avg_sq"] = torch.zeros_like(p)
+            state["step"] = 0
+        state["step"] += 1
+    by_kind: "OrderedDict[tuple, list]" = OrderedDict()
+    for p in params:
+        by_kind.setdefault((p.dtype, p.device), []).append(p)
+    for plist in by_kind.values():
+        backend.adam_step(plist, [p.grad for p in plist],
+                          [optimizer.state[p]["exp_avg"] for p in plist],
+                          [optimizer.state[p]["exp_avg_sq"] for p in plist],
+                          [optimizer.state[p]["step"] for p in plist],
+                          group["lr"], group["weight_decay"], group["betas"], group["eps"])
+
+
+def _distributed_muon_group_step(optimizer, group) -> None:
+    """Windowed round-robin of muon.py:54-68. Window k holds params[kW:(k+1)W]; rank r
+    updates params[kW + r] and every rank then receives the whole window."""
+    backend = get_backend()
+    world, rank = dist.get_world_size(), dist.get_rank()
+    params = group["params"]
+    # muon.py:55 — the pad entries alias one scratch tensor and only ever receive.
+    params_pad = params + [torch.empty_like(params[-1])] * (world - len(params) % world)
+    owned = list(range(rank, len(params), world))
+    done_upto = 0  # owned[:done_upto] have been updated
+    pending = []
+    for base_i in range(0, len(params), world):
+        mine = base_i + rank
+        if mine < len(params) and done_upto < len(owned) and owned[done_upto] == mine:
+            # Update this window's parameter together with the same-shape ones this rank
+            # owns in the following windows (one grouped launch sequence).
+            p0 = params[mine]
+            rows, cols = view_2d(p0.shape)
+            limit = batch_size_for(min(rows, cols), max(rows, cols), len(owned) - done_upto,
+                                   getattr(backend, "workspace_cap_bytes", 4 << 30))
+            chunk = []
+            for idx in owned[done_upto:done_upto + limit]:
+                q = params[idx]
+                if q.shape != p0.shape or q.dtype != p0.dtype:
+                    break
+                chunk.append(q)
+            _muon_update_params(optimizer, chunk, group)
+            done_upto += len(chunk)
+        pending.append(dist.all_gather(params_pad[base_i:base_i + world], params_pad[mine],
+                                       async_op=True))
+    for work in pending:
+        if work is not None:
+            work.wait()
+
+
+class Muon(torch.optim.Optimizer):
+    """Distributed Muon (muon.py:18-70): momentum SGD whose 2-D updates are orthogonalised
+    by a Newton-Schulz iteration. Requires an initialised default process group.
+
+    Arguments:
+        lr: learning rate, in units of spectral norm per update.
+        weight_decay: AdamW-style decoupled weight decay.
+        momentum: momentum coefficient.
+    """
+
+    def __init__(self, params, lr=0.02, weight_decay=0, momentum=0.95):
+        defaults = dict(lr=lr, weight_decay=weight_decay, momentum=momentum)
+        assert isinstance(params, list) and len(params) >= 1 and isinstance(params[0], torch.nn.Parameter)
+        params = sorted(params, key=lambda x: x.size(), reverse=True)
+        super().__init__(params, defaults)
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for group in self.param_groups:
+            _distributed_muon_group_step(self, group)
+        return loss
+
+
+class SingleDeviceMuon(torch.optim.Optimizer):
+    """Muon for non-distributed settings (muon.py:73-101)."""
+
+    def __init__(self, params, lr=0.02, weight_decay=0, momentum=0.95):
+        defaults = dict(lr=lr, weight_decay=weight_decay, momentum=momentum)
+        super().__init__(params, defaults)
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for group in self.param_groups:
+            _muon_update_params(self, group["params"], group)
+        return loss
+
+
+def _apply_group_defaults(param_groups, sort_muon_params: bool) -> None:
+    """muon.py:140-155 / :207-221: per-group defaults and exact key-set checks."""
+    for group in param_groups:
+        assert "use_muon" in group
+        if group["use_muon"]:
+            if sort_muon_params:
+                group["params"] = sorted(group["params"], key=lambda x: x.size(), reverse=True)
+            group["lr"] = group.get("lr", 0.02)
+            group["momentum"] = group.get("momentum", 0.95)
+            group["weight_decay"] = group.get("weight_decay", 0)
+            assert set(group.keys()) == set(["params", "lr", "momentum", "weight_decay", "use_muon"])
+        else:
+            group["lr"] = group.get("lr", 3e-4)
+            group["betas"] = group.get("betas", (0.9, 0.95))
+            group["eps"] = group.get("eps", 1e-10)
+            group["weight_decay"] = group.get("weight_decay", 0)
+            assert set(group.keys()) == set(["params", "lr", "betas", "eps", "weight_decay", "use_muon"])
+
+
+class MuonWithAuxAdam(torch.optim.Optimizer):
+    """Distributed Muon with an internal Adam for the parameters Muon does not suit
+    (muon.py:112-199). Every group carries ``use_muon``; Muon groups accept ``lr``,
+    ``momentum``, ``weight_decay``; Adam groups accept ``lr``, ``betas``, ``eps``,
+    ``weight_decay``."""
+
+    def __init__(self, param_groups):
+        _apply_group_defaults(param_groups, sort_muon_params=True)
+        super().__init__(param_groups, dict())
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for group in self.param_groups:
+            if group["use_muon"]:
+                _distributed_muon_group_step(self, group)
+            else:
+                _adam_update_params(self, group)
+        return loss
+
+
+class SingleDeviceMuonWithAuxAdam(torch.optim.Optimizer):
+    """Non-distributed variant of MuonWithAuxAdam (muon.py:202-260)."""
+
+    def __init__(self, param_groups):
+        _apply_group_defaults(param_groups, sort_muon_params=False)
+        super().__init__(param_groups, dict())
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for group in self.param_groups:
+            if group["use_muon"]:
+                _muon_update_params(self, group["params"], group)
+            else:
+                _adam_update_params(self, group)
+        return loss

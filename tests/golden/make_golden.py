@@ -1,0 +1,173 @@
+"""Generates tests/golden/*.pt from the REAL reference (thib-s/Muon's muon.py) on CPU.
+
+Run in a container that has the reference checked out:
+
+    python tests/golden/make_golden.py /path/to/reference
+
+What the real reference can execute without a GPU, and what each fixture therefore pins:
+
+* ``adam.pt``        real ``SingleDeviceMuonWithAuxAdam`` Adam groups, 3 steps (muon.py:104-109, :244-258).
+* ``ns_lines_fp32.pt`` the real Triton kernels ``ns_line_1/2/3`` under Triton's CPU interpreter, fp32
+                     inputs, tile configs pinned to 64x64x64 (the interpreter cannot execute bf16).
+* ``muon_glue.pt``   real ``SingleDeviceMuon`` / ``muon_update`` (momentum lerps, Nesterov write-back,
+                     4-D view, aspect scale, weight decay, apply; muon.py:8-15, :81-101) with
+                     ``zeropower_via_newtonschulz5`` replaced by the oracle's restatement, because the
+                     real one needs a GPU. Inputs: fp32 wide, fp32 tall, bf16, 4-D filter with kH > kW.
+* ``api.pt``         constructor behaviour: sort order, group keys and defaults, assertion cases.
+* ``ns_oracle_bf16.pt`` the oracle's own bf16 Newton-Schulz output on seeded inputs (a drift guard for the
+                     restatement itself; NOT produced by the reference).
+
+Everything is seeded; files are a few hundred KB in total.
+"""
+import os
+import sys
+
+os.environ["TRITON_INTERPRET"] = "1"
+os.environ["TORCH_COMPILE_DISABLE"] = "1"
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+ref_dir = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+sys.path.insert(0, ref_dir)
+
+import muon as ref  # noqa: E402  the real reference module
+from oracle import muon_oracle as orc  # noqa: E402
+
+assert os.path.realpath(ref.__file__).startswith(os.path.realpath(ref_dir)), ref.__file__
+
+
+def gen_adam():
+    torch.manual_seed(11)
+    shapes = [(768,), (1000,), (7,), (33, 5), (4, 3, 2)]
+    out = {"shapes": shapes, "cases": []}
+    for dtype in (torch.float32, torch.bfloat16):
+        params = [torch.nn.Parameter(torch.randn(s).to(dtype)) for s in shapes]
+        p0 = [p.detach().clone() for p in params]
+        grads = [[(torch.randn(s) * 0.01).to(dtype) for s in shapes] for _ in range(3)]
+        opt = ref.SingleDeviceMuonWithAuxAdam(
+            [dict(params=params, use_muon=False, lr=3e-3, betas=(0.9, 0.95), eps=1e-10, weight_decay=0.01)])
+        for step_grads in grads:
+            for p, g in zip(params, step_grads):
+                p.grad = g.clone()
+            opt.step()
+        out["cases"].append(dict(
+            dtype=dtype, p0=p0, grads=grads, p=[p.detach().clone() for p in params],
+            exp_avg=[opt.state[p]["exp_avg"].clone() for p in params],
+            exp_avg_sq=[opt.state[p]["exp_avg_sq"].clone() for p in params],
+            step=[opt.state[p]["step"] for p in params],
+            hyper=dict(lr=3e-3, betas=(0.9, 0.95), eps=1e-10, weight_decay=0.01)))
+    # functional form, one call
+    g = torch.randn(50); b1 = torch.randn(50) * 0.1; b2 = torch.rand(50) * 0.1
+    b1o, b2o = b1.clone(), b2.clone()
+    u = ref.adam_update(g, b1o, b2o, 3, (0.9, 0.95), 1e-10)
+    out["functional"] = dict(grad=g, buf1=b1, buf2=b2, step=3, betas=(0.9, 0.95), eps=1e-10,
+                             buf1_out=b1o, buf2_out=b2o, update=u)
+    return out
+
+
+def gen_ns_lines_fp32():
+    for k in (ref.ns_line_1_kernel, ref.ns_line_2_kernel, ref.ns_line_3_kernel):
+        k.configs = [c for c in k.configs
+                     if c.kwargs["BLOCK_SIZE_M"] == 64 and c.kwargs["BLOCK_SIZE_N"] == 64
+                     and c.kwargs["BLOCK_SIZE_K"] == 64][:1]
+    torch.manual_seed(5)
+    cases = []
+    for (m, n, batch) in [(96, 160, None), (64, 64, None), (130, 200, None), (72, 136, 2)]:
+        shape = (m, n) if batch is None else (batch, m, n)
+        X = torch.randn(shape)
+        A = ref.ns_line_1(X)
+        As = A / A.abs().sum(-1, keepdim=True)  # asymmetric on purpose, like muon.py:785
+        B = ref.ns_line_2(As, alpha=2.4635, beta=-7.0585)
+        C = ref.ns_line_3(B, X, 4.0098)
+        cases.append(dict(X=X, A=A, As=As, alpha=2.4635, beta=-7.0585, B=B, a=4.0098, C=C, tile=64))
+    return {"cases": cases}
+
+
+def gen_muon_glue():
+    ref.zeropower_via_newtonschulz5 = orc.zeropower_via_newtonschulz5  # the one substitution
+    torch.manual_seed(23)
+    specs = [((64, 160), torch.float32), ((160, 64), torch.float32), ((48, 96), torch.bfloat16),
+             ((32, 16, 4, 2), torch.float32), ((96, 48), torch.bfloat16)]
+    hyper = dict(lr=0.02, weight_decay=0.01, momentum=0.95)
+    cases = []
+    for shape, dtype in specs:
+        p = torch.nn.Parameter((torch.randn(shape) * 0.02).to(dtype))
+        p0 = p.detach().clone()
+        grads = [torch.randn(shape).to(dtype) for _ in range(3)]
+        opt = ref.SingleDeviceMuon([p], **hyper)
+        trace = []
+        for g in grads:
+            p.grad = g.clone()
+            opt.step()
+            trace.append(dict(p=p.detach().clone(), grad_after=p.grad.clone(),
+                              momentum=opt.state[p]["momentum_buffer"].clone()))
+        cases.append(dict(shape=shape, dtype=dtype, p0=p0, grads=grads, trace=trace, hyper=hyper))
+    # functional muon_update, nesterov on/off
+    fn = []
+    for nesterov in (True, False):
+        g = torch.randn(40, 72); m = torch.randn(40, 72) * 0.1
+        g_in, m_in = g.clone(), m.clone()
+        u = ref.muon_update(g, m, beta=0.9, nesterov=nesterov)
+        fn.append(dict(grad=g_in, momentum=m_in, beta=0.9, nesterov=nesterov, grad_out=g, momentum_out=m,
+                       update=u.clone()))
+    return {"cases": cases, "functional": fn}
+
+
+def gen_api():
+    out = {}
+    ps = [torch.nn.Parameter(torch.zeros(s)) for s in [(32, 64), (64, 32), (64, 64), (16, 64), (64, 32)]]
+    # Muon needs a process group only in step(); construction works without one.
+    m = ref.Muon(list(ps))
+    out["muon_sorted_shapes"] = [tuple(p.shape) for p in m.param_groups[0]["params"]]
+    out["muon_group_keys"] = sorted(k for k in m.param_groups[0].keys())
+    out["muon_defaults"] = {k: m.param_groups[0][k] for k in ("lr", "momentum", "weight_decay")}
+    try:
+        ref.Muon([dict(params=ps)])
+        out["muon_rejects_group_dicts"] = False
+    except AssertionError:
+        out["muon_rejects_group_dicts"] = True
+    s = ref.SingleDeviceMuon([dict(params=ps)])
+    out["single_accepts_group_dicts"] = True
+    out["single_order_kept"] = [tuple(p.shape) for p in s.param_groups[0]["params"]]
+    aux = ref.MuonWithAuxAdam([dict(params=list(ps), use_muon=True),
+                               dict(params=[torch.nn.Parameter(torch.zeros(5))], use_muon=False)])
+    out["aux_muon_group"] = {k: v for k, v in aux.param_groups[0].items() if k != "params"}
+    out["aux_adam_group"] = {k: v for k, v in aux.param_groups[1].items() if k != "params"}
+    out["aux_sorted_shapes"] = [tuple(p.shape) for p in aux.param_groups[0]["params"]]
+    saux = ref.SingleDeviceMuonWithAuxAdam([dict(params=list(ps), use_muon=True)])
+    out["single_aux_order_kept"] = [tuple(p.shape) for p in saux.param_groups[0]["params"]]
+    for bad_key in ("nesterov", "ns_steps"):
+        try:
+            ref.MuonWithAuxAdam([dict(params=list(ps), use_muon=True, **{bad_key: 1})])
+            out[f"aux_rejects_{bad_key}"] = False
+        except AssertionError:
+            out[f"aux_rejects_{bad_key}"] = True
+    try:
+        ref.MuonWithAuxAdam([dict(params=list(ps))])
+        out["aux_requires_use_muon"] = False
+    except AssertionError:
+        out["aux_requires_use_muon"] = True
+    return out
+
+
+def gen_ns_oracle():
+    torch.manual_seed(31)
+    cases = []
+    for shape in [(64, 160), (160, 64), (96, 96), (3, 40, 72)]:
+        G = torch.randn(shape)
+        U = orc.zeropower_via_newtonschulz5(G)
+        Uc = orc.zeropower_classic5(G)
+        cases.append(dict(G=G, aol4=U.clone(), classic5=Uc.clone()))
+    return {"cases": cases}
+
+
+if __name__ == "__main__":
+    for name, fn in [("adam", gen_adam), ("ns_lines_fp32", gen_ns_lines_fp32), ("api", gen_api),
+                     ("ns_oracle_bf16", gen_ns_oracle), ("muon_glue", gen_muon_glue)]:
+        data = fn()
+        path = os.path.join(HERE, f"{name}.pt")
+        torch.save(data, path)
+        print(f"{name}: {os.path.getsize(path) / 1024:.1f} KiB")

@@ -1,0 +1,226 @@
+"""CPU tests of the host side: the C-ABI library's symbol table, the drop-in API surface
+(constructor behaviour recorded from the real reference in tests/golden/api.pt), the engine's
+grouping helpers, and the distributed ownership/windowing logic on gloo CPU ranks with a
+stand-in backend (the CUDA kernels need a GPU; the stand-in is test-only and uses the oracle)."""
+import os
+import re
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import muon_oracle as orc
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+# ------------------------------------------------------------------ library / header
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "muon_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(muon_b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    import muon_b200._lib as L
+    names = _declared_symbols()
+    assert len(names) >= 12
+    for n in names:
+        assert hasattr(L.lib, n), f"{n} declared in include/muon_b200.h but not exported"
+    assert set(names) == set(L.PROTOTYPES), "ctypes prototypes and header disagree"
+    assert L.lib.muon_b200_version() >= 100
+    assert L.lib.muon_b200_last_error() is not None
+
+
+def test_workspace_layout_is_host_only_and_consistent():
+    import muon_b200._lib as L
+    lay = L.ns_layout(3, 200, 330)
+    assert lay.ldn == 336 and lay.ldm == 200 and lay.x_bs == 200 * 336 and lay.a_bs == 200 * 200
+    offs = [lay.x_offset_bytes, lay.c_offset_bytes, lay.a_offset_bytes, lay.b_offset_bytes,
+            lay.partials_offset_bytes, lay.total_bytes]
+    assert offs == sorted(offs) and all(o % 256 == 0 for o in offs)
+    assert lay.c_offset_bytes - lay.x_offset_bytes >= 3 * lay.x_bs * 2
+    with pytest.raises(L.MuonB200Error):
+        L.ns_layout(1, 300, 200)  # m must be the short side
+    with pytest.raises(L.MuonB200Error):
+        L.ns_layout(0, 8, 8)
+
+
+def test_argument_errors_are_reported_without_a_gpu():
+    import ctypes
+    import muon_b200._lib as L
+    rc = L.lib.muon_b200_ns_run(None, 1, 8, 8, 0, 0, None, 1e-7, None, None)
+    assert rc == -1 and b"workspace" in L.lib.muon_b200_last_error()
+    rc = L.lib.muon_b200_ns_run(ctypes.c_void_p(256 * 10), 1, 8, 8, 7, 0, None, 1e-7, None, None)
+    assert rc == -1 and b"mode" in L.lib.muon_b200_last_error()
+    rc = L.lib.muon_b200_ns_run(ctypes.c_void_p(8), 1, 8, 8, 0, 0, None, 1e-7, None, None)
+    assert rc == -2
+    one = L.ptr_array([16])
+    rc = L.lib.muon_b200_prologue(one, one, 1, 8, 8, 5, 0.95, 1, ctypes.c_void_p(256), 8, 64, 0, None)
+    assert rc == -1 and b"dtype" in L.lib.muon_b200_last_error()
+
+
+def test_no_cpu_fallback():
+    import muon_b200
+    p = torch.nn.Parameter(torch.randn(8, 16))
+    p.grad = torch.randn(8, 16)
+    with pytest.raises(RuntimeError, match="no CPU implementation"):
+        muon_b200.SingleDeviceMuon([p]).step()
+    with pytest.raises(RuntimeError, match="no CPU implementation"):
+        muon_b200.zeropower_via_newtonschulz5(torch.randn(8, 16))
+    with pytest.raises(RuntimeError, match="no CPU implementation"):
+        muon_b200.adam_update(torch.randn(4), torch.zeros(4), torch.zeros(4), 1, (0.9, 0.95), 1e-10)
+
+
+# ------------------------------------------------------------------------ API surface
+def test_constructors_behave_like_the_reference(golden):
+    import muon_b200 as mb
+    api = golden("api")
+    shapes = [(32, 64), (64, 32), (64, 64), (16, 64), (64, 32)]
+    ps = [torch.nn.Parameter(torch.zeros(s)) for s in shapes]
+    m = mb.Muon(list(ps))
+    assert [tuple(p.shape) for p in m.param_groups[0]["params"]] == api["muon_sorted_shapes"]
+    assert {k: m.param_groups[0][k] for k in ("lr", "momentum", "weight_decay")} == api["muon_defaults"]
+    assert set(api["muon_group_keys"]) <= set(m.param_groups[0].keys())
+    with pytest.raises(AssertionError):
+        mb.Muon([dict(params=ps)])
+    assert api["muon_rejects_group_dicts"]
+    s = mb.SingleDeviceMuon([dict(params=ps)])
+    assert [tuple(p.shape) for p in s.param_groups[0]["params"]] == api["single_order_kept"]
+    aux = mb.MuonWithAuxAdam([dict(params=list(ps), use_muon=True),
+                              dict(params=[torch.nn.Parameter(torch.zeros(5))], use_muon=False)])
+    assert {k: v for k, v in aux.param_groups[0].items() if k != "params"} == api["aux_muon_group"]
+    assert {k: v for k, v in aux.param_groups[1].items() if k != "params"} == api["aux_adam_group"]
+    assert [tuple(p.shape) for p in aux.param_groups[0]["params"]] == api["aux_sorted_shapes"]
+    saux = mb.SingleDeviceMuonWithAuxAdam([dict(params=list(ps), use_muon=True)])
+    assert [tuple(p.shape) for p in saux.param_groups[0]["params"]] == api["single_aux_order_kept"]
+    for bad in ("nesterov", "ns_steps"):
+        assert api[f"aux_rejects_{bad}"]
+        with pytest.raises(AssertionError):
+            mb.MuonWithAuxAdam([dict(params=list(ps), use_muon=True, **{bad: 1})])
+    with pytest.raises(AssertionError):
+        mb.MuonWithAuxAdam([dict(params=list(ps))])
+    assert issubclass(mb.Muon, torch.optim.Optimizer)
+
+
+def test_muon_module_alias_exports_reference_names():
+    import muon
+    for name in ("Muon", "SingleDeviceMuon", "MuonWithAuxAdam", "SingleDeviceMuonWithAuxAdam",
+                 "muon_update", "adam_update", "zeropower_via_newtonschulz5",
+                 "ns_line_1", "ns_line_2", "ns_line_3"):
+        assert callable(getattr(muon, name))
+
+
+def test_engine_helpers():
+    from muon_b200 import engine as E
+    assert E.view_2d((256, 256, 3, 3)) == (256, 2304) and E.view_2d((5, 7)) == (5, 7)
+    with pytest.raises(ValueError):
+        E.view_2d((5,))
+    assert E.aspect_scale((3072, 768)) == 2.0 and E.aspect_scale((768, 3072)) == 1
+    assert E.aspect_scale((256, 256, 3, 3)) == 1 and E.aspect_scale((32, 16, 4, 2)) == 2 ** 0.5
+    assert E.tri_tiles(128) == 1 and E.tri_tiles(256) == 2 and E.tri_tiles(768) == 12
+    assert E.tri_tiles(4096) == sum(min(16, (i * 128 + 127) // 256 + 1) for i in range(32))
+    assert E.batch_size_for(128, 1152, 64, 4 << 30) == 64
+    assert E.batch_size_for(4096, 14336, 64, 4 << 30) >= 1
+    assert E.batch_size_for(4096, 14336, 64, 1 << 20) == 1
+    E.set_ns_mode("classic5", 3)
+    assert E.get_ns_mode() == ("classic5", 3)
+    E.set_ns_mode("aol4")
+    with pytest.raises(ValueError):
+        E.set_ns_mode("cubic")
+
+
+# -------------------------------------------------- distributed logic on gloo CPU ranks
+class OracleBackend:
+    """Test-only stand-in for the CUDA backend: same interface, oracle arithmetic."""
+
+    name = "oracle-test-double"
+    workspace_cap_bytes = 4 << 30
+
+    def __init__(self):
+        self.muon_calls = []
+
+    def muon_step(self, params, grads, moms, lr, weight_decay, beta, nesterov=True):
+        self.muon_calls.append([tuple(p.shape) for p in params])
+        for p, g, m in zip(params, grads, moms):
+            orc.muon_param_step(p, g, m, lr, weight_decay, beta)
+
+    def adam_step(self, params, grads, exp_avgs, exp_avg_sqs, steps, lr, weight_decay, betas, eps):
+        for p, g, m, v, s in zip(params, grads, exp_avgs, exp_avg_sqs, steps):
+            orc.adam_param_step(p, g, m, v, s, lr, weight_decay, betas, eps)
+
+
+def _make_problem(shapes, seed=0, steps=2):
+    g = torch.Generator().manual_seed(seed)
+    p0 = [torch.randn(s, generator=g) * 0.02 for s in shapes]
+    grads = [[torch.randn(s, generator=g) for s in shapes] for _ in range(steps)]
+    return p0, grads
+
+
+def _rank_main(rank, world, shapes, tmpdir, with_adam):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    dist.init_process_group("gloo", init_method=f"file://{tmpdir}/pg", rank=rank, world_size=world)
+    try:
+        import muon_b200 as mb
+        from muon_b200 import engine as E
+        backend = OracleBackend()
+        E._set_backend_for_testing(backend)
+        p0, grads = _make_problem(shapes)
+        params = [torch.nn.Parameter(p.clone()) for p in p0]
+        gains = [torch.nn.Parameter(torch.ones(8)) for _ in range(3)]
+        if with_adam:
+            opt = mb.MuonWithAuxAdam([dict(params=list(params), use_muon=True, lr=0.02, weight_decay=0.01),
+                                      dict(params=gains, use_muon=False)])
+        else:
+            opt = mb.Muon(list(params), lr=0.02, weight_decay=0.01)
+        skip_grad_for = 1  # this parameter never gets a gradient: it must be treated as zeros
+        for step_grads in grads:
+            for i, (p, gr) in enumerate(zip(params, step_grads)):
+                p.grad = None if i == skip_grad_for else gr.clone()
+            for gp in gains:
+                gp.grad = torch.full((8,), 0.5)
+            opt.step()
+        sorted_params = opt.param_groups[0]["params"]
+        owned = [i for i in range(len(sorted_params)) if i % world == rank]
+        has_state = [i for i, p in enumerate(sorted_params) if len(opt.state[p]) > 0]
+        torch.save(dict(params=[p.detach().clone() for p in params], owned=owned, has_state=has_state,
+                        calls=backend.muon_calls, gains=[g.detach().clone() for g in gains]),
+                   f"{tmpdir}/out{rank}.pt")
+    finally:
+        dist.destroy_process_group()
+
+
+def _single_device_oracle(shapes, skip_grad_for=1, steps=2):
+    p0, grads = _make_problem(shapes, steps=steps)
+    params = [p.clone() for p in p0]
+    moms = [torch.zeros_like(p) for p in p0]
+    for step_grads in grads:
+        for i, (p, gr, m) in enumerate(zip(params, step_grads, moms)):
+            g = torch.zeros_like(p) if i == skip_grad_for else gr.clone()
+            orc.muon_param_step(p, g, m, 0.02, 0.01, 0.95)
+    return params
+
+
+@pytest.mark.parametrize("world,with_adam", [(2, False), (2, True), (3, False)])
+def test_distributed_muon_on_gloo_ranks(tmp_path, world, with_adam):
+    # counts per shape are multiples of the world size so that windows are shape-homogeneous
+    # (gloo, like the reference on gloo, rejects unequal sizes inside one all_gather) except for
+    # the tail window, which is shorter than the world and exercises the padding rule.
+    shapes = [(24, 48)] * (2 * world) + [(48, 24)] * world + [(16, 16)] * (world - 1)
+    mp.spawn(_rank_main, args=(world, shapes, str(tmp_path), with_adam), nprocs=world, join=True)
+    outs = [torch.load(f"{tmp_path}/out{r}.pt", weights_only=False) for r in range(world)]
+    ref = _single_device_oracle(shapes)
+    for r, o in enumerate(outs):
+        for p, q in zip(o["params"], ref):
+            assert torch.equal(p, q), f"rank {r} disagrees with the single-device result"
+        assert o["has_state"] == o["owned"], "momentum state must exist on the owning rank only"
+        # same-shape parameters owned by a rank are handed to the backend together
+        assert all(len(set(c)) == 1 for c in o["calls"])
+        assert max(len(c) for c in o["calls"]) > 1
+    if with_adam:
+        g0 = outs[0]["gains"]
+        for o in outs[1:]:
+            for a, b in zip(o["gains"], g0):
+                assert torch.equal(a, b)
+        assert not torch.equal(g0[0], torch.ones(8))
