@@ -106,8 +106,9 @@ def _distributed_muon_group_step(optimizer, group) -> None:
                 chunk.append(q)
             _muon_update_params(optimizer, chunk, group)
             done_upto += len(chunk)
-        pending.append(dist.all_gather(params_pad[base_i:base_i + world], params_pad[mine],
-                                       async_op=True))
+        if world > 1:  # with one rank the gather would copy each parameter onto itself
+            pending.append(dist.all_gather(params_pad[base_i:base_i + world], params_pad[mine],
+                                           async_op=True))
     for work in pending:
         if work is not None:
             work.wait()
