@@ -21,15 +21,17 @@
 // output for a non-symmetric A depends on tile shape and store order.
 //
 // Roles inside a CTA (192 threads):
-//   warp 0      TMA producer: fills a 4-stage ring of {A tile, B tile} in shared memory
-//   warp 1      MMA issuer: tcgen05.mma 128x256x16, accumulators double-buffered in TMEM
+//   warp 0      TMA producer: fills a ring of {A tile, B tile} stages in shared memory
+//   warp 1      MMA issuer: tcgen05.mma, K = 16 per instruction, accumulators double-buffered
+//               in TMEM (2 x 256 columns)
 //   warps 2..5  epilogue: tcgen05.ld -> fp32 epilogue -> bf16 stores (+ mirrored stores)
-// The grid is persistent: each CTA walks tiles blockIdx.x, +gridDim.x, ...
+// The grid is persistent: each CTA (or CTA pair) walks tiles w, w + stride, ...
 #include "common.cuh"
 #include "ns_gemm.h"
 #include "profiling.h"
 
 #include <cuda.h>
+#include <cstdlib>
 #include <mutex>
 
 namespace mb {
@@ -49,42 +51,57 @@ int clear_device_status() {
 
 namespace {
 
-constexpr int BM = 128;  // UMMA M
+constexpr int BM = 128;  // rows of the output tile each CTA owns (TMEM lanes)
 constexpr int BN = 256;  // UMMA N
 constexpr int BK = 64;   // one 128-byte swizzle span of bf16
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 4;
-constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
-constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int TMEM_COLS = 512;  // two 128x256 fp32 accumulators
+constexpr int TMEM_COLS = 512;  // two 256-column fp32 accumulators
 constexpr int NUM_THREADS = 192;
 constexpr int SMEM_BARRIER_BYTES = 256;
-constexpr int SMEM_TOTAL = STAGES * STAGE_BYTES + SMEM_BARRIER_BYTES + 1024;  // + align slack
+
+// CTAS = 1: one CTA computes a 128 x 256 tile (tcgen05.mma.cta_group::1, M = 128).
+// CTAS = 2: a cluster of two CTAs computes a 256 x 256 tile with one cta_group::2 MMA
+//           (M = 256): each CTA stages its 128 rows of the A tile and its 128 of the 256
+//           rows of the B tile, so per FLOP a third less operand traffic leaves L2 and
+//           each SM's shared memory is read half as often for B.
+template <int CTAS>
+struct Cfg {
+  static constexpr int TILE_M = BM * CTAS;
+  static constexpr int B_ROWS = BN / CTAS;               // B-operand rows this CTA stages
+  static constexpr int STAGES = CTAS == 1 ? 4 : 6;
+  static constexpr int A_STAGE_BYTES = BM * BK * 2;       // 16 KiB
+  static constexpr int B_STAGE_BYTES = B_ROWS * BK * 2;   // 32 / 16 KiB
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int SMEM_TOTAL = STAGES * STAGE_BYTES + SMEM_BARRIER_BYTES + 1024;  // + align
+};
 
 struct TileCoord {
   int batch, tm, tn;
 };
 
 // Linear tile index -> (batch, tile row, tile col). For the triangular schedule row
-// tile i owns the column tiles j with j*BN <= i*BM + BM - 1.
-__device__ __forceinline__ int tri_row_count(int i, int tiles_n) {
-  int c = (i * BM + BM - 1) / BN + 1;
+// tile i (tile_m rows) owns the column tiles j with j*BN <= i*tile_m + tile_m - 1.
+__host__ __device__ __forceinline__ int tri_row_count(int i, int tiles_n, int tile_m) {
+  int c = (i * tile_m + tile_m - 1) / BN + 1;
   return c < tiles_n ? c : tiles_n;
 }
 
+template <int TILE_M>
 __device__ __forceinline__ TileCoord decode_tile(int t, const GemmParams& p) {
   TileCoord tc;
   tc.batch = t / p.tiles_per_batch;
   int r = t - tc.batch * p.tiles_per_batch;
   if (!p.triangular) {
-    tc.tm = r / p.tiles_n;
-    tc.tn = r - tc.tm * p.tiles_n;
+    // Row tiles vary fastest: the CTAs of one wave share a few 256-column slabs of the wide
+    // operand X, which is then streamed from HBM once, while the small square operand
+    // (every row tile reads a different part of it) stays resident in L2.
+    tc.tn = r / p.tiles_m;
+    tc.tm = r - tc.tn * p.tiles_m;
     return tc;
   }
   int i = 0;
   for (; i < p.tiles_m; ++i) {
-    int c = tri_row_count(i, p.tiles_n);
+    int c = tri_row_count(i, p.tiles_n, TILE_M);
     if (r < c) break;
     r -= c;
   }
@@ -93,14 +110,14 @@ __device__ __forceinline__ TileCoord decode_tile(int t, const GemmParams& p) {
   return tc;
 }
 
-// Instruction descriptor: bf16 x bf16 -> fp32, M=128, N=256, A K-major, B as templated.
-__host__ __device__ constexpr uint32_t make_idesc(bool b_mn_major) {
-  return (1u << 4)                      // D format: f32
-         | (1u << 7)                    // A format: bf16
-         | (1u << 10)                   // B format: bf16
+// Instruction descriptor: bf16 x bf16 -> fp32, N = 256, A K-major, B K- or MN-major.
+__host__ __device__ constexpr uint32_t make_idesc(bool b_mn_major, int mma_m) {
+  return (1u << 4)                         // D format: f32
+         | (1u << 7)                       // A format: bf16
+         | (1u << 10)                      // B format: bf16
          | ((b_mn_major ? 1u : 0u) << 16)  // B major: 0 = K, 1 = MN
-         | (uint32_t(BN >> 3) << 17)    // N
-         | (uint32_t(BM >> 4) << 24);   // M
+         | (uint32_t(BN >> 3) << 17)       // N
+         | (uint32_t(mma_m >> 4) << 24);   // M
 }
 
 // ---------------------------------------------------------------------------
@@ -152,15 +169,18 @@ __device__ __forceinline__ void store_row32(__nv_bfloat16* dst, int col0, int co
   }
 }
 
-template <int MODE, bool B_MN>
+template <int MODE, bool B_MN, int CTAS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const GemmParams p) {
+  using C = Cfg<CTAS>;
+  constexpr int STAGES = C::STAGES;
+  constexpr int TILE_M = C::TILE_M;
   extern __shared__ uint8_t smem_raw[];
   __shared__ int s_abort;
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  const uint32_t bar_base = smem_base + STAGES * C::STAGE_BYTES;
   // barrier layout (8 bytes each): full[STAGES], empty[STAGES], tfull[2], tempty[2], tmem slot
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
@@ -168,11 +188,14 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
   const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  volatile uint32_t* tmem_slot_ptr =
-      reinterpret_cast<volatile uint32_t*>(smem_gen + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(
+      smem_gen + STAGES * C::STAGE_BYTES + 8 * (2 * STAGES + 4));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // In a pair, CTA 0 issues the MMAs and owns the barriers the pair shares (full, tempty).
+  const uint32_t cta_rank = CTAS == 2 ? cluster_cta_rank() : 0u;
+  const bool leader = cta_rank == 0;
 
   if (threadIdx.x == 0) {
     s_abort = 0;
@@ -182,23 +205,31 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+      mbar_init(tempty_bar(a), 4 * CTAS);  // one arrival per epilogue warp of every CTA
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, TMEM_COLS);
-    tmem_relinquish();
+    if (CTAS == 2) {
+      tmem_alloc_pair(tmem_slot, TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (CTAS == 2) cluster_sync_all();  // the peer's barriers exist before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
 
   const int k_blocks = (p.K + BK - 1) / BK;
   const int total_tiles = p.tiles_per_batch * p.batch;
+  const int work0 = blockIdx.x / CTAS;
+  const int work_stride = gridDim.x / CTAS;
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -206,28 +237,46 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const TileCoord tc = decode_tile(t, p);
+      for (int t = work0; t < total_tiles && ok; t += work_stride) {
+        const TileCoord tc = decode_tile<TILE_M>(t, p);
+        const int a_row = tc.tm * TILE_M + (int)cta_rank * BM;
+        const int b_row = tc.tn * BN + (int)cta_rank * C::B_ROWS;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, &s_abort)) {
+          const bool freed = CTAS == 2 ? mbar_wait_bounded_cluster(empty_bar(stage), phase ^ 1u, &s_abort)
+                                       : mbar_wait_bounded(empty_bar(stage), phase ^ 1u, &s_abort);
+          if (!freed) {
             atomicCAS(&g_device_status, 0, 1);
             s_abort = 1;
             ok = false;
             break;
           }
-          const uint32_t sa = smem_base + stage * STAGE_BYTES;
-          const uint32_t sb = sa + A_STAGE_BYTES;
-          mbar_expect_tx(full_bar(stage), STAGE_BYTES);
-          tma_load_3d(sa, &tmap_a, full_bar(stage), kb * BK, tc.tm * BM, tc.batch);
-          if (!B_MN) {
-            // B operand rows are output columns; K contiguous.
-            tma_load_3d(sb, &tmap_b, full_bar(stage), kb * BK, tc.tn * BN, tc.batch);
-          } else {
-            // B operand is [K, N] with N contiguous: four 64-column slabs of 64 k-rows.
+          const uint32_t sa = smem_base + stage * C::STAGE_BYTES;
+          const uint32_t sb = sa + C::A_STAGE_BYTES;
+          if (CTAS == 2) {
+            // Both CTAs' copies complete on the leader's barrier, which expects both halves.
+            const uint32_t full = map_to_cta(full_bar(stage), 0);
+            if (leader) mbar_expect_tx(full_bar(stage), 2 * C::STAGE_BYTES);
+            tma_load_3d_pair(sa, &tmap_a, full, kb * BK, a_row, tc.batch);
+            if (!B_MN) {
+              tma_load_3d_pair(sb, &tmap_b, full, kb * BK, b_row, tc.batch);
+            } else {
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c)
-              tma_load_3d(sb + c * (BK * 128), &tmap_b, full_bar(stage), tc.tn * BN + c * 64,
-                          kb * BK, tc.batch);
+              for (int c = 0; c < C::B_ROWS / 64; ++c)
+                tma_load_3d_pair(sb + c * (BK * 128), &tmap_b, full, b_row + c * 64, kb * BK, tc.batch);
+            }
+          } else {
+            mbar_expect_tx(full_bar(stage), C::STAGE_BYTES);
+            tma_load_3d(sa, &tmap_a, full_bar(stage), kb * BK, a_row, tc.batch);
+            if (!B_MN) {
+              // B operand rows are output columns; K contiguous.
+              tma_load_3d(sb, &tmap_b, full_bar(stage), kb * BK, b_row, tc.batch);
+            } else {
+              // B operand is [K, N] with N contiguous: 64-column slabs of 64 k-rows.
+#pragma unroll
+              for (int c = 0; c < C::B_ROWS / 64; ++c)
+                tma_load_3d(sb + c * (BK * 128), &tmap_b, full_bar(stage), b_row + c * 64, kb * BK,
+                            tc.batch);
+            }
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -242,16 +291,19 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(B_MN);
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc(B_MN, TILE_M);
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+      for (int t = work0; t < total_tiles && ok; t += work_stride, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1u;
-        if (!mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, &s_abort)) {
+        const bool drained = CTAS == 2
+                                 ? mbar_wait_bounded_cluster(tempty_bar(acc), acc_phase ^ 1u, &s_abort)
+                                 : mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, &s_abort);
+        if (!drained) {
           atomicCAS(&g_device_status, 0, 3);
           s_abort = 1;
           break;
@@ -259,15 +311,17 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait_bounded(full_bar(stage), phase, &s_abort)) {
+          const bool filled = CTAS == 2 ? mbar_wait_bounded_cluster(full_bar(stage), phase, &s_abort)
+                                        : mbar_wait_bounded(full_bar(stage), phase, &s_abort);
+          if (!filled) {
             atomicCAS(&g_device_status, 0, 2);
             s_abort = 1;
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_base + stage * STAGE_BYTES;
-          const uint32_t sb = sa + A_STAGE_BYTES;
+          const uint32_t sa = smem_base + stage * C::STAGE_BYTES;
+          const uint32_t sb = sa + C::A_STAGE_BYTES;
           // K-major tiles: rows of 128 bytes, 8-row groups 1024 bytes apart.
           const uint64_t a_desc = make_smem_desc_sw128(sa, 16, 1024);
           // MN-major B: 64-column slabs BK*128 bytes apart, 8-k groups 1024 bytes apart.
@@ -278,26 +332,36 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const uint64_t a_adv = static_cast<uint64_t>((kk * UMMA_K * 2) >> 4);
             const uint64_t b_adv = B_MN ? static_cast<uint64_t>((kk * UMMA_K * 128) >> 4)
                                         : static_cast<uint64_t>((kk * UMMA_K * 2) >> 4);
-            umma_bf16_ss(d_tmem, a_desc + a_adv, b_desc + b_adv, idesc, (kb | kk) != 0 ? 1u : 0u);
+            const uint32_t accumulate = (kb | kk) != 0 ? 1u : 0u;
+            if (CTAS == 2) umma_bf16_ss_pair(d_tmem, a_desc + a_adv, b_desc + b_adv, idesc, accumulate);
+            else umma_bf16_ss(d_tmem, a_desc + a_adv, b_desc + b_adv, idesc, accumulate);
           }
-          umma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+          // Frees the stage (in both CTAs of a pair) once these MMAs have read it.
+          if (CTAS == 2) umma_commit_pair(empty_bar(stage), 0x3);
+          else umma_commit(empty_bar(stage));
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (ok) umma_commit(tfull_bar(acc));  // accumulator complete
+        if (ok) {  // accumulator complete: wake the epilogue warps (of both CTAs)
+          if (CTAS == 2) umma_commit_pair(tfull_bar(acc), 0x3);
+          else umma_commit(tfull_bar(acc));
+        }
       }
     }
   } else {
     // -------------------------------- epilogue --------------------------------
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     int local = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
-      const TileCoord tc = decode_tile(t, p);
+    for (int t = work0; t < total_tiles; t += work_stride, ++local) {
+      const TileCoord tc = decode_tile<TILE_M>(t, p);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1u;
-      int ok = mbar_wait_bounded(tfull_bar(acc), acc_phase, &s_abort) ? 1 : 0;
+      int ok = (CTAS == 2 ? mbar_wait_bounded_cluster(tfull_bar(acc), acc_phase, &s_abort)
+                          : mbar_wait_bounded(tfull_bar(acc), acc_phase, &s_abort))
+                   ? 1
+                   : 0;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         if (lane == 0) {
@@ -308,8 +372,9 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
       tc_fence_after();
 
-      const int r = tc.tm * BM + q * 32 + lane;  // output row of this thread
-      const int r_warp_max = tc.tm * BM + q * 32 + 31;
+      const int row_base = tc.tm * TILE_M + (int)cta_rank * BM + q * 32;
+      const int r = row_base + lane;  // output row of this thread
+      const int r_warp_max = row_base + 31;
       const bool row_ok = r < p.M;
       __nv_bfloat16* out_b = p.out + static_cast<long long>(tc.batch) * p.out_bs;
       const __nv_bfloat16* add_b =
@@ -393,17 +458,26 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
         }
       }
-      // Accumulator drained: hand it back to the MMA warp.
+      // Accumulator drained: hand it back to the MMA warp (of the pair's leader).
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (lane == 0) {
+        if (CTAS == 2) mbar_arrive_remote(map_to_cta(tempty_bar(acc), 0));
+        else mbar_arrive(tempty_bar(acc));
+      }
     }
   }
 
   tc_fence_before();
   __syncthreads();
+  // A CTA of a pair must outlive every access its peer makes to its shared memory,
+  // barriers and tensor memory.
+  if (CTAS == 2) cluster_sync_all();
   tc_fence_after();
-  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (warp == 1) {
+    if (CTAS == 2) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -456,28 +530,70 @@ struct DeviceInfo {
   int sm_count = 0;
   int cc_major = 0;
   bool attr_set[6] = {false, false, false, false, false, false};
+  int max_clusters[6] = {0, 0, 0, 0, 0, 0};
 };
 DeviceInfo g_dev[64];
 std::mutex g_dev_mu;
 
-template <int MODE, bool B_MN>
-int launch_instance(int dev, int slot, const CUtensorMap& ta, const CUtensorMap& tb,
-                    const GemmParams& p, int grid, cudaStream_t stream) {
-  auto kern = ns_gemm_kernel<MODE, B_MN>;
+// 0 = pick per shape, 1 / 2 = force the one- or two-CTA kernel (environment variable
+// MUON_B200_NS_CTAS, read once; meant for A/B measurements).
+int forced_ctas() {
+  static int v = [] {
+    const char* e = std::getenv("MUON_B200_NS_CTAS");
+    int x = e ? std::atoi(e) : 0;
+    return (x == 1 || x == 2) ? x : 0;
+  }();
+  return v;
+}
+
+template <int MODE, bool B_MN, int CTAS>
+int launch_instance(int dev, int sms, const CUtensorMap& ta, const CUtensorMap& tb,
+                    const GemmParams& p, cudaStream_t stream) {
+  using C = Cfg<CTAS>;
+  auto kern = ns_gemm_kernel<MODE, B_MN, CTAS>;
+  const int slot = MODE * 2 + (CTAS - 1);
+  const long long total = (long long)p.tiles_per_batch * p.batch;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = C::SMEM_TOTAL;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTAS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+
+  int max_units;  // co-resident CTAs (CTAS = 1) or clusters (CTAS = 2)
   {
     std::lock_guard<std::mutex> lk(g_dev_mu);
     if (!g_dev[dev].attr_set[slot]) {
       MB_CUDA_CHECK(
-          cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
+          cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_TOTAL));
+      if (CTAS == 2) {
+        cfg.gridDim = dim3(sms / 2 * 2);
+        int n = 0;
+        cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+        if (e != cudaSuccess || n < 1) {
+          (void)cudaGetLastError();
+          n = sms / 2;
+        }
+        g_dev[dev].max_clusters[slot] = n;
+      }
       g_dev[dev].attr_set[slot] = true;
     }
+    max_units = CTAS == 2 ? g_dev[dev].max_clusters[slot] : sms;
   }
+  const int units = (int)(total < max_units ? total : max_units);
+  cfg.gridDim = dim3(units * CTAS);
   {
     const double m = p.M, n = p.N, k = p.K, b = p.batch;
     const double flops = MODE == MODE_BX ? 2.0 * m * k * n * b : m * (m + 1.0) * k * b;
     LaunchScope scope(MODE == MODE_SYRK ? K_NS_LINE1 : MODE == MODE_AXPBY ? K_NS_LINE2 : K_NS_LINE3,
                       flops, stream);
-    kern<<<grid, NUM_THREADS, SMEM_TOTAL, stream>>>(ta, tb, p);
+    MB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, ta, tb, p));
   }
   MB_CUDA_CHECK(cudaGetLastError());
   return OK;
@@ -525,12 +641,18 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
   int dev = 0;
   MB_CUDA_CHECK(cudaGetDevice(&dev));
 
+  // A pair wastes half its rows on a matrix of at most 128 rows: those stay on one CTA.
+  int ctas = forced_ctas();
+  if (ctas == 0) ctas = M > BM ? 2 : 1;
+  const int tile_m = BM * ctas;
+  const int b_rows = BN / ctas;
+
   GemmParams p{};
   p.M = (int)M;
   p.N = (int)N;
   p.K = (int)K;
   p.batch = batch;
-  p.tiles_m = (int)((M + BM - 1) / BM);
+  p.tiles_m = (int)((M + tile_m - 1) / tile_m);
   p.tiles_n = (int)((N + BN - 1) / BN);
   p.alpha = alpha;
   p.beta = beta;
@@ -543,10 +665,7 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
     if (M != N) return set_error(ERR_INVALID_ARG, "symmetric product needs a square output");
     p.triangular = 1;
     int cnt = 0;
-    for (int i = 0; i < p.tiles_m; ++i) {
-      int c = (i * BM + BM - 1) / BN + 1;
-      cnt += c < p.tiles_n ? c : p.tiles_n;
-    }
+    for (int i = 0; i < p.tiles_m; ++i) cnt += tri_row_count(i, p.tiles_n, tile_m);
     p.tiles_per_batch = cnt;
     p.sym_add = sym_add;
     p.add = opa;  // line 2 adds beta * A, where A is the operand itself
@@ -556,7 +675,7 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
       return set_error(ERR_INVALID_ARG, "line 2 needs a square operand (got %lld x %lld)",
                        (long long)M, (long long)K);
     if ((rc = encode_map(&ta, opa, M, K, lda, a_bs, batch, BM)) != OK) return rc;
-    if ((rc = encode_map(&tb, opb, M, K, ldb, b_bs, batch, BN)) != OK) return rc;
+    if ((rc = encode_map(&tb, opb, M, K, ldb, b_bs, batch, b_rows)) != OK) return rc;
   } else if (mode == MODE_BX) {
     if (K != M) return set_error(ERR_INVALID_ARG, "line 3 needs a square left operand");
     p.triangular = 0;
@@ -571,18 +690,20 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
   }
   if ((reinterpret_cast<uintptr_t>(p.add) & 15) != 0 || (p.ldadd % 8) != 0)
     return set_error(ERR_ALIGNMENT, "NS GEMM addend must be 16-byte aligned with pitch %% 8 == 0");
+  if ((long long)p.tiles_per_batch * batch > (1ll << 30))
+    return set_error(ERR_UNSUPPORTED, "too many output tiles");
 
-  long long total = (long long)p.tiles_per_batch * batch;
-  if (total > (1ll << 30)) return set_error(ERR_UNSUPPORTED, "too many output tiles");
-  int grid = (int)(total < sms ? total : sms);
-
+  if (ctas == 2) {
+    switch (mode) {
+      case MODE_SYRK: return launch_instance<MODE_SYRK, false, 2>(dev, sms, ta, tb, p, stream);
+      case MODE_AXPBY: return launch_instance<MODE_AXPBY, false, 2>(dev, sms, ta, tb, p, stream);
+      default: return launch_instance<MODE_BX, true, 2>(dev, sms, ta, tb, p, stream);
+    }
+  }
   switch (mode) {
-    case MODE_SYRK:
-      return launch_instance<MODE_SYRK, false>(dev, 0, ta, tb, p, grid, stream);
-    case MODE_AXPBY:
-      return launch_instance<MODE_AXPBY, false>(dev, 1, ta, tb, p, grid, stream);
-    default:
-      return launch_instance<MODE_BX, true>(dev, 2, ta, tb, p, grid, stream);
+    case MODE_SYRK: return launch_instance<MODE_SYRK, false, 1>(dev, sms, ta, tb, p, stream);
+    case MODE_AXPBY: return launch_instance<MODE_AXPBY, false, 1>(dev, sms, ta, tb, p, stream);
+    default: return launch_instance<MODE_BX, true, 1>(dev, sms, ta, tb, p, stream);
   }
 }
 

@@ -84,15 +84,24 @@ def aspect_scale(shape: Sequence[int]) -> float:
 
 
 def tri_tiles(m: int) -> int:
-    """Output tiles of the triangular schedule for an m x m product (128 x 256 tiles)."""
-    tiles_n = (m + 255) // 256
-    return sum(min(tiles_n, (i * 128 + 127) // 256 + 1) for i in range((m + 127) // 128))
+    """Work units of the triangular schedule for an m x m product: 256 x 256 tiles computed
+    by CTA pairs when m > 128, one 128 x 256 tile otherwise (mirrors csrc/ns_gemm.cu)."""
+    if m <= 128:
+        return 1
+    t = (m + 255) // 256
+    return t * (t + 1) // 2
+
+
+# A launch ends with one partly filled wave of the 74 CTA pairs of a B200; with this many
+# work units per launch that tail costs at most about a twelfth of the launch.
+_TARGET_UNITS_PER_LAUNCH = 888
 
 
 def batch_size_for(m: int, n: int, count: int, workspace_cap_bytes: int) -> int:
-    """How many same-shape matrices share one grouped launch: enough for about four waves
-    of tiles on the smallest product (line 2), within the workspace cap."""
-    want = max(1, math.ceil(592 / max(1, tri_tiles(m))))
+    """How many same-shape matrices share one grouped launch: enough work units on the
+    triangular products (lines 1 and 2) to amortise the last partial wave, within the
+    workspace cap."""
+    want = max(1, math.ceil(_TARGET_UNITS_PER_LAUNCH / max(1, tri_tiles(m))))
     per_matrix = 2 * (2 * m * ((n + 7) // 8 * 8) + 2 * m * ((m + 7) // 8 * 8)) + 2048
     fit = max(1, workspace_cap_bytes // per_matrix)
     return max(1, min(count, want, fit))

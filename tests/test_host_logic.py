@@ -119,9 +119,10 @@ def test_engine_helpers():
         E.view_2d((5,))
     assert E.aspect_scale((3072, 768)) == 2.0 and E.aspect_scale((768, 3072)) == 1
     assert E.aspect_scale((256, 256, 3, 3)) == 1 and E.aspect_scale((32, 16, 4, 2)) == 2 ** 0.5
-    assert E.tri_tiles(128) == 1 and E.tri_tiles(256) == 2 and E.tri_tiles(768) == 12
-    assert E.tri_tiles(4096) == sum(min(16, (i * 128 + 127) // 256 + 1) for i in range(32))
+    assert E.tri_tiles(128) == 1 and E.tri_tiles(256) == 1 and E.tri_tiles(768) == 6
+    assert E.tri_tiles(4096) == 136
     assert E.batch_size_for(128, 1152, 64, 4 << 30) == 64
+    assert E.batch_size_for(4096, 14336, 64, 4 << 30) == 7
     assert E.batch_size_for(4096, 14336, 64, 4 << 30) >= 1
     assert E.batch_size_for(4096, 14336, 64, 1 << 20) == 1
     E.set_ns_mode("classic5", 3)
