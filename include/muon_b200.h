@@ -72,6 +72,11 @@ int muon_b200_timing_enable(int on);
 /* Waits for the recorded intervals; returns per kind the summed device time (ms), summed
  * work units and number of launches since the last collect, and forgets them. */
 int muon_b200_timing_collect(double* ms, double* work, int64_t* launches, int n_kinds);
+/* Same data, one record per launch in launch order (at most max_records; the rest is dropped).
+ * tags[i] describes the launch: for the NS lines (M << 40) | (K << 16) | (batch << 4) | flags (for line 3 the K field holds N),
+ * with flag bit 0 = line 2 ran with a_is_symmetric, bit 1 = two-CTA kernel; 0 for other kinds. */
+int muon_b200_timing_collect_records(int max_records, int* kinds, int64_t* tags, double* ms,
+                                     double* work, int* n_out);
 
 /* ---- Newton-Schulz GEMM lines ---------------------------------------------------
  * All matrices are bf16, row-major with a pitch (ld*, in elements, multiple of 8) and a

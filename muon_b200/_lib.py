@@ -47,6 +47,8 @@ PROTOTYPES = {
     "muon_b200_launch_counts": (c_int, [POINTER(c_int64), c_int]),
     "muon_b200_timing_enable": (c_int, [c_int]),
     "muon_b200_timing_collect": (c_int, [POINTER(c_double), POINTER(c_double), POINTER(c_int64), c_int]),
+    "muon_b200_timing_collect_records": (c_int, [c_int, POINTER(c_int), POINTER(c_int64), POINTER(c_double),
+                                                 POINTER(c_double), POINTER(c_int)]),
     "muon_b200_ns_line1": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int,
                                    c_int64, c_int64, c_void_p]),
     "muon_b200_ns_line2": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int,
@@ -129,6 +131,14 @@ def timing_collect() -> dict:
     ms, work, cnt = (c_double * n)(), (c_double * n)(), (c_int64 * n)()
     check(lib.muon_b200_timing_collect(ms, work, cnt, n))
     return {k: (ms[i], work[i], cnt[i]) for i, k in enumerate(KERNEL_KINDS)}
+
+
+def timing_collect_records(max_records: int = 1 << 16) -> list:
+    """[(kind, tag, device ms, work units)] per launch since the last collect (see the header)."""
+    kinds, tags = (c_int * max_records)(), (c_int64 * max_records)()
+    ms, work, n = (c_double * max_records)(), (c_double * max_records)(), c_int(0)
+    check(lib.muon_b200_timing_collect_records(max_records, kinds, tags, ms, work, ctypes.byref(n)))
+    return [(KERNEL_KINDS[kinds[i]], tags[i], ms[i], work[i]) for i in range(n.value)]
 
 
 def ns_layout(batch: int, m: int, n: int) -> NsLayout:

@@ -101,6 +101,13 @@ int muon_b200_timing_collect(double* ms, double* work, int64_t* launches, int n_
   return timing_collect(ms, work, launches, n_kinds);
 }
 
+int muon_b200_timing_collect_records(int max_records, int* kinds, int64_t* tags, double* ms,
+                                     double* work, int* n_out) {
+  if (max_records < 0 || !kinds || !tags || !ms || !work || !n_out)
+    return set_error(ERR_INVALID_ARG, "timing_collect_records: bad arguments");
+  return timing_collect_records(max_records, kinds, tags, ms, work, n_out);
+}
+
 int muon_b200_ns_line1(const void* x, int64_t ldx, int64_t x_bs, void* a_out, int64_t lda,
                        int64_t a_bs, int batch, int64_t m, int64_t k, muon_b200_stream_t stream) {
   return launch_ns_gemm(MODE_SYRK, bf(x), ldx, x_bs, bf(x), ldx, x_bs, bf(a_out), lda, a_bs, batch,
@@ -141,7 +148,9 @@ int muon_b200_ns_workspace_layout(int batch, int64_t m, int64_t n, muon_b200_ns_
   l.a_offset_bytes = 2 * xb;
   l.b_offset_bytes = 2 * xb + ab;
   l.partials_offset_bytes = 2 * xb + 2 * ab;
-  l.total_bytes = l.partials_offset_bytes + round_up((int64_t)batch * kFroChunksMax * 4, 256);
+  // fp32 scratch per matrix: Frobenius partial sums (classic) or the AOL row sums s (m floats).
+  const int64_t per_matrix = l.ldm > kFroChunksMax ? l.ldm : kFroChunksMax;
+  l.total_bytes = l.partials_offset_bytes + round_up((int64_t)batch * per_matrix * 4, 256);
   *out = l;
   return OK;
 }
@@ -175,7 +184,10 @@ int muon_b200_ns_run(void* workspace, int batch, int64_t m, int64_t n, int mode,
     rc = launch_ns_gemm(MODE_SYRK, X, l.ldn, l.x_bs, X, l.ldn, l.x_bs, A, l.ldm, l.a_bs, batch, m,
                         m, n, 1.f, 0.f, 1, st);
     if (rc != OK) return rc;
-    rc = launch_aol_rescale(X, l.ldn, l.x_bs, A, l.ldm, l.a_bs, (int)m, (int)n, batch, eps, st);
+    // A / s is written into slot C (free until the first line 3 writes it, and m <= n) with
+    // A's pitches, so the symmetric unscaled A and s remain for line 2's epilogue.
+    rc = launch_aol_rescale(X, l.ldn, l.x_bs, A, C, l.ldm, l.a_bs, partials, l.ldm, (int)m, (int)n,
+                            batch, eps, st);
     if (rc != OK) return rc;
     have_gram = true;
   } else {
@@ -197,12 +209,17 @@ int muon_b200_ns_run(void* workspace, int batch, int64_t m, int64_t n, int mode,
                           m, m, n, 1.f, 0.f, 1, st);
       if (rc != OK) return rc;
     }
-    // A is exactly symmetric when it comes straight from line 1; after the AOL row
-    // scaling (first iteration) it is not.
-    const int a_symmetric = have_gram ? 0 : 1;
+    if (have_gram) {
+      // First AOL iteration: the operand is A / s (rows scaled, not symmetric, in slot C); the
+      // addend beta * (A / s) is rebuilt per element from the symmetric A and s.
+      rc = launch_ns_gemm(MODE_AXPBY, C, l.ldm, l.a_bs, C, l.ldm, l.a_bs, B, l.ldm, l.a_bs, batch,
+                          m, m, m, c, b, ADD_ROW_SCALED, st, A, partials, l.ldm);
+    } else {
+      // A comes straight from line 1 and is exactly symmetric.
+      rc = launch_ns_gemm(MODE_AXPBY, A, l.ldm, l.a_bs, A, l.ldm, l.a_bs, B, l.ldm, l.a_bs, batch,
+                          m, m, m, c, b, ADD_SYMMETRIC, st);
+    }
     have_gram = false;
-    rc = launch_ns_gemm(MODE_AXPBY, A, l.ldm, l.a_bs, A, l.ldm, l.a_bs, B, l.ldm, l.a_bs, batch, m,
-                        m, m, c, b, a_symmetric, st);
     if (rc != OK) return rc;
     rc = launch_ns_gemm(MODE_BX, B, l.ldm, l.a_bs, X, l.ldn, l.x_bs, C, l.ldn, l.x_bs, batch, m, n,
                         m, a, 0.f, 0, st);

@@ -320,11 +320,16 @@ epilogue_kernel(const EpilogueArgs a) {
 // AOL rescale (reference muon.py:779-785), one CTA per matrix row i:
 //   s_i  = bf16( max( sum_j |A_ij|, eps ) )
 //   X_i: = bf16( X_i: * rsqrt(s_i) )
-//   A_i: = bf16( A_i: / s_i )          (rows only, exactly as the reference does)
+//   A_i: = bf16( A_i: * (1/s_i) )      (rows only, exactly as the reference does; the
+//                                       quotient is formed with the correctly rounded
+//                                       reciprocal so that other kernels can rebuild it)
+// The scaled A goes to A_out (same pitches; may be A itself) so that the symmetric,
+// unscaled A stays available; 1/s goes to svec (one float per row) when given.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads)
-aol_rescale_kernel(__nv_bfloat16* X, long long ldx, long long x_bs, __nv_bfloat16* A, long long lda,
-                   long long a_bs, int m, int n, int batch, float eps) {
+aol_rescale_kernel(__nv_bfloat16* X, long long ldx, long long x_bs, const __nv_bfloat16* A,
+                   __nv_bfloat16* A_out, long long lda, long long a_bs, float* svec, long long s_bs,
+                   int m, int n, int batch, float eps) {
   __shared__ float warp_sums[kThreads / 32];
   __shared__ float s_bcast;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -332,7 +337,8 @@ aol_rescale_kernel(__nv_bfloat16* X, long long ldx, long long x_bs, __nv_bfloat1
   for (long long row = blockIdx.x; row < rows_total; row += gridDim.x) {
     const int b = (int)(row / m);
     const int i = (int)(row - (long long)b * m);
-    __nv_bfloat16* arow = A + (long long)b * a_bs + (long long)i * lda;
+    const __nv_bfloat16* arow = A + (long long)b * a_bs + (long long)i * lda;
+    __nv_bfloat16* orow = A_out + (long long)b * a_bs + (long long)i * lda;
     __nv_bfloat16* xrow = X + (long long)b * x_bs + (long long)i * ldx;
     float acc = 0.f;
     const int mv = m & ~7;
@@ -351,19 +357,21 @@ aol_rescale_kernel(__nv_bfloat16* X, long long ldx, long long x_bs, __nv_bfloat1
       float s = 0.f;
       for (int w = 0; w < kThreads / 32; ++w) s += warp_sums[w];
       s_bcast = bf16_round(fmaxf(s, eps));
+      if (svec) svec[(long long)b * s_bs + i] = __frcp_rn(s_bcast);
     }
     __syncthreads();
     const float s = s_bcast;
     const float rs = rsqrtf(s);
+    const float w = __frcp_rn(s);  // A / s is evaluated as A * (1/s), one rounding each
     for (int j = threadIdx.x * 8; j < mv; j += kThreads * 8) {
       float v[8];
       Vec<__nv_bfloat16>::load(arow + j, v);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) v[k] = __fdiv_rn(v[k], s);
-      Vec<__nv_bfloat16>::store(arow + j, v);
+      for (int k = 0; k < 8; ++k) v[k] *= w;
+      Vec<__nv_bfloat16>::store(orow + j, v);
     }
     for (int j = mv + threadIdx.x; j < m; j += kThreads)
-      arow[j] = __float2bfloat16_rn(__fdiv_rn(__bfloat162float(arow[j]), s));
+      orow[j] = __float2bfloat16_rn(__bfloat162float(arow[j]) * w);
     const int nv = n & ~7;
     for (int j = threadIdx.x * 8; j < nv; j += kThreads * 8) {
       float v[8];
@@ -572,14 +580,15 @@ int launch_epilogue(const EpilogueArgs& a, int dtype, int transpose, cudaStream_
   return OK;
 }
 
-int launch_aol_rescale(__nv_bfloat16* X, long long ldx, long long x_bs, __nv_bfloat16* A,
-                       long long lda, long long a_bs, int m, int n, int batch, float eps,
-                       cudaStream_t stream) {
+int launch_aol_rescale(__nv_bfloat16* X, long long ldx, long long x_bs, const __nv_bfloat16* A,
+                       __nv_bfloat16* A_out, long long lda, long long a_bs, float* svec,
+                       long long s_bs, int m, int n, int batch, float eps, cudaStream_t stream) {
   int grid = grid_for((long long)m * batch, 16);
   if (grid < 0) return ERR_UNSUPPORTED;
   // read + write A (m x m) and X (m x n), bf16
   LaunchScope scope(K_AOL_RESCALE, 4.0 * m * ((double)m + n) * batch, stream);
-  aol_rescale_kernel<<<grid, kThreads, 0, stream>>>(X, ldx, x_bs, A, lda, a_bs, m, n, batch, eps);
+  aol_rescale_kernel<<<grid, kThreads, 0, stream>>>(X, ldx, x_bs, A, A_out, lda, a_bs, svec, s_bs, m, n,
+                                                     batch, eps);
   MB_CUDA_CHECK(cudaGetLastError());
   return OK;
 }

@@ -58,9 +58,9 @@ struct AdamArgs {
 int adam_elems_per_block(int dtype);
 int launch_prologue(const PrologueArgs& a, int dtype, int transpose, cudaStream_t stream);
 int launch_epilogue(const EpilogueArgs& a, int dtype, int transpose, cudaStream_t stream);
-int launch_aol_rescale(__nv_bfloat16* X, long long ldx, long long x_bs, __nv_bfloat16* A,
-                       long long lda, long long a_bs, int m, int n, int batch, float eps,
-                       cudaStream_t stream);
+int launch_aol_rescale(__nv_bfloat16* X, long long ldx, long long x_bs, const __nv_bfloat16* A,
+                       __nv_bfloat16* A_out, long long lda, long long a_bs, float* svec,
+                       long long s_bs, int m, int n, int batch, float eps, cudaStream_t stream);
 int launch_fro_normalize(__nv_bfloat16* X, long long ldx, long long x_bs, int m, int n, int batch,
                          float eps, float* partials, int chunks, cudaStream_t stream);
 int launch_adam(const AdamArgs& a, int dtype, cudaStream_t stream);

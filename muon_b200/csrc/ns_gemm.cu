@@ -403,9 +403,35 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (MODE == MODE_AXPBY) {
           float a[32];
           load_row32(add_row, col0, p.N, a);
-          if (p.sym_add) {
+          if (p.sym_add == ADD_SYMMETRIC) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) f[j] = fmaf(a[j], p.beta, f[j] * p.alpha);
+          } else if (p.sym_add == ADD_ROW_SCALED) {
+            // The addend is S * w (rows scaled by w = 1/s), S symmetric and given unscaled:
+            // position (r, col) takes bf16(S[r,col] * w[r]) and its mirror bf16(S[r,col] * w[col]),
+            // bit for bit what the materialised scaled matrix holds at (r, col) and (col, r).
+            const float* wv = p.row_scale + static_cast<long long>(tc.batch) * p.scale_bs;
+            const float w_r = wv[r];
+            float w_c[32];
+            if (col0 + 32 <= p.N) {
+              const float4* w4 = reinterpret_cast<const float4*>(wv + col0);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float4 q4 = __ldg(w4 + i);
+                w_c[4 * i] = q4.x; w_c[4 * i + 1] = q4.y; w_c[4 * i + 2] = q4.z; w_c[4 * i + 3] = q4.w;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) w_c[j] = (col0 + j < p.N) ? __ldg(wv + col0 + j) : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float prod = f[j] * p.alpha;
+              const float direct = __bfloat162float(__float2bfloat16_rn(a[j] * w_r));
+              const float mirrored = __bfloat162float(__float2bfloat16_rn(a[j] * w_c[j]));
+              f[j] = fmaf(direct, p.beta, prod);
+              mirror[j] = fmaf(mirrored, p.beta, prod);
+            }
           } else {
             // The product alpha*A*A^T is symmetric, the addend beta*A need not be: the
             // mirrored position takes its own addend A[col, r].
@@ -441,7 +467,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           // Mirror: element (r, col) with col < r also lands at (col, r). Lanes hold
           // consecutive r, so each of these stores is a contiguous run across the warp.
           unsigned short* out_s = reinterpret_cast<unsigned short*>(out_b);
-          const bool own_mirror = (MODE == MODE_AXPBY) && !p.sym_add;
+          const bool own_mirror = (MODE == MODE_AXPBY) && p.sym_add != ADD_SYMMETRIC;
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const int col = col0 + j;
@@ -591,8 +617,11 @@ int launch_instance(int dev, int sms, const CUtensorMap& ta, const CUtensorMap& 
   {
     const double m = p.M, n = p.N, k = p.K, b = p.batch;
     const double flops = MODE == MODE_BX ? 2.0 * m * k * n * b : m * (m + 1.0) * k * b;
+    const int64_t tag = ((int64_t)p.M << 40) | ((int64_t)(MODE == MODE_BX ? p.N : p.K) << 16) | ((int64_t)(p.batch & 0xfff) << 4) |
+                        (p.sym_add == ADD_SYMMETRIC ? 1 : 0) | (CTAS == 2 ? 2 : 0) |
+                        (p.sym_add == ADD_ROW_SCALED ? 4 : 0);
     LaunchScope scope(MODE == MODE_SYRK ? K_NS_LINE1 : MODE == MODE_AXPBY ? K_NS_LINE2 : K_NS_LINE3,
-                      flops, stream);
+                      flops, stream, tag);
     MB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, ta, tb, p));
   }
   MB_CUDA_CHECK(cudaGetLastError());
@@ -626,7 +655,8 @@ int device_sm_count(int* sm_count_out) {
 int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs,
                    const __nv_bfloat16* opb, int64_t ldb, int64_t b_bs, __nv_bfloat16* out,
                    int64_t ldo, int64_t out_bs, int batch, int64_t M, int64_t N, int64_t K,
-                   float alpha, float beta, int sym_add, cudaStream_t stream) {
+                   float alpha, float beta, int sym_add, cudaStream_t stream, const __nv_bfloat16* addend,
+                   const float* row_scale, int64_t scale_bs) {
   if (!opa || !opb || !out) return set_error(ERR_INVALID_ARG, "null pointer passed to NS GEMM");
   if (batch < 1 || M < 1 || N < 1 || K < 1)
     return set_error(ERR_INVALID_ARG, "NS GEMM needs batch, M, N, K >= 1 (got %d, %lld, %lld, %lld)",
@@ -668,9 +698,15 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
     for (int i = 0; i < p.tiles_m; ++i) cnt += tri_row_count(i, p.tiles_n, tile_m);
     p.tiles_per_batch = cnt;
     p.sym_add = sym_add;
-    p.add = opa;  // line 2 adds beta * A, where A is the operand itself
+    // Line 2 adds beta * A. Normally A is the operand itself; in row-scaled mode the operand is
+    // the materialised S / s while the addend is rebuilt from the unscaled S and s.
+    p.add = (sym_add == ADD_ROW_SCALED) ? addend : opa;
     p.ldadd = lda;
     p.add_bs = a_bs;
+    p.row_scale = row_scale;
+    p.scale_bs = scale_bs;
+    if (sym_add == ADD_ROW_SCALED && (!addend || !row_scale))
+      return set_error(ERR_INVALID_ARG, "row-scaled line 2 needs the unscaled matrix and the scale vector");
     if (mode == MODE_AXPBY && K != M)
       return set_error(ERR_INVALID_ARG, "line 2 needs a square operand (got %lld x %lld)",
                        (long long)M, (long long)K);

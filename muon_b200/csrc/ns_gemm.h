@@ -13,13 +13,22 @@ enum GemmMode : int {
   MODE_BX = 2,     // out = opA · opB + alpha · opB           (full)
 };
 
+// How line 2 obtains the addend beta * A for the mirrored (upper-triangle) element.
+enum AddendMode : int {
+  ADD_GENERIC = 0,     // A arbitrary: the mirrored element reads A[col, row] from memory
+  ADD_SYMMETRIC = 1,   // A == A^T bit for bit: the finished value is mirrored
+  ADD_ROW_SCALED = 2,  // A = S / s with S symmetric: both addends are rebuilt from S and s
+};
+
 struct GemmParams {
   int M, N, K;  // output rows, output cols, contraction length
   int batch;
   int tiles_m, tiles_n;
   int tiles_per_batch;
   int triangular;
-  int sym_add;  // line 2: the addend is known symmetric, mirror the finished value
+  int sym_add;  // line 2: an AddendMode
+  const float* row_scale;  // ADD_ROW_SCALED: s, one float per matrix row
+  long long scale_bs;      // batch pitch of row_scale in floats
   float alpha, beta;
   __nv_bfloat16* out;
   long long ldo, out_bs;
@@ -32,6 +41,8 @@ int device_sm_count(int* sm_count_out);
 int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs,
                    const __nv_bfloat16* opb, int64_t ldb, int64_t b_bs, __nv_bfloat16* out,
                    int64_t ldo, int64_t out_bs, int batch, int64_t M, int64_t N, int64_t K,
-                   float alpha, float beta, int sym_add, cudaStream_t stream);
+                   float alpha, float beta, int sym_add, cudaStream_t stream,
+                   const __nv_bfloat16* addend = nullptr, const float* row_scale = nullptr,
+                   int64_t scale_bs = 0);
 
 }  // namespace mb

@@ -14,14 +14,15 @@ std::atomic<bool> g_timing{false};
 struct Interval {
   int kind;
   double work;
+  int64_t tag;
   cudaEvent_t start, stop;
 };
 std::vector<Interval> g_intervals;
 std::mutex g_mu;
 }  // namespace
 
-LaunchScope::LaunchScope(int kind, double work, cudaStream_t stream)
-    : kind_(kind), work_(work), stream_(stream) {
+LaunchScope::LaunchScope(int kind, double work, cudaStream_t stream, int64_t tag)
+    : kind_(kind), work_(work), stream_(stream), tag_(tag) {
   g_counts[kind].fetch_add(1, std::memory_order_relaxed);
   if (g_timing.load(std::memory_order_relaxed)) {
     if (cudaEventCreate(&start_) == cudaSuccess) cudaEventRecord(start_, stream_);
@@ -38,7 +39,7 @@ LaunchScope::~LaunchScope() {
   }
   cudaEventRecord(stop, stream_);
   std::lock_guard<std::mutex> lk(g_mu);
-  g_intervals.push_back({kind_, work_, start_, stop});
+  g_intervals.push_back({kind_, work_, tag_, start_, stop});
 }
 
 void timing_enable(bool on) { g_timing.store(on); }
@@ -69,6 +70,34 @@ int timing_collect(double* ms, double* work, int64_t* launches, int n_kinds) {
     cudaEventDestroy(iv.start);
     cudaEventDestroy(iv.stop);
   }
+  return rc;
+}
+
+int timing_collect_records(int max_records, int* kinds, int64_t* tags, double* ms, double* work,
+                           int* n_out) {
+  std::vector<Interval> taken;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    taken.swap(g_intervals);
+  }
+  int n = 0, rc = OK;
+  for (const Interval& iv : taken) {
+    float t = 0.f;
+    cudaError_t e = cudaEventSynchronize(iv.stop);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&t, iv.start, iv.stop);
+    if (e != cudaSuccess && rc == OK)
+      rc = set_error(ERR_CUDA, "timing_collect_records: %s", cudaGetErrorString(e));
+    if (e == cudaSuccess && n < max_records) {
+      kinds[n] = iv.kind;
+      tags[n] = iv.tag;
+      ms[n] = t;
+      work[n] = iv.work;
+      ++n;
+    }
+    cudaEventDestroy(iv.start);
+    cudaEventDestroy(iv.stop);
+  }
+  *n_out = n;
   return rc;
 }
 

@@ -22,19 +22,24 @@ enum KernelKind : int {
 // `stream` (the launching stream), so the interval covers exactly this kernel.
 class LaunchScope {
  public:
-  LaunchScope(int kind, double work, cudaStream_t stream);
+  // `tag` is free-form and only reported back by timing_collect_records.
+  LaunchScope(int kind, double work, cudaStream_t stream, int64_t tag = 0);
   ~LaunchScope();
 
  private:
   int kind_;
   double work_;
   cudaStream_t stream_;
+  int64_t tag_;
   cudaEvent_t start_ = nullptr;
 };
 
 void timing_enable(bool on);
 // Waits for all recorded intervals, adds them up per kind and forgets them.
 int timing_collect(double* ms, double* work, int64_t* launches, int n_kinds);
+// Same, but one entry per launch (in launch order), at most `max_records`.
+int timing_collect_records(int max_records, int* kinds, int64_t* tags, double* ms, double* work,
+                           int* n_out);
 void launch_counts(int64_t* counts, int n_kinds);
 
 }  // namespace mb

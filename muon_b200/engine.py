@@ -107,6 +107,34 @@ def batch_size_for(m: int, n: int, count: int, workspace_cap_bytes: int) -> int:
     return max(1, min(count, want, fit))
 
 
+def plan_launches(m: int, n: int, count: int, workspace_cap_bytes: int, sm_pairs: int = 74) -> list[int]:
+    """Split `count` same-shape matrices into grouped launches.
+
+    Every launch of the triangular products ends with a partly filled wave of the `sm_pairs`
+    CTA pairs, so the cost of a split is the sum over launches of ceil(units / sm_pairs) waves
+    (+ a small per-launch charge). Among balanced splits that fit the workspace cap and do not
+    exceed twice the default batch size (launches stay fine-grained enough to overlap the
+    exchange in the distributed step), the cheapest one is returned."""
+    if count <= 0:
+        return []
+    units = max(1, tri_tiles(m))
+    want = batch_size_for(m, n, count, workspace_cap_bytes)
+    per_matrix = 2 * (2 * m * ((n + 7) // 8 * 8) + 2 * m * ((m + 7) // 8 * 8)) + 2048
+    max_b = max(1, min(count, 2 * want, workspace_cap_bytes // per_matrix))
+    best, best_cost = None, None
+    for launches in range(-(-count // max_b), count + 1):
+        bounds = [round(i * count / launches) for i in range(launches + 1)]
+        sizes = [e - s for s, e in zip(bounds[:-1], bounds[1:])]
+        if max(sizes) > max_b:
+            continue
+        cost = sum(-(-(units * b) // sm_pairs) for b in sizes) + 0.25 * launches
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = sizes, cost
+        if launches >= -(-count // max(1, want // 2)):
+            break
+    return best
+
+
 class CudaBackend:
     """Calls the sm_100a library. One instance per process; workspaces cached per device."""
 
@@ -127,6 +155,10 @@ class CudaBackend:
             buf = torch.empty(nbytes + 256, dtype=torch.uint8, device=device)
             self._workspaces[key] = buf
         return buf
+
+    @staticmethod
+    def _sm_pairs(device: torch.device) -> int:
+        return max(1, torch.cuda.get_device_properties(device).multi_processor_count // 2)
 
     @staticmethod
     def _aligned_ptr(buf: Tensor) -> int:
@@ -152,12 +184,14 @@ class CudaBackend:
         scale = aspect_scale(p0.shape)
         mode, steps = _ns_mode, _ns_steps
         eps = 1e-7
-        bsz = batch_size_for(m_, n_, len(params), self.workspace_cap_bytes)
+        sizes = plan_launches(m_, n_, len(params), self.workspace_cap_bytes, self._sm_pairs(p0.device))
+        bounds = [0]
+        for b in sizes:
+            bounds.append(bounds[-1] + b)
         dev = p0.device
         with torch.cuda.device(dev):
             stream = _stream_ptr(dev)
-            for s in range(0, len(params), bsz):
-                e = min(s + bsz, len(params))
+            for s, e in zip(bounds[:-1], bounds[1:]):
                 layout = _lib.ns_layout(e - s, m_, n_)
                 ws = self.workspace(dev, layout.total_bytes)
                 check(lib.muon_b200_muon_step(

@@ -18,7 +18,7 @@ from collections import OrderedDict
 import torch
 import torch.distributed as dist
 
-from .engine import batch_size_for, get_backend, view_2d
+from .engine import get_backend, plan_launches, view_2d
 
 
 def _ensure_grad_and_state(optimizer, p) -> None:
@@ -96,14 +96,14 @@ def _distributed_muon_group_step(optimizer, group) -> None:
             # owns in the following windows (one grouped launch sequence).
             p0 = params[mine]
             rows, cols = view_2d(p0.shape)
-            limit = batch_size_for(min(rows, cols), max(rows, cols), len(owned) - done_upto,
-                                   getattr(backend, "workspace_cap_bytes", 4 << 30))
-            chunk = []
-            for idx in owned[done_upto:done_upto + limit]:
-                q = params[idx]
-                if q.shape != p0.shape or q.dtype != p0.dtype:
+            run = 0  # same-shape parameters this rank owns from here on
+            for idx in owned[done_upto:]:
+                if params[idx].shape != p0.shape or params[idx].dtype != p0.dtype:
                     break
-                chunk.append(q)
+                run += 1
+            limit = plan_launches(min(rows, cols), max(rows, cols), run,
+                                  getattr(backend, "workspace_cap_bytes", 4 << 30))[0]
+            chunk = [params[idx] for idx in owned[done_upto:done_upto + limit]]
             _muon_update_params(optimizer, chunk, group)
             done_upto += len(chunk)
         if world > 1:  # with one rank the gather would copy each parameter onto itself

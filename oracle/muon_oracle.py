@@ -120,7 +120,10 @@ def zeropower_via_newtonschulz5(G: Tensor, epsilon: float = 1e-7, *, mirror: str
     A = ns_line_1(X, mirror=m1)  # :778
     s = torch.clamp_min(A.float().abs().sum(dim=-1, keepdim=True), epsilon).to(dtype)  # :779-781
     X = (X.float() * torch.rsqrt(s.float())).to(dtype)  # :782
-    A = (A.float() / s.float()).to(dtype)  # :785 (rows only)
+    # :785 (rows only). The quotient is formed as A * (1/s) with a correctly rounded reciprocal:
+    # the reference's compiled division is itself approximate, and this form is the one the
+    # CUDA kernels can reproduce bit for bit in two places.
+    A = (A.float() * (1.0 / s.float())).to(dtype)
     for k, (a, b, c) in enumerate(AOL4_COEFFS):
         if k > 0:
             A = ns_line_1(X, mirror=m1)  # :792
