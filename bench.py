@@ -153,7 +153,13 @@ def run_ours(args):
     if not dist.is_initialized():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29531")
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+        import datetime
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device,
+                                timeout=datetime.timedelta(seconds=120))
+
+    comm_sms = int(os.environ.get("MUON_B200_COMM_SMS", "0"))
+    if world > 1 and comm_sms > 0:
+        _lib.check(_lib.lib.muon_b200_set_reserved_sms(comm_sms))
 
     shapes, dtype, grad_std, desc = WORKLOADS[args.workload]
     params = make_problem(shapes, dtype, grad_std, device, rank, world)

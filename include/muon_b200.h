@@ -58,6 +58,13 @@ const char* muon_b200_last_error(void);
  * is cleared afterwards. Returns MUON_B200_ERR_DEVICE_TIMEOUT when the word is set. */
 int muon_b200_device_status(int* status_out, int reset);
 
+/* The Newton-Schulz GEMMs run as persistent grids that fill the device. A caller that runs
+ * other kernels concurrently on another stream (the copy kernels of a collective that overlaps
+ * the step) can ask the grids to leave n SMs free. Process-wide, default 0. No counterpart in
+ * the reference. */
+int muon_b200_set_reserved_sms(int n);
+int muon_b200_get_reserved_sms(void);
+
 /* ---- Accounting and per-kernel timing -----------------------------------------------
  * Kernel kinds, in the order of every array below:
  *   0 NS line 1, 1 NS line 2, 2 NS line 3 (work unit: algorithmic FLOPs, symmetric products

@@ -43,6 +43,8 @@ PROTOTYPES = {
     "muon_b200_version": (c_int, []),
     "muon_b200_last_error": (c_char_p, []),
     "muon_b200_device_status": (c_int, [POINTER(c_int), c_int]),
+    "muon_b200_set_reserved_sms": (c_int, [c_int]),
+    "muon_b200_get_reserved_sms": (c_int, []),
     "muon_b200_kernel_kinds": (c_int, []),
     "muon_b200_launch_counts": (c_int, [POINTER(c_int64), c_int]),
     "muon_b200_timing_enable": (c_int, [c_int]),

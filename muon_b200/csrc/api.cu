@@ -82,6 +82,14 @@ int muon_b200_device_status(int* status_out, int reset) {
   return OK;
 }
 
+int muon_b200_set_reserved_sms(int n) {
+  if (n < 0) return set_error(ERR_INVALID_ARG, "reserved SM count must be >= 0");
+  set_reserved_sms(n);
+  return OK;
+}
+
+int muon_b200_get_reserved_sms(void) { return get_reserved_sms(); }
+
 int muon_b200_kernel_kinds(void) { return K_KIND_COUNT; }
 
 int muon_b200_launch_counts(int64_t* counts, int n_kinds) {

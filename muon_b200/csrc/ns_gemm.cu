@@ -31,6 +31,7 @@
 #include "profiling.h"
 
 #include <cuda.h>
+#include <atomic>
 #include <cstdlib>
 #include <mutex>
 
@@ -572,6 +573,10 @@ int forced_ctas() {
   return v;
 }
 
+// SMs the persistent GEMM grids leave free, for kernels of other streams that must make
+// progress while a GEMM runs (a collective's copy kernels in the distributed step).
+std::atomic<int> g_reserved_sms{0};
+
 template <int MODE, bool B_MN, int CTAS>
 int launch_instance(int dev, int sms, const CUtensorMap& ta, const CUtensorMap& tb,
                     const GemmParams& p, cudaStream_t stream) {
@@ -612,6 +617,11 @@ int launch_instance(int dev, int sms, const CUtensorMap& ta, const CUtensorMap& 
     }
     max_units = CTAS == 2 ? g_dev[dev].max_clusters[slot] : sms;
   }
+  const int reserved = g_reserved_sms.load(std::memory_order_relaxed);
+  if (reserved > 0) {
+    max_units -= (reserved + CTAS - 1) / CTAS;
+    if (max_units < 1) max_units = 1;
+  }
   const int units = (int)(total < max_units ? total : max_units);
   cfg.gridDim = dim3(units * CTAS);
   {
@@ -629,6 +639,9 @@ int launch_instance(int dev, int sms, const CUtensorMap& ta, const CUtensorMap& 
 }
 
 }  // namespace
+
+void set_reserved_sms(int n) { g_reserved_sms.store(n < 0 ? 0 : n); }
+int get_reserved_sms() { return g_reserved_sms.load(); }
 
 int device_sm_count(int* sm_count_out) {
   int dev = 0;

@@ -37,6 +37,8 @@ struct GemmParams {
 };
 
 int device_sm_count(int* sm_count_out);
+void set_reserved_sms(int n);
+int get_reserved_sms();
 
 int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs,
                    const __nv_bfloat16* opb, int64_t ldb, int64_t b_bs, __nv_bfloat16* out,

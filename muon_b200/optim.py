@@ -19,6 +19,7 @@ import torch
 import torch.distributed as dist
 
 from .engine import get_backend, plan_launches, view_2d
+from .exchange import get_peer_push
 
 
 def _ensure_grad_and_state(optimizer, p) -> None:
@@ -78,6 +79,21 @@ def _adam_update_params(optimizer, group) -> None:
                           group["lr"], group["weight_decay"], group["betas"], group["eps"])
 
 
+def _next_chunk(params, owned, done_upto, backend):
+    """The next parameters this rank updates in one grouped launch sequence: the same-shape run
+    starting at owned[done_upto], cut to the first launch the planner proposes."""
+    p0 = params[owned[done_upto]]
+    rows, cols = view_2d(p0.shape)
+    run = 0
+    for idx in owned[done_upto:]:
+        if params[idx].shape != p0.shape or params[idx].dtype != p0.dtype:
+            break
+        run += 1
+    limit = plan_launches(min(rows, cols), max(rows, cols), run,
+                          getattr(backend, "workspace_cap_bytes", 4 << 30))[0]
+    return [params[idx] for idx in owned[done_upto:done_upto + limit]]
+
+
 def _distributed_muon_group_step(optimizer, group) -> None:
     """Windowed round-robin of muon.py:54-68. Window k holds params[kW:(k+1)W]; rank r
     updates params[kW + r] and every rank then receives the whole window."""
@@ -89,21 +105,23 @@ def _distributed_muon_group_step(optimizer, group) -> None:
     owned = list(range(rank, len(params), world))
     done_upto = 0  # owned[:done_upto] have been updated
     pending = []
+    push = get_peer_push(optimizer, group) if world > 1 else None
+    if push is not None:
+        # Copy-engine exchange: same ownership and update order, pushes instead of gathers.
+        push.begin_step()
+        while done_upto < len(owned):
+            chunk = _next_chunk(params, owned, done_upto, backend)
+            _muon_update_params(optimizer, chunk, group)
+            push.push(chunk)
+            done_upto += len(chunk)
+        push.end_step()
+        return
     for base_i in range(0, len(params), world):
         mine = base_i + rank
         if mine < len(params) and done_upto < len(owned) and owned[done_upto] == mine:
             # Update this window's parameter together with the same-shape ones this rank
             # owns in the following windows (one grouped launch sequence).
-            p0 = params[mine]
-            rows, cols = view_2d(p0.shape)
-            run = 0  # same-shape parameters this rank owns from here on
-            for idx in owned[done_upto:]:
-                if params[idx].shape != p0.shape or params[idx].dtype != p0.dtype:
-                    break
-                run += 1
-            limit = plan_launches(min(rows, cols), max(rows, cols), run,
-                                  getattr(backend, "workspace_cap_bytes", 4 << 30))[0]
-            chunk = [params[idx] for idx in owned[done_upto:done_upto + limit]]
+            chunk = _next_chunk(params, owned, done_upto, backend)
             _muon_update_params(optimizer, chunk, group)
             done_upto += len(chunk)
         if world > 1:  # with one rank the gather would copy each parameter onto itself

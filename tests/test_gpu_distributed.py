@@ -1,0 +1,71 @@
+"""Multi-GPU test of the distributed step (needs >= 2 GPUs; skipped otherwise): after `Muon.step`
+every rank holds every updated parameter, bit-identical to what `SingleDeviceMuon` produces on one
+GPU with the same kernels, for both exchange transports (copy-engine pushes, NCCL all_gather)."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")]
+
+SHAPES = [(512, 1024)] * 6 + [(1024, 512)] * 4 + [(256, 256)] * 5 + [(64, 32, 3, 3)] * 3
+
+
+def _problem(steps=2):
+    g = torch.Generator().manual_seed(5)
+    p0 = [torch.randn(s, generator=g) * 0.02 for s in SHAPES]
+    grads = [[torch.randn(s, generator=g) for s in SHAPES] for _ in range(steps)]
+    return p0, grads
+
+
+def _worker(rank, world, tmpdir, exchange, dtype):
+    import datetime
+    os.environ["MUON_B200_EXCHANGE"] = exchange
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", init_method=f"file://{tmpdir}/pg_{exchange}", rank=rank,
+                            world_size=world, timeout=datetime.timedelta(seconds=60))
+    try:
+        import muon_b200 as mb
+        dev = torch.device("cuda", rank)
+        p0, grads = _problem()
+        params = [torch.nn.Parameter(p.to(dtype).to(dev)) for p in p0]
+        opt = mb.Muon(list(params), lr=0.02, weight_decay=0.01)
+        for step_grads in grads:
+            for p, gr in zip(params, step_grads):
+                p.grad = gr.to(dtype).to(dev)
+            opt.step()
+        torch.cuda.synchronize()
+        used_ce = any(v is not None for v in opt.__dict__.get("_muon_b200_exchange", {}).values())
+        owned = [i for i, p in enumerate(opt.param_groups[0]["params"]) if len(opt.state[p]) > 0]
+        torch.save(dict(params=[p.detach().cpu() for p in params], used_ce=used_ce, owned=owned,
+                        status=mb.device_status()), f"{tmpdir}/out_{exchange}_{rank}.pt")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("exchange", ["ce", "nccl"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16])
+def test_distributed_step_matches_single_device(tmp_path, exchange, dtype):
+    world = min(torch.cuda.device_count(), 4)
+    mp.spawn(_worker, args=(world, str(tmp_path), exchange, dtype), nprocs=world, join=True)
+    outs = [torch.load(f"{tmp_path}/out_{exchange}_{r}.pt", weights_only=False) for r in range(world)]
+
+    import muon_b200 as mb
+    p0, grads = _problem()
+    ref = [torch.nn.Parameter(p.to(dtype).cuda()) for p in p0]
+    opt = mb.SingleDeviceMuon(ref, lr=0.02, weight_decay=0.01)
+    for step_grads in grads:
+        for p, gr in zip(ref, step_grads):
+            p.grad = gr.to(dtype).cuda()
+        opt.step()
+    ref = [p.detach().cpu() for p in ref]
+
+    for r, o in enumerate(outs):
+        assert o["status"] == 0
+        assert o["used_ce"] == (exchange == "ce")
+        assert o["owned"] == list(range(r, len(SHAPES), world))
+        for i, (p, q) in enumerate(zip(o["params"], ref)):
+            assert torch.equal(p, q), f"rank {r}, parameter {i} {tuple(q.shape)} ({exchange})"
