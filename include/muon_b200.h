@@ -65,6 +65,25 @@ int muon_b200_device_status(int* status_out, int reset);
 int muon_b200_set_reserved_sms(int n);
 int muon_b200_get_reserved_sms(void);
 
+/* ---- Peer memory for the distributed step's exchange ---------------------------------
+ * These four are the exceptions to "never allocates, never maps": they create and remove
+ * address-space mappings of OTHER processes' device memory. They have no counterpart in the
+ * reference, whose exchange is dist.all_gather (muon.py:68). */
+
+/* Exports the cudaMalloc allocation that contains ptr: writes the 64-byte CUDA IPC handle, the
+ * offset of ptr inside that allocation and (optionally) the allocation's size. */
+int muon_b200_ipc_export(const void* ptr, void* handle64, int64_t* offset_out,
+                         int64_t* alloc_bytes_out);
+/* Maps a peer process's allocation on the CURRENT device with peer access enabled and returns
+ * its base address. A process must open a given handle only once (cache by the 64 bytes). */
+int muon_b200_ipc_open(const void* handle64, void** base_out);
+int muon_b200_ipc_close(void* base);
+/* Enqueues n device-to-device copies of `bytes` bytes from src to dst[0..n) on `stream`. With
+ * destinations obtained from muon_b200_ipc_open these are copy-engine transfers over NVLink
+ * and occupy no SM. */
+int muon_b200_push_copies(void* const* dst, int n, const void* src, int64_t bytes,
+                          muon_b200_stream_t stream);
+
 /* ---- Accounting and per-kernel timing -----------------------------------------------
  * Kernel kinds, in the order of every array below:
  *   0 NS line 1, 1 NS line 2, 2 NS line 3 (work unit: algorithmic FLOPs, symmetric products

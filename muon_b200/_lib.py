@@ -45,6 +45,10 @@ PROTOTYPES = {
     "muon_b200_device_status": (c_int, [POINTER(c_int), c_int]),
     "muon_b200_set_reserved_sms": (c_int, [c_int]),
     "muon_b200_get_reserved_sms": (c_int, []),
+    "muon_b200_ipc_export": (c_int, [c_void_p, c_void_p, POINTER(c_int64), POINTER(c_int64)]),
+    "muon_b200_ipc_open": (c_int, [c_void_p, POINTER(c_void_p)]),
+    "muon_b200_ipc_close": (c_int, [c_void_p]),
+    "muon_b200_push_copies": (c_int, [POINTER(c_void_p), c_int, c_void_p, c_int64, c_void_p]),
     "muon_b200_kernel_kinds": (c_int, []),
     "muon_b200_launch_counts": (c_int, [POINTER(c_int64), c_int]),
     "muon_b200_timing_enable": (c_int, [c_int]),

@@ -5,81 +5,108 @@ The reference ends every window with ``dist.all_gather`` of the freshly updated 
 
 ``nccl``  the same ``dist.all_gather`` call, issued asynchronously. NCCL moves the data with
           copy kernels that need SMs; the Newton-Schulz GEMMs are persistent grids that fill
-          the device, so the two compete and little of the transfer is hidden.
+          the device, so the two compete and only part of the transfer is hidden.
 
-``ce``    every rank maps the other ranks' parameter tensors into its address space (CUDA IPC,
-          through ``torch.multiprocessing.reductions``) and, as soon as one of its own
-          parameters is updated, pushes it to the seven peers with device-to-device copies on
-          a side stream. Those copies run on the GPU's copy engines over NVLink and take no SM,
-          so they overlap the remaining Newton-Schulz work. Two tiny NCCL all-reduces bracket
-          the step: the first makes sure every rank has reached ``step()`` (and, in stream
-          order, finished whatever read the parameters before) before any push lands in its
-          memory; the second returns only after every rank's pushes have completed, which gives
-          ``step()`` the reference's post-condition that all ranks hold all updated parameters.
+``ce``    every rank maps the other ranks' parameter allocations on its own device (CUDA IPC
+          handles opened with peer access, ``muon_b200_ipc_export`` / ``muon_b200_ipc_open``)
+          and, as soon as some of its own parameters are updated, pushes them to the peers
+          with device-to-device copies on a side stream (``muon_b200_push_copies``). Those
+          copies run on the copy engines over NVLink and take no SM, so they overlap the
+          remaining Newton-Schulz work. Two tiny NCCL all-reduces bracket the step: the first
+          makes sure every rank has reached ``step()`` (and, in stream order, finished whatever
+          read the parameters before) before any push lands in its memory; the second returns
+          only after every rank's pushes have completed, which gives ``step()`` the reference's
+          post-condition that all ranks hold all updated parameters.
 
-``MUON_B200_EXCHANGE`` selects ``nccl`` (default), ``ce``, or ``auto`` (``ce`` when every rank
-can map its peers, else ``nccl``). CPU tensors (the gloo test ranks) always use ``all_gather``.
-
-Status of ``ce``: functionally verified (tests/test_gpu_distributed.py) but not the default.
-Tensors imported through ``torch.multiprocessing.reductions`` are mapped in a context of the
-*peer's* device; a copy into them from this rank's device is not a direct NVLink transfer
-(measured 35 GB/s on B200 against 730 GB/s for a copy between two devices of one process), so
-this transport is currently slower than NCCL. Mapping the peers with the IPC handle opened on
-this rank's own device is what makes it a copy-engine NVLink push.
+``MUON_B200_EXCHANGE`` selects ``nccl``, ``ce``, or ``auto`` (``ce`` when every rank can map
+its peers, else ``nccl``). CPU tensors (the gloo test ranks) always use ``all_gather``.
+The ``ce`` transport needs parameters that live in plain ``cudaMalloc`` blocks (PyTorch's
+default allocator without expandable segments) and stay allocated while the optimizer lives.
 """
 from __future__ import annotations
 
+import ctypes
 import os
 
 import torch
 import torch.distributed as dist
 
+DEFAULT_MODE = "auto"
+
 
 def _mode() -> str:
-    m = os.environ.get("MUON_B200_EXCHANGE", "nccl").lower()
+    m = os.environ.get("MUON_B200_EXCHANGE", DEFAULT_MODE).lower()
     if m not in ("auto", "ce", "nccl"):
         raise ValueError(f"MUON_B200_EXCHANGE must be auto, ce or nccl, got {m!r}")
     return m
 
 
 class PeerPush:
-    """Peer-mapped views of one param group's tensors on every other rank + a copy stream."""
+    """Addresses of one param group's tensors in every other rank's memory + a copy stream."""
 
     def __init__(self, params):
-        from torch.multiprocessing.reductions import reduce_tensor
+        from ._lib import lib
 
         self.world, self.rank = dist.get_world_size(), dist.get_rank()
         self.device = params[0].device
-        exported, error = None, None
-        try:
-            exported = [reduce_tensor(p.detach()) for p in params]
-        except Exception as e:  # e.g. allocator backends whose blocks cannot be shared
-            error = repr(e)
+        exported, errors = [], []
+        with torch.cuda.device(self.device):
+            for p in params:
+                handle = ctypes.create_string_buffer(64)
+                off = ctypes.c_int64(0)
+                rc = lib.muon_b200_ipc_export(p.data_ptr(), handle, ctypes.byref(off), None)
+                if rc != 0 or not p.is_contiguous():
+                    errors.append(lib.muon_b200_last_error().decode() if rc else "non-contiguous parameter")
+                    break
+                exported.append((handle.raw, off.value, p.numel() * p.element_size()))
         gathered = [None] * self.world
-        dist.all_gather_object(gathered, (exported, error))
-        errors = [g[1] for g in gathered if g[1] is not None]
-        self.views = None
+        dist.all_gather_object(gathered, (exported, errors))
+        errors = [e for g in gathered for e in g[1]]
+        self.ptrs = None  # ptrs[r][i]: address of parameter i in rank r's memory, mapped here
+        self._opened = {}
         if not errors:
             try:
-                self.views = []
-                for r, (items, _) in enumerate(gathered):
-                    if r == self.rank:
-                        self.views.append(None)
-                        continue
-                    self.views.append([fn(*args) for fn, args in items])
-            except Exception as e:
-                errors.append(repr(e))
-                self.views = None
+                with torch.cuda.device(self.device):
+                    self.ptrs = [self._map(items) if r != self.rank else None
+                                 for r, (items, _) in enumerate(gathered)]
+            except RuntimeError as e:
+                errors.append(str(e))
+                self.ptrs = None
         ok = [None] * self.world
-        dist.all_gather_object(ok, self.views is not None)
+        dist.all_gather_object(ok, self.ptrs is not None)
         self.ok = all(ok)
         self.error = "; ".join(errors) if errors else (None if self.ok else "a peer could not map this rank")
         if not self.ok:
-            self.views = None
+            self.close()
             return
+        self.nbytes = [e[2] for e in exported]
         self.stream = torch.cuda.Stream(device=self.device)
         self._token = torch.zeros(1, device=self.device)
         self.index = {id(p): i for i, p in enumerate(params)}
+        # Rank r serves its peers in the order r+1, r+2, ...: at any moment every receiver is
+        # the target of one sender instead of all ranks converging on the same GPU's ingress.
+        self.peers = [(self.rank + k) % self.world for k in range(1, self.world)]
+
+    def _map(self, items):
+        from ._lib import lib
+        out = []
+        for handle, offset, _ in items:
+            base = self._opened.get(handle)
+            if base is None:
+                ptr = ctypes.c_void_p(0)
+                rc = lib.muon_b200_ipc_open(handle, ctypes.byref(ptr))
+                if rc != 0:
+                    raise RuntimeError(lib.muon_b200_last_error().decode())
+                base = self._opened[handle] = ptr.value
+            out.append(base + offset)
+        return out
+
+    def close(self) -> None:
+        from ._lib import lib
+        for base in self._opened.values():
+            lib.muon_b200_ipc_close(base)
+        self._opened = {}
+        self.ptrs = None
 
     def begin_step(self) -> None:
         """All ranks are inside step() (stream-ordered after their earlier work) from here on."""
@@ -87,16 +114,16 @@ class PeerPush:
 
     def push(self, updated) -> None:
         """Copy each freshly updated local parameter into every peer's copy of it."""
+        from ._lib import check, lib, ptr_array
         ready = torch.cuda.Event()
         ready.record(torch.cuda.current_stream(self.device))
         self.stream.wait_event(ready)
-        with torch.cuda.stream(self.stream):
+        with torch.cuda.device(self.device):
             for p in updated:
                 i = self.index[id(p)]
-                src = p.detach()
-                for r in range(self.world):
-                    if r != self.rank:
-                        self.views[r][i].copy_(src, non_blocking=True)
+                check(lib.muon_b200_push_copies(ptr_array([self.ptrs[r][i] for r in self.peers]),
+                                                len(self.peers), p.data_ptr(), self.nbytes[i],
+                                                self.stream.cuda_stream))
 
     def end_step(self) -> None:
         """Returns (in stream order) once every rank's pushes have landed."""
