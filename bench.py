@@ -48,6 +48,10 @@ WORKLOADS = {
                           "GPT-2 small hidden weights, 72 matrices, fp32"),
 }
 NS_ITERS = 4  # the reference's live algorithm
+# DRAM bytes (read + write) per matrix element that one launch of the line-3 kernel moved in the
+# ncu capture summarised in profiles/ns_gemm_line3_llama3-8b-4layers.md: 3.723 GB for 8 matrices
+# of 4096 x 14336. Traffic of that kernel grows with the elements a launch covers.
+LINE3_DRAM_BYTES_PER_ELEMENT = 3.723e9 / (8 * 4096 * 14336)
 
 
 def ns_flops(shapes, iters=NS_ITERS):
@@ -262,7 +266,12 @@ def run_ours(args):
                          "peak_kind": f"{peaks['source']} bf16 GEMM, sustained (kernel timed inside a long step); "
                                       f"burst figure is {peaks['tflops_burst']}",
                          "launches": int(n3), "avg_launch_ms": ms3 / n3 if n3 else None,
-                         "traffic": None, "rank": 0},
+                         # average DRAM bytes per launch, scaled from the ncu capture by elements covered
+                         "traffic": (LINE3_DRAM_BYTES_PER_ELEMENT * sum(r * c for r, c in shapes) * NS_ITERS
+                                     / world / (n3 / args.steps)) if n3 and args.workload.startswith("llama3") else None,
+                         "traffic_algorithmic": ((2 * sum(r * c for r, c in shapes) + sum(min(r, c) ** 2 for r, c in shapes))
+                                                 * 2 * NS_ITERS / world / (n3 / args.steps)) if n3 else None,
+                         "rank": 0},
             "kernels": kernels,
             "clocks": clocks.summary(),
             "device_status": status,
