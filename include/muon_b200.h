@@ -151,6 +151,31 @@ int muon_b200_ns_workspace_layout(int batch, int64_t m, int64_t n, muon_b200_ns_
 int muon_b200_ns_run(void* workspace, int batch, int64_t m, int64_t n, int mode, int steps,
                      const float* coeffs, float eps, int* result_slot, muon_b200_stream_t stream);
 
+/* Newton-Schulz for callers that cannot allocate device memory: hosts whose allocator is
+ * frozen while the step runs (memory-planned graphs, fixed-budget real-time loops) and
+ * plugins that are handed buffers and nothing else. Same computation as muon_b200_ns_run, but
+ * the scratch (ping-pong copy of X, Gram matrix, its row-scaled copy, B, row scales) is a
+ * 64 MiB array built into the library instead of a caller workspace. This entry point has no
+ * counterpart in the reference.
+ *   x    bf16 [batch, m, n], m <= n, pitch ldx, batch pitch x_bs (elements); not modified.
+ *   out  bf16 [batch, m, n], pitch ldo, batch pitch o_bs; receives the result; must not alias x.
+ * Pointers 16-byte aligned, pitches multiples of 8 and >= n. Other arguments as muon_b200_ns_run.
+ * Limits and caveats:
+ *   - every GPU on which the library is loaded holds the 64 MiB until the process exits;
+ *   - a problem needing more than muon_b200_ns_static_scratch_bytes() is rejected with
+ *     MUON_B200_ERR_UNSUPPORTED (muon_b200_ns_static_required_bytes tells how much it needs);
+ *   - all calls share the one array and it keeps the previous call's contents (nothing in it
+ *     has to start at zero: every part is written before it is read), so two calls that overlap
+ *     on a GPU, from any streams or threads, race: serialise them;
+ *   - the first call on a device looks up the array's device address; make that call before
+ *     starting any stream capture.
+ * Calls no cudaMalloc/cudaFree or other allocating routine. */
+int muon_b200_ns_run_static(const void* x, int64_t ldx, int64_t x_bs, void* out, int64_t ldo,
+                            int64_t o_bs, int batch, int64_t m, int64_t n, int mode, int steps,
+                            const float* coeffs, float eps, muon_b200_stream_t stream);
+int64_t muon_b200_ns_static_scratch_bytes(void);
+int64_t muon_b200_ns_static_required_bytes(int batch, int64_t m, int64_t n);
+
 /* ---- Elementwise stages, multi-tensor ------------------------------------------------
  * `count` tensors of identical shape rows x cols (a 4-D conv filter is passed as
  * rows = size(0), cols = numel / size(0), muon.py:11-12) and identical dtype. */

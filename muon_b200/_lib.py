@@ -45,6 +45,11 @@ PROTOTYPES = {
     "muon_b200_device_status": (c_int, [POINTER(c_int), c_int]),
     "muon_b200_set_reserved_sms": (c_int, [c_int]),
     "muon_b200_get_reserved_sms": (c_int, []),
+    "muon_b200_ns_run_static": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int,
+                                        c_int64, c_int64, c_int, c_int, POINTER(c_float), c_float,
+                                        c_void_p]),
+    "muon_b200_ns_static_scratch_bytes": (c_int64, []),
+    "muon_b200_ns_static_required_bytes": (c_int64, [c_int, c_int64, c_int64]),
     "muon_b200_ipc_export": (c_int, [c_void_p, c_void_p, POINTER(c_int64), POINTER(c_int64)]),
     "muon_b200_ipc_open": (c_int, [c_void_p, POINTER(c_void_p)]),
     "muon_b200_ipc_close": (c_int, [c_void_p]),
