@@ -64,6 +64,17 @@ template <>
 __device__ __forceinline__ float round_to<__nv_bfloat16>(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
 }
+// Same for two values at once: for bf16 one packed conversion instead of two scalar ones.
+template <typename T>
+__device__ __forceinline__ void round_pair_to(float& a, float& b);
+template <>
+__device__ __forceinline__ void round_pair_to<float>(float&, float&) {}
+template <>
+__device__ __forceinline__ void round_pair_to<__nv_bfloat16>(float& a, float& b) {
+  const uint32_t w = pack_bf16x2(a, b);
+  a = bf16_bits_to_float(w & 0xffffu);
+  b = bf16_bits_to_float(w >> 16);
+}
 template <typename T>
 __device__ __forceinline__ T from_f(float v);
 template <>
@@ -139,15 +150,23 @@ prologue_kernel(const PrologueArgs a) {
             mv[j] = in ? to_f<T>(m[off + j]) : 0.f;
           }
         }
+        // Two elements at a time: rounding to bf16 is one packed conversion per pair.
 #pragma unroll
-        for (int j = 0; j < V; ++j) {
-          mv[j] = round_to<T>(torch_lerp(mv[j], gv[j], w1));
+        for (int j = 0; j < V; j += 2) {
+          mv[j] = torch_lerp(mv[j], gv[j], w1);
+          mv[j + 1] = torch_lerp(mv[j + 1], gv[j + 1], w1);
+          round_pair_to<T>(mv[j], mv[j + 1]);
           if (a.nesterov) {
-            gv[j] = round_to<T>(torch_lerp(gv[j], mv[j], w2));
-            xv[j] = bf16_round(gv[j]);
+            gv[j] = torch_lerp(gv[j], mv[j], w2);
+            gv[j + 1] = torch_lerp(gv[j + 1], mv[j + 1], w2);
+            round_pair_to<T>(gv[j], gv[j + 1]);
+            xv[j] = gv[j];
+            xv[j + 1] = gv[j + 1];
           } else {
-            xv[j] = bf16_round(mv[j]);
+            xv[j] = mv[j];
+            xv[j + 1] = mv[j + 1];
           }
+          if (sizeof(T) == 4) round_pair_to<__nv_bfloat16>(xv[j], xv[j + 1]);  // fp32 state -> bf16 X
         }
         if (full) {
           Vec<T>::store(m + off, mv);
@@ -298,10 +317,14 @@ epilogue_kernel(const EpilogueArgs a) {
           }
         }
 #pragma unroll
-        for (int j = 0; j < V; ++j) {
-          const float us = bf16_round(uv[j] * a.scale);
-          const float p1 = round_to<T>(pv[j] * a.decay);
-          pv[j] = round_to<T>(fmaf(a.neg_lr, us, p1));
+        for (int j = 0; j < V; j += 2) {
+          float u0 = uv[j] * a.scale, u1 = uv[j + 1] * a.scale;
+          round_pair_to<__nv_bfloat16>(u0, u1);
+          float p0 = pv[j] * a.decay, p1 = pv[j + 1] * a.decay;
+          round_pair_to<T>(p0, p1);
+          pv[j] = fmaf(a.neg_lr, u0, p0);
+          pv[j + 1] = fmaf(a.neg_lr, u1, p1);
+          round_pair_to<T>(pv[j], pv[j + 1]);
         }
         if (full) {
           Vec<T>::store(p + off, pv);

@@ -2,12 +2,15 @@
 :705, :749), executed by the sm_100a library."""
 from __future__ import annotations
 
+import ctypes
+
 import torch
 from torch import Tensor
 
 from . import _lib
 from ._lib import check, lib
-from .engine import _require_cuda, _stream_ptr, aspect_scale, get_backend
+from .engine import (_NS_MODES, _require_cuda, _stream_ptr, aspect_scale, dtype_code, get_backend,
+                     get_ns_mode, view_2d)
 
 
 def _as_bf16_3d(t: Tensor, name: str) -> tuple[Tensor, int]:
@@ -118,8 +121,6 @@ def muon_update(grad: Tensor, momentum: Tensor, beta: float = 0.95, nesterov: bo
     """muon.py:8-15: momentum update in place, Nesterov blend written back into ``grad``,
     then the orthogonalised, aspect-scaled bf16 update of the (collapsed) 2-D shape."""
     _require_cuda(grad, "grad")
-    from .engine import dtype_code, view_2d, _ns_mode, _ns_steps, _NS_MODES  # local: avoid cycles
-    import ctypes
     if grad.shape != momentum.shape or grad.dtype != momentum.dtype:
         raise ValueError("grad and momentum must have the same shape and dtype")
     if not (grad.is_contiguous() and momentum.is_contiguous()):
@@ -139,8 +140,7 @@ def muon_update(grad: Tensor, momentum: Tensor, beta: float = 0.95, nesterov: bo
                                      wptr + layout.x_offset_bytes, layout.ldn, layout.x_bs,
                                      1 if tall else 0, stream))
         res = ctypes.c_int(0)
-        from . import engine
-        mode, steps = engine.get_ns_mode()
+        mode, steps = get_ns_mode()
         check(lib.muon_b200_ns_run(wptr, 1, m_, n_, _NS_MODES[mode], steps, None, 1e-7,
                                    ctypes.byref(res), stream))
         off = (wptr - ws.data_ptr()) + (layout.x_offset_bytes if res.value == 0 else layout.c_offset_bytes)

@@ -1,0 +1,115 @@
+"""The benchmark configurations as parity cases: GPT-2-small-shaped hidden weights with aux Adam
+(reduced to 2 of 12 layers so that the CPU oracle finishes in seconds), batched conv filters
+(8 + 8 of the 64 + 64), and — at the full Llama-3-8B sizes, where the oracle would take minutes —
+size-independent properties of the orthogonalised update."""
+import pytest
+import torch
+
+from oracle import muon_oracle as orc
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def mb():
+    import muon_b200
+    yield muon_b200
+    assert muon_b200.device_status() == 0
+
+
+def _step_both(mb, opt, params, ref_p, ref_m, grads, lr, wd, beta=0.95):
+    for p, g in zip(params, grads):
+        p.grad = g.clone().to(DEV)
+    opt.step()
+    for p, g, m in zip(ref_p, grads, ref_m):
+        orc.muon_param_step(p, g.clone(), m, lr, wd, beta)
+
+
+def test_gpt2_small_hidden_weights_with_aux_adam(mb, tmp_path):
+    """12 layers x {q,k,v,o 768x768; fc 3072x768; proj 768x3072} fp32, grads ~N(0, 1e-2), 1-D gains
+    through Adam, MuonWithAuxAdam on a one-rank process group. Two layers are compared."""
+    import torch.distributed as dist
+    dist.init_process_group("nccl", init_method=f"file://{tmp_path}/pg", rank=0, world_size=1)
+    try:
+        g = torch.Generator().manual_seed(2000)
+        layer = [(768, 768)] * 4 + [(3072, 768), (768, 3072)]
+        shapes = layer * 2
+        p0 = [torch.randn(s, generator=g) * 0.02 for s in shapes]
+        gains0 = [torch.ones(768) for _ in range(5)]
+        hidden = [torch.nn.Parameter(p.clone().to(DEV)) for p in p0]
+        gains = [torch.nn.Parameter(p.clone().to(DEV)) for p in gains0]
+        opt = mb.MuonWithAuxAdam([dict(params=hidden, use_muon=True, lr=0.02, weight_decay=0.01),
+                                  dict(params=gains, use_muon=False, lr=3e-4, betas=(0.9, 0.95), eps=1e-10,
+                                       weight_decay=0)])
+        sorted_hidden = opt.param_groups[0]["params"]
+        ref = {id(p): q.clone() for p, q in zip(hidden, p0)}
+        mom = {id(p): torch.zeros_like(q) for p, q in zip(hidden, p0)}
+        ref_g = [p.clone() for p in gains0]
+        ma, va = [torch.zeros(768) for _ in gains0], [torch.zeros(768) for _ in gains0]
+        for step in (1, 2):
+            grads = {id(p): torch.randn(p.shape, generator=g) * 1e-2 for p in hidden}
+            gg = [torch.randn(768, generator=g) * 1e-2 for _ in gains0]
+            for p in hidden:
+                p.grad = grads[id(p)].clone().to(DEV)
+            for p, gr in zip(gains, gg):
+                p.grad = gr.clone().to(DEV)
+            opt.step()
+            for p in hidden:
+                orc.muon_param_step(ref[id(p)], grads[id(p)].clone(), mom[id(p)], 0.02, 0.01, 0.95)
+            for q, gr, m, v in zip(ref_g, gg, ma, va):
+                orc.adam_param_step(q, gr.clone(), m, v, step, 3e-4, 0, (0.9, 0.95), 1e-10)
+        assert [tuple(p.shape) for p in sorted_hidden] == sorted([tuple(s) for s in shapes], reverse=True)
+        for p in hidden:
+            assert orc.rel_fro(p.detach().cpu(), ref[id(p)]) <= 1e-3, tuple(p.shape)
+        for p, q in zip(gains, ref_g):
+            assert torch.allclose(p.detach().cpu(), q, rtol=1e-5, atol=1e-7)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_batched_conv_filters(mb):
+    """256x256x3x3 (-> 256x2304) and 128x128x3x3 (-> 128x1152) fp32 filters, grads ~N(0,1),
+    SingleDeviceMuon; every same-shape set goes through one grouped launch sequence."""
+    g = torch.Generator().manual_seed(3000)
+    shapes = [(256, 256, 3, 3)] * 8 + [(128, 128, 3, 3)] * 8
+    p0 = [torch.randn(s, generator=g) * 0.02 for s in shapes]
+    params = [torch.nn.Parameter(p.clone().to(DEV)) for p in p0]
+    opt = mb.SingleDeviceMuon(params, lr=0.02, weight_decay=0.01)
+    ref_p = [p.clone() for p in p0]
+    ref_m = [torch.zeros_like(p) for p in p0]
+    before = dict(mb._lib.launch_counts())
+    for _ in range(2):
+        grads = [torch.randn(s, generator=g) for s in shapes]
+        _step_both(mb, opt, params, ref_p, ref_m, grads, 0.02, 0.01)
+    after = mb._lib.launch_counts()
+    assert after["prologue"] - before["prologue"] == 4  # 2 steps x 2 shape classes
+    assert after["ns_line3"] - before["ns_line3"] == 16  # 2 steps x 2 classes x 4 iterations
+    for p, r in zip(params, ref_p):
+        assert p.shape == r.shape and orc.rel_fro(p.detach().cpu(), r) <= 1e-3
+
+
+@pytest.mark.parametrize("shape", [(4096, 14336), (14336, 4096), (4096, 4096), (1024, 4096)])
+def test_llama3_8b_shapes_properties(mb, shape):
+    """Full-size bf16 matrices, grads ~N(0, 1e-3): the update must be orthogonal up to the band the
+    live algorithm guarantees, scale-invariant in the gradient, and deterministic."""
+    g = torch.Generator(device=DEV).manual_seed(4000)
+    G = torch.empty(shape, device=DEV, dtype=torch.bfloat16).normal_(0, 1e-3, generator=g)
+    U = mb.zeropower_via_newtonschulz5(G)
+    assert U.shape == G.shape and U.dtype == torch.bfloat16
+    Uf = U.float()
+    gram = Uf @ Uf.T if shape[0] <= shape[1] else Uf.T @ Uf
+    eye = torch.eye(gram.shape[0], device=DEV)
+    if shape[0] != shape[1]:
+        # singular values within [0.98, 1.02] -> eigenvalues of the Gram matrix within ~[0.96, 1.04]
+        dev = torch.linalg.matrix_norm(gram - eye, ord=2).item()
+        assert dev < 0.05, dev
+    else:
+        assert torch.linalg.matrix_norm(gram, ord=2).item() < 1.2
+    # alignment with the input: <U, G> equals the nuclear norm of G for the exact polar factor
+    assert (Uf * G.float()).sum().item() > 0
+    # NS normalises its input, so a power-of-two rescaling of G (exact in bf16) changes nothing
+    assert torch.equal(mb.zeropower_via_newtonschulz5(G * 4), U)
+    assert torch.equal(mb.zeropower_via_newtonschulz5(G), U)
+    # transposition symmetry: NS(G^T) == NS(G)^T bit for bit (tall inputs run as their transpose)
+    assert torch.equal(mb.zeropower_via_newtonschulz5(G.T.contiguous()), U.T)

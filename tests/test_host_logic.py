@@ -132,6 +132,22 @@ def test_engine_helpers():
         E.set_ns_mode("cubic")
 
 
+def test_launch_planner():
+    from muon_b200 import engine as E
+    cap = 4 << 30
+    for m, n, count in [(4096, 14336, 64), (4096, 14336, 32), (4096, 4096, 64), (1024, 4096, 64),
+                        (4096, 14336, 8), (768, 3072, 12), (128, 1152, 64), (4096, 14336, 1), (40, 72, 3)]:
+        sizes = E.plan_launches(m, n, count, cap)
+        assert sum(sizes) == count and min(sizes) >= 1 and max(sizes) - min(sizes) <= 1
+        per_matrix = 2 * (2 * m * n + 2 * m * m)
+        assert max(sizes) * per_matrix <= cap
+        # never worse (in partial waves) than one matrix per launch
+        waves = lambda b: -(-(E.tri_tiles(m) * b) // 74)
+        assert sum(waves(b) for b in sizes) <= count * waves(1)
+    assert E.plan_launches(4096, 14336, 0, cap) == []
+    assert E.plan_launches(4096, 14336, 64, 1 << 20) == [1] * 64  # workspace cap of one matrix
+
+
 # -------------------------------------------------- distributed logic on gloo CPU ranks
 class OracleBackend:
     """Test-only stand-in for the CUDA backend: same interface, oracle arithmetic."""
