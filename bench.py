@@ -46,12 +46,25 @@ WORKLOADS = {
                           "Llama-3-8B hidden weights, 4 of 32 layers, bf16 (small case for profiling)"),
     "gpt2-small-hidden": (GPT2_SMALL_LAYER * 12, torch.float32, 1e-2,
                           "GPT-2 small hidden weights, 72 matrices, fp32"),
+    "conv-filters": ([(256, 256, 3, 3)] * 64 + [(128, 128, 3, 3)] * 64, torch.float32, 1.0,
+                     "conv filters, 64 x 256x256x3x3 + 64 x 128x128x3x3, fp32"),
 }
 NS_ITERS = 4  # the reference's live algorithm
 # DRAM bytes (read + write) per matrix element that one launch of the line-3 kernel moved in the
 # ncu capture summarised in profiles/ns_gemm_line3_llama3-8b-4layers.md: 3.723 GB for 8 matrices
 # of 4096 x 14336. Traffic of that kernel grows with the elements a launch covers.
 LINE3_DRAM_BYTES_PER_ELEMENT = 3.723e9 / (8 * 4096 * 14336)
+
+
+def as_matrices(shapes):
+    """(rows, cols) each parameter presents to the iteration: 4-D filters collapse to [O, I*kH*kW]."""
+    out = []
+    for s in shapes:
+        cols = 1
+        for d in s[1:]:
+            cols *= d
+        out.append((s[0], cols))
+    return out
 
 
 def ns_flops(shapes, iters=NS_ITERS):
@@ -166,6 +179,7 @@ def run_ours(args):
         _lib.check(_lib.lib.muon_b200_set_reserved_sms(comm_sms))
 
     shapes, dtype, grad_std, desc = WORKLOADS[args.workload]
+    mats = as_matrices(shapes)
     params = make_problem(shapes, dtype, grad_std, device, rank, world)
     opt = muon_b200.Muon(list(params), lr=0.02, weight_decay=0.01, momentum=0.95)
     sorted_params = opt.param_groups[0]["params"]
@@ -234,7 +248,7 @@ def run_ours(args):
 
     if rank == 0:
         peaks = load_peaks()
-        red, dense = ns_flops(shapes)
+        red, dense = ns_flops(mats)
         ms3, work3, n3 = per_kind["ns_line3"]
         ns_ms = sum(per_kind[k][0] for k in ("ns_line1", "ns_line2", "ns_line3"))
         ns_work = sum(per_kind[k][1] for k in ("ns_line1", "ns_line2", "ns_line3"))
@@ -250,7 +264,7 @@ def run_ours(args):
             "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": args.workload, "description": desc, "matrices": len(shapes),
-                       "elements": sum(r * c for r, c in shapes), "param_dtype": str(dtype).split(".")[-1],
+                       "elements": sum(r * c for r, c in mats), "param_dtype": str(dtype).split(".")[-1],
                        "ns_mode": "aol4", "ns_iters": NS_ITERS, "parallelism": f"muon-round-robin-dp{world}",
                        "l2_policy": "inputs (>= 14 GB per step at full size) are larger than the 126 MB L2"},
             "steps_per_s": 1e3 / ms_per_step,
@@ -267,9 +281,9 @@ def run_ours(args):
                                       f"burst figure is {peaks['tflops_burst']}",
                          "launches": int(n3), "avg_launch_ms": ms3 / n3 if n3 else None,
                          # average DRAM bytes per launch, scaled from the ncu capture by elements covered
-                         "traffic": (LINE3_DRAM_BYTES_PER_ELEMENT * sum(r * c for r, c in shapes) * NS_ITERS
+                         "traffic": (LINE3_DRAM_BYTES_PER_ELEMENT * sum(r * c for r, c in mats) * NS_ITERS
                                      / world / (n3 / args.steps)) if n3 and args.workload.startswith("llama3") else None,
-                         "traffic_algorithmic": ((2 * sum(r * c for r, c in shapes) + sum(min(r, c) ** 2 for r, c in shapes))
+                         "traffic_algorithmic": ((2 * sum(r * c for r, c in mats) + sum(min(r, c) ** 2 for r, c in mats))
                                                  * 2 * NS_ITERS / world / (n3 / args.steps)) if n3 else None,
                          "rank": 0},
             "kernels": kernels,
@@ -306,7 +320,7 @@ def reference_sample(workload):
     else:
         sample = [(768, 768)] * 4 + [(3072, 768), (768, 3072)]
         text = "one GPT-2 small layer (6 matrices); scaled to the full step by NS FLOPs"
-    scale = ns_flops(shapes)[1] / ns_flops(sample)[1]
+    scale = ns_flops(as_matrices(shapes))[1] / ns_flops(sample)[1]
     return sample, dtype, grad_std, scale, text
 
 

@@ -36,12 +36,9 @@ def _as_bf16_3d(t: Tensor, name: str) -> tuple[Tensor, int]:
 def _out_3d(out: Tensor | None, like: Tensor, shape: tuple[int, ...]) -> tuple[Tensor, Tensor | None]:
     """(kernel output buffer, user tensor to copy back into or None)."""
     batch, r, c = shape
-    if out is not None:
-        o3 = out.reshape(batch, r, c) if out.ndim in (2, 3) else None
-        if o3 is not None and out.dtype == torch.bfloat16 and o3.stride(-1) == 1 and \
-                o3.stride(-2) % 8 == 0 and o3.data_ptr() % 16 == 0 and (batch == 1 or o3.stride(0) % 8 == 0) \
-                and o3.data_ptr() == out.data_ptr():
-            return o3, None
+    if out is not None and out.dtype == torch.bfloat16 and out.is_contiguous() and c % 8 == 0 \
+            and out.data_ptr() % 16 == 0 and out.numel() == batch * r * c:
+        return out.view(batch, r, c), None  # the kernel can write the user's tensor directly
     ld = (c + 7) // 8 * 8
     buf = torch.empty(batch, r, ld, dtype=torch.bfloat16, device=like.device)[:, :, :c]
     return buf, out
