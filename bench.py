@@ -339,7 +339,10 @@ def run_reference(args):
         "impl": "reference", "metric": "muon_step_ms", "value": ms, "unit": "ms", "n_gpus": args.gpus,
         "steps": len(times), "warmup": min(args.warmup, 1), "ms_per_step": ms, "higher_is_better": False,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": args.workload, "description": desc, "matrices": len(shapes)},
+        "config": {"workload": args.workload, "description": desc, "matrices": len(shapes),
+                   "elements": sum(r * c for r, c in as_matrices(shapes)),
+                   "param_dtype": str(dtype).split(".")[-1], "ns_mode": "aol4", "ns_iters": NS_ITERS,
+                   "parallelism": "host cores"},
         "cpu_baseline": {"value": ms, "unit": "ms", "cores": threads, "kind": "port",
                          "sample": text + f" (x{scale:.1f}); oracle restatement of muon.py on torch CPU"},
         "e2e": {"value": ms, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

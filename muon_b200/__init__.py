@@ -5,6 +5,7 @@ Drop-in for the public names of thib-s/Muon's ``muon`` module. All arithmetic ru
 importing this package fails if that library has not been built.
 """
 from ._lib import MuonB200Error, device_status  # noqa: F401  (import fails loudly without the library)
+from .checkpoint import consolidated_state_dict, load_consolidated_state_dict  # noqa: F401
 from .engine import get_backend, get_ns_mode, set_ns_mode  # noqa: F401
 from .ops import (  # noqa: F401
     adam_update,

@@ -241,3 +241,59 @@ def test_distributed_muon_on_gloo_ranks(tmp_path, world, with_adam):
             for a, b in zip(o["gains"], g0):
                 assert torch.equal(a, b)
         assert not torch.equal(g0[0], torch.ones(8))
+
+
+# ------------------------------------------- consolidated checkpoints across world sizes
+CKPT_SHAPES = [(24, 48)] * 6 + [(48, 24)] * 6
+
+
+def _ckpt_rank(rank, world, tmpdir, phase):
+    dist.init_process_group("gloo", init_method=f"file://{tmpdir}/pg{phase}", rank=rank, world_size=world)
+    try:
+        import muon_b200 as mb
+        from muon_b200 import checkpoint as ck
+        from muon_b200 import engine as E
+        E._set_backend_for_testing(OracleBackend())
+        p0, grads = _make_problem(CKPT_SHAPES, seed=7, steps=3)
+        if phase == 1:
+            params = [torch.nn.Parameter(p.clone()) for p in p0]
+            opt = mb.Muon(list(params), lr=0.02, weight_decay=0.01)
+            for step_grads in grads[:2]:
+                for p, gr in zip(params, step_grads):
+                    p.grad = gr.clone()
+                opt.step()
+            state = ck.consolidated_state_dict(opt)
+            if rank == 0:
+                assert sorted(state["groups"][0]["momentum"]) == list(range(len(CKPT_SHAPES)))
+                torch.save(dict(opt=state, params=[p.detach().clone() for p in params]), f"{tmpdir}/ckpt.pt")
+            else:
+                assert state is None
+        else:
+            saved = torch.load(f"{tmpdir}/ckpt.pt", weights_only=False)
+            params = [torch.nn.Parameter(p.clone()) for p in saved["params"]]
+            opt = mb.Muon(list(params), lr=0.5, weight_decay=0.5)  # overwritten by the checkpoint
+            ck.load_consolidated_state_dict(opt, saved["opt"])
+            sorted_params = opt.param_groups[0]["params"]
+            assert [i for i, p in enumerate(sorted_params) if len(opt.state[p])] == \
+                list(range(rank, len(sorted_params), world))
+            for p, gr in zip(params, grads[2]):
+                p.grad = gr.clone()
+            opt.step()
+            torch.save([p.detach().clone() for p in params], f"{tmpdir}/final{rank}.pt")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_consolidated_checkpoint_survives_a_world_size_change(tmp_path):
+    mp.spawn(_ckpt_rank, args=(2, str(tmp_path), 1), nprocs=2, join=True)
+    mp.spawn(_ckpt_rank, args=(3, str(tmp_path), 2), nprocs=3, join=True)
+    p0, grads = _make_problem(CKPT_SHAPES, seed=7, steps=3)
+    ref = [p.clone() for p in p0]
+    moms = [torch.zeros_like(p) for p in p0]
+    for step_grads in grads:
+        for p, gr, m in zip(ref, step_grads, moms):
+            orc.muon_param_step(p, gr.clone(), m, 0.02, 0.01, 0.95)
+    for r in range(3):
+        got = torch.load(f"{tmp_path}/final{r}.pt", weights_only=False)
+        for p, q in zip(got, ref):
+            assert torch.equal(p, q), f"rank {r} after resume differs from the uninterrupted run"
