@@ -14,6 +14,7 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kTileRows = 64;
+constexpr int kRowsInFlight = 2;  // rows of a tile whose loads a thread issues back to back
 
 template <typename T>
 struct Vec;
@@ -21,6 +22,10 @@ template <>
 struct Vec<float> {
   static constexpr int N = 4;
   using Raw = float4;
+  __device__ static Raw load_raw(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  __device__ static void unpack(const Raw& r, float (&v)[4]) {
+    v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+  }
   __device__ static void load(const float* p, float (&v)[4]) {
     float4 r = *reinterpret_cast<const float4*>(p);
     v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
@@ -32,6 +37,16 @@ struct Vec<float> {
 template <>
 struct Vec<__nv_bfloat16> {
   static constexpr int N = 8;
+  using Raw = uint4;
+  __device__ static Raw load_raw(const __nv_bfloat16* p) { return *reinterpret_cast<const uint4*>(p); }
+  __device__ static void unpack(const Raw& r, float (&v)[8]) {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[2 * j] = bf16_bits_to_float(w[j] & 0xffffu);
+      v[2 * j + 1] = bf16_bits_to_float(w[j] >> 16);
+    }
+  }
   __device__ static void load(const __nv_bfloat16* p, float (&v)[8]) {
     uint4 r = *reinterpret_cast<const uint4*>(p);
     uint32_t w[4] = {r.x, r.y, r.z, r.w};
@@ -128,8 +143,24 @@ prologue_kernel(const PrologueArgs a) {
     __nv_bfloat16* x = a.x + (long long)ti * a.x_bs;
     const int c0 = tcn * kTileCols + tx * V;
 
+    const bool full = a.vec_ok && (c0 + V <= a.cols);
 #pragma unroll
-    for (int it = 0; it < kTileRows / 16; ++it) {
+    for (int it0 = 0; it0 < kTileRows / 16; it0 += kRowsInFlight) {
+     // The 128-bit loads of kRowsInFlight rows are issued together and kept as raw words, so
+     // each thread has 2 * kRowsInFlight requests in flight at little register cost.
+     typename Vec<T>::Raw rg[kRowsInFlight], rm[kRowsInFlight];
+#pragma unroll
+     for (int u = 0; u < kRowsInFlight; ++u) {
+       const int r = tr * kTileRows + (it0 + u) * 16 + ty;
+       if (full && r < a.rows) {
+         const long long off = (long long)r * a.cols + c0;
+         rg[u] = Vec<T>::load_raw(g + off);
+         rm[u] = Vec<T>::load_raw(m + off);
+       }
+     }
+#pragma unroll
+     for (int u = 0; u < kRowsInFlight; ++u) {
+      const int it = it0 + u;
       const int rl = it * 16 + ty;
       const int r = tr * kTileRows + rl;
       float xv[V];
@@ -138,10 +169,9 @@ prologue_kernel(const PrologueArgs a) {
       if (r < a.rows && c0 < a.cols) {
         const long long off = (long long)r * a.cols + c0;
         float gv[V], mv[V];
-        const bool full = a.vec_ok && (c0 + V <= a.cols);
         if (full) {
-          Vec<T>::load(g + off, gv);
-          Vec<T>::load(m + off, mv);
+          Vec<T>::unpack(rg[u], gv);
+          Vec<T>::unpack(rm[u], mv);
         } else {
 #pragma unroll
           for (int j = 0; j < V; ++j) {
@@ -201,6 +231,7 @@ prologue_kernel(const PrologueArgs a) {
 #pragma unroll
         for (int j = 0; j < V; ++j) tile[tx * V + j][rl] = __float2bfloat16_rn(xv[j]);
       }
+     }
     }
     if (TRANSPOSE) {
       __syncthreads();
@@ -279,13 +310,16 @@ epilogue_kernel(const EpilogueArgs a) {
     }
 
     const int c0 = tcn * kTileCols + tx * V;
+    const bool full = a.vec_ok && (c0 + V <= a.cols);
+    // One row per pass here: batching the loads of two rows, which helps the prologue, made
+    // this kernel a third slower (fewer resident warps, nothing gained on its two streams).
 #pragma unroll
     for (int it = 0; it < kTileRows / 16; ++it) {
+     {
       const int rl = it * 16 + ty;
       const int r = tr * kTileRows + rl;
       if (r < a.rows && c0 < a.cols) {
         const long long off = (long long)r * a.cols + c0;
-        const bool full = a.vec_ok && (c0 + V <= a.cols);
         float pv[V], uv[V];
         if (full) {
           Vec<T>::load(p + off, pv);
@@ -334,6 +368,7 @@ epilogue_kernel(const EpilogueArgs a) {
             if (c0 + j < a.cols) p[off + j] = from_f<T>(pv[j]);
         }
       }
+     }
     }
     if (TRANSPOSE) __syncthreads();
   }

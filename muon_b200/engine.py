@@ -264,6 +264,33 @@ class CudaBackend:
         return out if G.ndim == 3 else out[0]
 
 
+def _install_stats_dump() -> None:
+    """MUON_B200_STATS=1: time every kernel launch with CUDA events and print, at interpreter
+    exit, device time, launches and achieved rate per kernel kind."""
+    import atexit
+    import os
+    import sys
+    if os.environ.get("MUON_B200_STATS", "0") not in ("1", "true", "yes"):
+        return
+    _lib.timing_enable(True)
+
+    def dump():
+        try:
+            stats = _lib.timing_collect()
+        except Exception as e:  # the CUDA context may already be gone
+            print(f"[muon_b200] stats unavailable: {e}", file=sys.stderr)
+            return
+        for kind, (ms, work, launches) in stats.items():
+            if launches:
+                unit, scale = ("TFLOP/s", 1e12) if kind.startswith("ns_") else ("GB/s", 1e9)
+                print(f"[muon_b200] {kind:14s} launches={launches:7d} device_ms={ms:10.3f} "
+                      f"rate={work / (ms * 1e-3) / scale:8.1f} {unit}", file=sys.stderr)
+
+    atexit.register(dump)
+
+
+_install_stats_dump()
+
 _backend = None
 
 
