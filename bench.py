@@ -315,8 +315,8 @@ def cpu_sample_step(shapes_sample, dtype, grad_std, threads):
 def reference_sample(workload):
     shapes, dtype, grad_std, _ = WORKLOADS[workload]
     if workload.startswith("llama3"):
-        sample = [(1024, 4096), (4096, 4096)]
-        text = "one 1024x4096 (k/v) and one 4096x4096 (q/o) matrix; scaled to the full step by NS FLOPs"
+        sample = list(LLAMA3_8B_LAYER)
+        text = "one of the 32 layers (7 matrices); scaled to the full step by NS FLOPs"
     else:
         sample = [(768, 768)] * 4 + [(3072, 768), (768, 3072)]
         text = "one GPT-2 small layer (6 matrices); scaled to the full step by NS FLOPs"

@@ -234,6 +234,29 @@ def test_grad_none_becomes_zero_and_state_keys(mb):
     assert torch.allclose(p.detach(), before * (1 - 0.1 * 0.5), rtol=1e-6)  # decay only
 
 
+def test_degenerate_parameters_are_rejected_loudly(mb):
+    """Empty matrices and 1-D / 3-D tensors have no orthogonalisation: clear errors, no silent skip."""
+    empty = torch.nn.Parameter(torch.zeros(0, 8, device=DEV))
+    empty.grad = torch.zeros(0, 8, device=DEV)
+    with pytest.raises(mb.MuonB200Error):
+        mb.SingleDeviceMuon([empty]).step()
+    vec = torch.nn.Parameter(torch.zeros(8, device=DEV))
+    vec.grad = torch.zeros(8, device=DEV)
+    with pytest.raises(ValueError, match="2-D or 4-D"):
+        mb.SingleDeviceMuon([vec]).step()
+    half = torch.nn.Parameter(torch.zeros(8, 8, device=DEV, dtype=torch.float16))
+    half.grad = torch.zeros_like(half)
+    with pytest.raises(ValueError, match="float32 and bfloat16"):
+        mb.SingleDeviceMuon([half]).step()
+    # a 1 x n and an n x 1 matrix are legal: the update is the normalised row / column
+    row = torch.nn.Parameter(torch.ones(1, 64, device=DEV))
+    row.grad = torch.full((1, 64), 2.0, device=DEV)
+    mb.SingleDeviceMuon([row], lr=1.0, weight_decay=0.0).step()
+    ref = torch.ones(1, 64)
+    orc.muon_param_step(ref, torch.full((1, 64), 2.0), torch.zeros(1, 64), 1.0, 0.0, 0.95)
+    assert torch.allclose(row.detach().cpu(), ref, rtol=2e-2, atol=2e-3)
+
+
 def test_state_dict_round_trip(mb):
     torch.manual_seed(0)
     p = torch.nn.Parameter(torch.randn(64, 96, device=DEV))
