@@ -142,14 +142,19 @@ class CudaBackend:
 
     def __init__(self, workspace_cap_bytes: int = 4 << 30):
         self.workspace_cap_bytes = workspace_cap_bytes
-        self._workspaces: dict[tuple[int, int], Tensor] = {}
+        self._workspaces: dict[tuple[int, int, int], Tensor] = {}
+        self._side_streams: dict[int, torch.cuda.Stream] = {}
         self.launch_groups = 0  # grouped C-ABI calls issued (for accounting)
+        # Run prologue/epilogue of one launch group beside the GEMMs of another (see
+        # _muon_step_pipelined). MUON_B200_OVERLAP=0 switches it off.
+        import os
+        self.overlap_elementwise = os.environ.get("MUON_B200_OVERLAP", "1") not in ("0", "false", "no")
 
     # -- memory ------------------------------------------------------------------------
-    def workspace(self, device: torch.device, nbytes: int) -> Tensor:
-        """uint8 buffer >= nbytes, private to (device, current stream)."""
+    def workspace(self, device: torch.device, nbytes: int, slot: int = 0) -> Tensor:
+        """uint8 buffer >= nbytes, private to (device, current stream, slot)."""
         key = (device.index if device.index is not None else torch.cuda.current_device(),
-               _stream_ptr(device))
+               _stream_ptr(device), slot)
         buf = self._workspaces.get(key)
         if buf is None or buf.numel() < nbytes:
             buf = torch.empty(nbytes + 256, dtype=torch.uint8, device=device)
@@ -169,8 +174,13 @@ class CudaBackend:
 
     # -- Muon --------------------------------------------------------------------------
     def muon_step(self, params: Sequence[Tensor], grads: Sequence[Tensor], moms: Sequence[Tensor],
-                  lr: float, weight_decay: float, beta: float, nesterov: bool = True) -> None:
-        """prologue -> Newton-Schulz -> epilogue for same-shape, same-dtype parameters."""
+                  lr: float, weight_decay: float, beta: float, nesterov: bool = True,
+                  after_group=None, max_group: int | None = None) -> None:
+        """prologue -> Newton-Schulz -> epilogue for same-shape, same-dtype parameters.
+
+        The parameters are processed in launch groups (see plan_launches), at most `max_group`
+        per group when given. `after_group(params_of_group, event)` is called once the update of
+        a group has been enqueued; `event` completes when those parameters hold their new values."""
         p0 = params[0]
         rows, cols = view_2d(p0.shape)
         code = dtype_code(p0)
@@ -185,10 +195,18 @@ class CudaBackend:
         mode, steps = _ns_mode, _ns_steps
         eps = 1e-7
         sizes = plan_launches(m_, n_, len(params), self.workspace_cap_bytes, self._sm_pairs(p0.device))
+        if max_group is not None and max(sizes) > max_group:
+            launches = -(-len(params) // max(1, max_group))
+            cuts = [round(i * len(params) / launches) for i in range(launches + 1)]
+            sizes = [e - s for s, e in zip(cuts[:-1], cuts[1:])]
         bounds = [0]
         for b in sizes:
             bounds.append(bounds[-1] + b)
         dev = p0.device
+        if self.overlap_elementwise and len(sizes) >= 2:
+            self._muon_step_pipelined(params, grads, moms, bounds, rows, cols, code, lr, weight_decay,
+                                      beta, nesterov, scale, mode, steps, eps, after_group)
+            return
         with torch.cuda.device(dev):
             stream = _stream_ptr(dev)
             for s, e in zip(bounds[:-1], bounds[1:]):
@@ -202,6 +220,74 @@ class CudaBackend:
                     _NS_MODES[mode], steps, None, eps, self._aligned_ptr(ws), layout.total_bytes,
                     stream))
                 self.launch_groups += 1
+                if after_group is not None:
+                    done = torch.cuda.Event()
+                    done.record(torch.cuda.current_stream(dev))
+                    after_group(params[s:e], done)
+
+    def _muon_step_pipelined(self, params, grads, moms, bounds, rows, cols, code, lr, weight_decay,
+                             beta, nesterov, scale, mode, steps, eps, after_group=None) -> None:
+        """Same work as the loop over muon_b200_muon_step, with the HBM-bound stages of one launch
+        group running on a side stream while the tensor-bound Newton-Schulz kernels of another
+        group run on the caller's stream. The persistent GEMM CTAs leave registers, threads and
+        ~30 KiB of shared memory free on every SM, so the elementwise CTAs are co-resident.
+
+        Side stream:  P(0) | for i: P(i+1), wait NS(i), E(i)        (two workspaces, i % 2)
+        Main stream:        for i: wait P(i), NS(i)                  then waits for the side stream
+        """
+        dev = params[0].device
+        tall = rows > cols
+        m_, n_ = min(rows, cols), max(rows, cols)
+        groups = list(zip(bounds[:-1], bounds[1:]))
+        with torch.cuda.device(dev):
+            main = torch.cuda.current_stream(dev)
+            side = self._side_stream(dev)
+            layouts = [_lib.ns_layout(e - s, m_, n_) for s, e in groups]
+            ws_ptr = [self._aligned_ptr(self.workspace(dev, max(l.total_bytes for l in layouts), slot))
+                      for slot in (0, 1)]
+            side.wait_stream(main)  # gradients and parameters are ready in main-stream order
+            ns_mode = _NS_MODES[mode]
+
+            def prologue(i):
+                s, e = groups[i]
+                l = layouts[i]
+                check(lib.muon_b200_prologue(
+                    ptr_array([g.data_ptr() for g in grads[s:e]]), ptr_array([m.data_ptr() for m in moms[s:e]]),
+                    e - s, rows, cols, code, beta, 1 if nesterov else 0, ws_ptr[i % 2] + l.x_offset_bytes,
+                    l.ldn, l.x_bs, 1 if tall else 0, side.cuda_stream))
+                ev = torch.cuda.Event()
+                ev.record(side)
+                return ev
+
+            p_done = prologue(0)
+            for i, (s, e) in enumerate(groups):
+                l = layouts[i]
+                next_p = prologue(i + 1) if i + 1 < len(groups) else None
+                main.wait_event(p_done)
+                slot = ctypes.c_int(0)
+                check(lib.muon_b200_ns_run(ws_ptr[i % 2], e - s, m_, n_, ns_mode, steps, None, eps,
+                                           ctypes.byref(slot), main.cuda_stream))
+                ns_done = torch.cuda.Event()
+                ns_done.record(main)
+                side.wait_event(ns_done)
+                u = ws_ptr[i % 2] + (l.x_offset_bytes if slot.value == 0 else l.c_offset_bytes)
+                check(lib.muon_b200_epilogue(
+                    ptr_array([p.data_ptr() for p in params[s:e]]), e - s, rows, cols, code, u, l.ldn,
+                    l.x_bs, 1 if tall else 0, lr, weight_decay, scale, side.cuda_stream))
+                if after_group is not None:
+                    done = torch.cuda.Event()
+                    done.record(side)
+                    after_group(params[s:e], done)
+                p_done = next_p
+                self.launch_groups += 1
+            main.wait_stream(side)
+
+    def _side_stream(self, device: torch.device):
+        key = device.index if device.index is not None else torch.cuda.current_device()
+        s = self._side_streams.get(key)
+        if s is None:
+            s = self._side_streams[key] = torch.cuda.Stream(device=device)
+        return s
 
     # -- Adam --------------------------------------------------------------------------
     def adam_step(self, params: Sequence[Tensor], grads: Sequence[Tensor], exp_avgs: Sequence[Tensor],

@@ -114,11 +114,13 @@ class PeerPush:
         """All ranks are inside step() (stream-ordered after their earlier work) from here on."""
         dist.all_reduce(self._token)
 
-    def push(self, updated) -> None:
-        """Copy each freshly updated local parameter into every peer's copy of it."""
+    def push(self, updated, ready=None) -> None:
+        """Copy each freshly updated local parameter into every peer's copy of it, once `ready`
+        (default: everything enqueued so far on the current stream) has completed."""
         from ._lib import check, lib, ptr_array
-        ready = torch.cuda.Event()
-        ready.record(torch.cuda.current_stream(self.device))
+        if ready is None:
+            ready = torch.cuda.Event()
+            ready.record(torch.cuda.current_stream(self.device))
         with torch.cuda.device(self.device):
             for r, stream in zip(self.peers, self.streams):
                 stream.wait_event(ready)

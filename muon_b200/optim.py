@@ -42,7 +42,7 @@ def _bucket_by_shape(params):
     return buckets
 
 
-def _muon_update_params(optimizer, params, group) -> None:
+def _muon_update_params(optimizer, params, group, **step_options) -> None:
     """Body of the reference's per-parameter loop (muon.py:91-99) for a list of parameters."""
     backend = get_backend()
     for p in params:
@@ -50,7 +50,7 @@ def _muon_update_params(optimizer, params, group) -> None:
     for plist in _bucket_by_shape(params).values():
         backend.muon_step(plist, [p.grad for p in plist],
                           [optimizer.state[p]["momentum_buffer"] for p in plist],
-                          group["lr"], group["weight_decay"], group["momentum"])
+                          group["lr"], group["weight_decay"], group["momentum"], **step_options)
 
 
 def _adam_update_params(optimizer, group) -> None:
@@ -79,7 +79,7 @@ def _adam_update_params(optimizer, group) -> None:
                           group["lr"], group["weight_decay"], group["betas"], group["eps"])
 
 
-def _next_chunk(params, owned, done_upto, backend, split_for_exchange=False):
+def _next_chunk(params, owned, done_upto, backend):
     """The next parameters this rank updates in one grouped launch sequence: the same-shape run
     starting at owned[done_upto], cut to the first launch the planner proposes."""
     p0 = params[owned[done_upto]]
@@ -91,12 +91,6 @@ def _next_chunk(params, owned, done_upto, backend, split_for_exchange=False):
         run += 1
     limit = plan_launches(min(rows, cols), max(rows, cols), run,
                           getattr(backend, "workspace_cap_bytes", 4 << 30))[0]
-    if split_for_exchange:
-        # The exchange of a launch group can only start when the group is done, and at 8 GPUs
-        # the copies take about as long as the compute: keep groups to half of the run so that
-        # the copy engines start early. (Quarters were tried at 4 GPUs: the smaller launches lost
-        # in GEMM efficiency what they gained in overlap.)
-        limit = min(limit, max(1, -(-run // 2)))
     return [params[idx] for idx in owned[done_upto:done_upto + limit]]
 
 
@@ -111,15 +105,23 @@ def _distributed_muon_group_step(optimizer, group) -> None:
     owned = list(range(rank, len(params), world))
     done_upto = 0  # owned[:done_upto] have been updated
     pending = []
-    push = get_peer_push(optimizer, group) if world > 1 else None
+    if world == 1:
+        # Nothing to exchange: the whole group goes to the engine, which plans its own launches.
+        _muon_update_params(optimizer, params, group)
+        return
+    push = get_peer_push(optimizer, group)
     if push is not None:
-        # Copy-engine exchange: same ownership and update order, pushes instead of gathers.
+        # Copy-engine exchange: same ownership and update order, pushes instead of gathers. Every
+        # launch group is pushed as soon as its epilogue is enqueued. The exchange of a group can
+        # only start when the group is done, and at 8 GPUs the copies take about as long as the
+        # compute: groups are capped to half of a same-shape run so the copy engines start early.
+        # (Quarters were tried at 4 GPUs: the smaller launches lost in GEMM efficiency what they
+        # gained in overlap.)
+        mine = [params[i] for i in owned]
         push.begin_step()
-        while done_upto < len(owned):
-            chunk = _next_chunk(params, owned, done_upto, backend, split_for_exchange=world >= 4)
-            _muon_update_params(optimizer, chunk, group)
-            push.push(chunk)
-            done_upto += len(chunk)
+        for plist in _bucket_by_shape(mine).values():
+            cap = max(1, -(-len(plist) // 2)) if world >= 4 else None
+            _muon_update_params(optimizer, plist, group, after_group=push.push, max_group=cap)
         push.end_step()
         return
     for base_i in range(0, len(params), world):
