@@ -217,9 +217,15 @@ def run_ours(args):
     launches = sum(counts1.values()) - sum(counts0.values())
 
     # ---- the same steps again with every kernel bracketed by events (roofline) ----
+    # In this pass the elementwise stages are not overlapped with the GEMMs of another launch
+    # group, so that every kernel's duration is its own (co-running kernels stretch each other).
+    backend = muon_b200.get_backend()
+    overlap = backend.overlap_elementwise
+    backend.overlap_elementwise = False
     _lib.timing_enable(True)
     timed(args.steps)
     _lib.timing_enable(False)
+    backend.overlap_elementwise = overlap
     per_kind = _lib.timing_collect()
 
     # ---- end to end: gradients arrive from pinned host memory, a scalar goes back ----
@@ -287,6 +293,9 @@ def run_ours(args):
                                                  * 2 * NS_ITERS / world / (n3 / args.steps)) if n3 else None,
                          "rank": 0},
             "kernels": kernels,
+            "kernels_note": "per-kernel CUDA-event times from a second pass over the same steps with the "
+                            "elementwise stages serialised behind the GEMMs (the timed `value` overlaps them)",
+            "overlap_elementwise": bool(overlap),
             "clocks": clocks.summary(),
             "device_status": status,
         }
