@@ -62,6 +62,14 @@ class PeerPush:
         gathered = [None] * self.world
         dist.all_gather_object(gathered, (exported, errors))
         errors = [e for g in gathered for e in g[1]]
+        # Every rank must hold the same parameters in the same order, or ownership (index % world)
+        # and the pushes would pair up different tensors: compare the byte sizes rank by rank.
+        sizes = [[item[2] for item in g[0]] for g in gathered]
+        if not errors and any(s != sizes[0] for s in sizes):
+            bad = [r for r, s in enumerate(sizes) if s != sizes[0]]
+            raise RuntimeError(f"muon_b200: ranks {bad} hold a different parameter list than rank 0 "
+                               "(count, order or sizes differ); the distributed optimizer needs "
+                               "identical, identically ordered parameters on every rank")
         self.ptrs = None  # ptrs[r][i]: address of parameter i in rank r's memory, mapped here
         self._opened = {}
         if not errors:
