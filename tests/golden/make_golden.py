@@ -30,7 +30,9 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-ref_dir = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+ref_dir = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MUON_REFERENCE_DIR", "")
+if not os.path.isfile(os.path.join(ref_dir, "muon.py")):
+    raise SystemExit("usage: make_golden.py <directory holding the reference's muon.py>")
 sys.path.insert(0, ref_dir)
 
 import muon as ref  # noqa: E402  the real reference module
