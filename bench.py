@@ -36,6 +36,8 @@ if ROOT not in sys.path:
 
 LLAMA3_8B_LAYER = [(4096, 4096), (4096, 4096), (1024, 4096), (1024, 4096),
                    (14336, 4096), (14336, 4096), (4096, 14336)]  # q, o, k, v, gate, up, down
+LLAMA3_70B_LAYER = [(8192, 8192), (8192, 8192), (1024, 8192), (1024, 8192),
+                    (28672, 8192), (28672, 8192), (8192, 28672)]
 GPT2_SMALL_LAYER = [(768, 768)] * 4 + [(3072, 768), (768, 3072)]
 
 WORKLOADS = {
@@ -44,6 +46,8 @@ WORKLOADS = {
                          "Llama-3-8B hidden weights, 224 matrices, bf16"),
     "llama3-8b-4layers": (LLAMA3_8B_LAYER * 4, torch.bfloat16, 1e-3,
                           "Llama-3-8B hidden weights, 4 of 32 layers, bf16 (small case for profiling)"),
+    "llama3-70b-2layers": (LLAMA3_70B_LAYER * 2, torch.bfloat16, 1e-3,
+                           "Llama-3-70B hidden weights, 2 of 80 layers, bf16 (the full set needs 8 GPUs)"),
     "gpt2-small-hidden": (GPT2_SMALL_LAYER * 12, torch.float32, 1e-2,
                           "GPT-2 small hidden weights, 72 matrices, fp32"),
     "conv-filters": ([(256, 256, 3, 3)] * 64 + [(128, 128, 3, 3)] * 64, torch.float32, 1.0,
@@ -238,9 +242,16 @@ def run_ours(args):
     result_host = torch.zeros(1, dtype=torch.float32).pin_memory()
     probe = sorted_params[0]
 
+    copy_stream = torch.cuda.Stream(device=device)
+
     def copy_in():
-        for p in owned:
-            p.grad.copy_(pinned[tuple(p.shape)], non_blocking=True)
+        # The gradients come in on a copy stream, in the order the optimizer consumes them, each
+        # marked with its own event: step() starts on the first ones while the rest are in flight.
+        copy_stream.wait_stream(torch.cuda.current_stream())  # the previous step has read them
+        with torch.cuda.stream(copy_stream):
+            for p in owned:
+                p.grad.copy_(pinned[tuple(p.shape)], non_blocking=True)
+                muon_b200.mark_grad_ready(p)
 
     def read_back():
         result_host.copy_(probe.detach().view(-1)[:1].float(), non_blocking=True)

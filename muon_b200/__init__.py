@@ -6,7 +6,7 @@ importing this package fails if that library has not been built.
 """
 from ._lib import MuonB200Error, device_status  # noqa: F401  (import fails loudly without the library)
 from .checkpoint import consolidated_state_dict, load_consolidated_state_dict  # noqa: F401
-from .engine import get_backend, get_ns_mode, set_ns_mode  # noqa: F401
+from .engine import get_backend, get_ns_mode, mark_grad_ready, set_ns_mode  # noqa: F401
 from .ops import (  # noqa: F401
     adam_update,
     muon_update,
@@ -27,4 +27,5 @@ __all__ = [
     "muon_update", "adam_update", "zeropower_via_newtonschulz5",
     "ns_line_1", "ns_line_2", "ns_line_3",
     "set_ns_mode", "get_ns_mode", "get_backend", "device_status", "MuonB200Error",
+    "mark_grad_ready", "consolidated_state_dict", "load_consolidated_state_dict",
 ]

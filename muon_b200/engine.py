@@ -49,6 +49,39 @@ def get_ns_mode() -> tuple[str, int]:
     return _ns_mode, _ns_steps
 
 
+# Gradients that are produced on another stream than the one step() runs on (copied in from
+# host memory, reduced by a communication stream, written by a backward stream): the event that
+# completes when the gradient holds its value, keyed by the gradient's address.
+_grad_ready: dict[int, "torch.cuda.Event"] = {}
+
+
+def mark_grad_ready(tensor: Tensor, event: "torch.cuda.Event | None" = None) -> None:
+    """Tell the engine that `tensor` (a gradient, or a parameter, meaning its ``.grad``) gets its
+    value from work enqueued on the CURRENT stream up to this call (or by `event`, if given).
+
+    ``step()`` may then be called from another stream without waiting for that stream: the engine
+    makes the first kernel that reads the gradient wait for the event, launch group by launch
+    group, so Newton-Schulz of the gradients that arrived first runs while later ones are still
+    in flight. Gradients without a mark are assumed ready in the order of step()'s own stream,
+    which is the reference's behaviour. A mark is consumed by the step that uses it."""
+    g = tensor.grad if isinstance(tensor, torch.nn.Parameter) and tensor.grad is not None else tensor
+    _require_cuda(g, "gradient")
+    if event is None:
+        event = torch.cuda.Event()
+        event.record(torch.cuda.current_stream(g.device))
+    _grad_ready[g.data_ptr()] = event
+
+
+def _wait_grads(stream, grads: Sequence[Tensor]) -> None:
+    """Make `stream` wait for the readiness events of `grads` (those that have one)."""
+    if not _grad_ready:
+        return
+    for g in grads:
+        ev = _grad_ready.pop(g.data_ptr(), None)
+        if ev is not None:
+            stream.wait_event(ev)
+
+
 def _stream_ptr(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
@@ -212,6 +245,7 @@ class CudaBackend:
             for s, e in zip(bounds[:-1], bounds[1:]):
                 layout = _lib.ns_layout(e - s, m_, n_)
                 ws = self.workspace(dev, layout.total_bytes)
+                _wait_grads(torch.cuda.current_stream(dev), grads[s:e])
                 check(lib.muon_b200_muon_step(
                     ptr_array([p.data_ptr() for p in params[s:e]]),
                     ptr_array([g.data_ptr() for g in grads[s:e]]),
@@ -251,6 +285,7 @@ class CudaBackend:
             def prologue(i):
                 s, e = groups[i]
                 l = layouts[i]
+                _wait_grads(side, grads[s:e])
                 check(lib.muon_b200_prologue(
                     ptr_array([g.data_ptr() for g in grads[s:e]]), ptr_array([m.data_ptr() for m in moms[s:e]]),
                     e - s, rows, cols, code, beta, 1 if nesterov else 0, ws_ptr[i % 2] + l.x_offset_bytes,
@@ -305,6 +340,7 @@ class CudaBackend:
                 raise ValueError("adam_step needs contiguous tensors")
         dev = params[0].device
         with torch.cuda.device(dev):
+            _wait_grads(torch.cuda.current_stream(dev), grads)
             check(lib.muon_b200_adam(
                 ptr_array([p.data_ptr() for p in params]), ptr_array([g.data_ptr() for g in grads]),
                 ptr_array([m.data_ptr() for m in exp_avgs]), ptr_array([v.data_ptr() for v in exp_avg_sqs]),

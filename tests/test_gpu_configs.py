@@ -89,10 +89,23 @@ def test_batched_conv_filters(mb):
         assert p.shape == r.shape and orc.rel_fro(p.detach().cpu(), r) <= 1e-3
 
 
-@pytest.mark.parametrize("shape", [(4096, 14336), (14336, 4096), (4096, 4096), (1024, 4096)])
-def test_llama3_8b_shapes_properties(mb, shape):
-    """Full-size bf16 matrices, grads ~N(0, 1e-3): the update must be orthogonal up to the band the
-    live algorithm guarantees, scale-invariant in the gradient, and deterministic."""
+def _spectral_norm_sym(S, iters=40):
+    """Largest |eigenvalue| of a symmetric matrix by power iteration (a lower bound that converges
+    from below; an SVD of an 8192 x 8192 matrix would take most of a minute)."""
+    v = torch.ones(S.shape[0], 1, device=S.device) / S.shape[0] ** 0.5
+    v = v + 1e-3 * torch.randn(v.shape, device=S.device, generator=torch.Generator(device=S.device).manual_seed(1))
+    for _ in range(iters):
+        w = S @ (S @ v)
+        v = w / w.norm()
+    return (S @ v).norm().item()
+
+
+@pytest.mark.parametrize("shape", [(4096, 14336), (14336, 4096), (4096, 4096), (1024, 4096),
+                                   (8192, 28672), (28672, 8192), (8192, 8192), (1024, 8192)])
+def test_llama3_shapes_properties(mb, shape):
+    """Full-size bf16 matrices of the Llama-3-8B and -70B layers, grads ~N(0, 1e-3): the update must
+    be orthogonal up to the band the live algorithm guarantees, scale-invariant in the gradient,
+    and deterministic."""
     g = torch.Generator(device=DEV).manual_seed(4000)
     G = torch.empty(shape, device=DEV, dtype=torch.bfloat16).normal_(0, 1e-3, generator=g)
     U = mb.zeropower_via_newtonschulz5(G)
@@ -102,10 +115,10 @@ def test_llama3_8b_shapes_properties(mb, shape):
     eye = torch.eye(gram.shape[0], device=DEV)
     if shape[0] != shape[1]:
         # singular values within [0.98, 1.02] -> eigenvalues of the Gram matrix within ~[0.96, 1.04]
-        dev = torch.linalg.matrix_norm(gram - eye, ord=2).item()
+        dev = _spectral_norm_sym(gram - eye)
         assert dev < 0.05, dev
     else:
-        assert torch.linalg.matrix_norm(gram, ord=2).item() < 1.2
+        assert _spectral_norm_sym(gram) < 1.2
     # alignment with the input: <U, G> equals the nuclear norm of G for the exact polar factor
     assert (Uf * G.float()).sum().item() > 0
     # NS normalises its input, so a power-of-two rescaling of G (exact in bf16) changes nothing
@@ -115,3 +128,46 @@ def test_llama3_8b_shapes_properties(mb, shape):
     # a square input is iterated as it is, so the identity only holds up to rounding there)
     if shape[0] != shape[1]:
         assert torch.equal(mb.zeropower_via_newtonschulz5(G.T.contiguous()), U.T)
+
+
+def test_gradients_arriving_on_a_copy_stream(mb):
+    """Gradients copied in from pinned host memory on a side stream and marked with
+    mark_grad_ready: step() called at once from the main stream gives bitwise the result of a step
+    whose gradients were resident before it started, for Muon and for Adam parameters."""
+    g = torch.Generator().manual_seed(77)
+    shapes = [(512, 1024)] * 24 + [(1024, 256)] * 8
+    p0 = [torch.randn(s, generator=g) * 0.02 for s in shapes]
+    grads = [[torch.randn(s, generator=g).pin_memory() for s in shapes] for _ in range(2)]
+    gain0 = torch.ones(4096)
+    gain_grads = [torch.randn(4096, generator=g).pin_memory() for _ in range(2)]
+
+    def make():
+        ps = [torch.nn.Parameter(p.clone().to(DEV)) for p in p0]
+        gain = torch.nn.Parameter(gain0.clone().to(DEV))
+        opt = mb.SingleDeviceMuonWithAuxAdam([dict(params=ps, use_muon=True, lr=0.02, weight_decay=0.01),
+                                              dict(params=[gain], use_muon=False, lr=1e-3)])
+        return ps + [gain], opt
+
+    ref_params, ref_opt = make()
+    params, opt = make()
+    copy_stream = torch.cuda.Stream()
+    for step in range(2):
+        host = grads[step] + [gain_grads[step]]
+        for p, h in zip(ref_params, host):
+            p.grad = h.to(DEV)
+        torch.cuda.synchronize()
+        ref_opt.step()
+        for p in params:
+            if p.grad is None:
+                p.grad = torch.empty_like(p)
+        copy_stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(copy_stream):
+            for p, h in zip(params, host):
+                p.grad.copy_(h, non_blocking=True)
+                mb.mark_grad_ready(p)
+        opt.step()  # no synchronisation with copy_stream other than the marks
+        torch.cuda.synchronize()
+        for p, r in zip(params, ref_params):
+            assert torch.equal(p, r)
+    from muon_b200 import engine
+    assert not engine._grad_ready  # every mark was consumed
