@@ -20,11 +20,11 @@
 // instead stores every computed tile and then its transpose (muon.py:534-544): its
 // output for a non-symmetric A depends on tile shape and store order.
 //
-// Roles inside a CTA (192 threads):
+// Roles inside a CTA (64 + 32 * EW threads, EW = 4, 8 or 16 epilogue warps):
 //   warp 0      TMA producer: fills a ring of {A tile, B tile} stages in shared memory
 //   warp 1      MMA issuer: tcgen05.mma, K = 16 per instruction, accumulators double-buffered
 //               in TMEM (2 x 256 columns)
-//   warps 2..5  epilogue: tcgen05.ld -> fp32 epilogue -> bf16 stores (+ mirrored stores)
+//   warps 2..   epilogue: tcgen05.ld -> fp32 epilogue -> bf16 stores (+ mirrored stores)
 // The grid is persistent: each CTA (or CTA pair) walks tiles w, w + stride, ...
 #include "common.cuh"
 #include "ns_gemm.h"
@@ -57,7 +57,8 @@ constexpr int BN = 256;  // UMMA N
 constexpr int BK = 64;   // one 128-byte swizzle span of bf16
 constexpr int UMMA_K = 16;
 constexpr int TMEM_COLS = 512;  // two 256-column fp32 accumulators
-constexpr int NUM_THREADS = 192;
+// Threads of a CTA with EW epilogue warps (warp 0 = TMA producer, warp 1 = MMA issuer).
+__host__ __device__ constexpr int num_threads(int epi_warps) { return 64 + 32 * epi_warps; }
 constexpr int SMEM_BARRIER_BYTES = 256;
 
 // CTAS = 1: one CTA computes a 128 x 256 tile (tcgen05.mma.cta_group::1, M = 128).
@@ -124,28 +125,35 @@ __host__ __device__ constexpr uint32_t make_idesc(bool b_mn_major, int mma_m) {
 // ---------------------------------------------------------------------------
 // Epilogue helpers. Thread owns one output row `r` and 32 consecutive columns.
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ void load_row32(const __nv_bfloat16* src, int col0, int ncols,
-                                           float (&dst)[32]) {
-  // src points at (r, 0). Vector path when the whole span is in range (16-byte aligned
-  // because leading dimensions and col0 are multiples of 8).
+// 32 columns of the row `src` points at, as packed bf16 pairs, not yet converted: issued one chunk
+// ahead so that the global-memory latency passes while the previous chunk is converted and
+// stored. Vector path when the whole span is in range (16-byte aligned because leading
+// dimensions and col0 are multiples of 8).
+__device__ __forceinline__ void load_row32_raw(const __nv_bfloat16* src, int col0, int ncols,
+                                               uint32_t (&raw)[16]) {
   if (col0 + 32 <= ncols) {
     const uint4* v = reinterpret_cast<const uint4*>(src + col0);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      uint4 q = __ldg(v + i);
-      uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        dst[i * 8 + j * 2] = bf16_bits_to_float(w[j] & 0xffffu);
-        dst[i * 8 + j * 2 + 1] = bf16_bits_to_float(w[j] >> 16);
-      }
+      const uint4 q = __ldg(v + i);
+      raw[4 * i] = q.x; raw[4 * i + 1] = q.y; raw[4 * i + 2] = q.z; raw[4 * i + 3] = q.w;
     }
   } else {
+    const unsigned short* s = reinterpret_cast<const unsigned short*>(src);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      int c = col0 + j;
-      dst[j] = (c < ncols) ? __bfloat162float(src[c]) : 0.f;
+    for (int j = 0; j < 16; ++j) {
+      const int c = col0 + 2 * j;
+      const uint32_t lo = (c < ncols) ? __ldg(s + c) : 0u;
+      const uint32_t hi = (c + 1 < ncols) ? __ldg(s + c + 1) : 0u;
+      raw[j] = lo | (hi << 16);
     }
+  }
+}
+__device__ __forceinline__ void unpack_row32(const uint32_t (&raw)[16], float (&dst)[32]) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    dst[2 * j] = bf16_bits_to_float(raw[j] & 0xffffu);
+    dst[2 * j + 1] = bf16_bits_to_float(raw[j] >> 16);
   }
 }
 
@@ -170,8 +178,9 @@ __device__ __forceinline__ void store_row32(__nv_bfloat16* dst, int col0, int co
   }
 }
 
-template <int MODE, bool B_MN, int CTAS>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+// ADD: how line 2's addend is formed (AddendMode); the other two lines pass ADD_SYMMETRIC.
+template <int MODE, bool B_MN, int CTAS, int EW, int ADD>
+__global__ void __launch_bounds__(num_threads(EW), 1)
 ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const GemmParams p) {
   using C = Cfg<CTAS>;
@@ -206,7 +215,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4 * CTAS);  // one arrival per epilogue warp of every CTA
+      mbar_init(tempty_bar(a), EW * CTAS);  // one arrival per epilogue warp of every CTA
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
@@ -353,7 +362,15 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   } else {
     // -------------------------------- epilogue --------------------------------
-    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    // A warp may only read the TMEM lanes of quarter (warp id % 4). With EW = 4 * PARTS epilogue
+    // warps every quarter is served by PARTS warps, each taking a share of the tile's columns.
+    // Each scheduler of the SM then interleaves PARTS epilogue warps: with a single one, the
+    // dependent-instruction latency of the conversion and store code is fully exposed and a
+    // short-K tile's epilogue takes several times longer than its MMAs.
+    constexpr int PARTS = EW / 4;
+    constexpr int CHUNKS = (BN / 32) / PARTS;  // 32-column chunks per warp and tile
+    const int q = warp & 3;
+    const int c_begin = ((warp - 2) >> 2) * CHUNKS;
     int local = 0;
     for (int t = work0; t < total_tiles; t += work_stride, ++local) {
       const TileCoord tc = decode_tile<TILE_M>(t, p);
@@ -384,103 +401,151 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const __nv_bfloat16* add_row =
           (MODE == MODE_SYRK) ? nullptr : add_b + static_cast<long long>(r) * p.ldadd;
 
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      // A chunk is worked on when it is inside the matrix and, for the triangular products, not
+      // strictly above the diagonal for every row of this warp (both tests are warp-uniform).
+      auto chunk_live = [&](int c) {
         const int col0 = tc.tn * BN + c * 32;
-        if (col0 >= p.N) break;                               // uniform: past the right edge
-        if (MODE != MODE_BX && col0 > r_warp_max) break;      // uniform: strictly above diagonal
+        return col0 < p.N && (MODE == MODE_BX || col0 <= r_warp_max);
+      };
+      // Addend of the chunk about to be processed, fetched one chunk ahead.
+      uint32_t add_raw[MODE == MODE_SYRK ? 1 : 16];
+      if constexpr (MODE != MODE_SYRK) {
+        if (row_ok && chunk_live(c_begin))
+          load_row32_raw(add_row, tc.tn * BN + c_begin * 32, p.N, add_raw);
+      }
+
+#pragma unroll 1
+      for (int c = c_begin; c < c_begin + CHUNKS; ++c) {
+        if (!chunk_live(c)) break;
+        const int col0 = tc.tn * BN + c * 32;
         uint32_t v[32];
         __syncwarp();  // tcgen05.ld is warp-collective: reconverge after the predicated stores
         tmem_ld_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, v);
+        uint32_t add_next[MODE == MODE_SYRK ? 1 : 16];
+        const bool more = MODE != MODE_SYRK && row_ok && c + 1 < c_begin + CHUNKS && chunk_live(c + 1);
+        if constexpr (MODE != MODE_SYRK) {
+          if (more) load_row32_raw(add_row, col0 + 32, p.N, add_next);
+        }
         tmem_ld_wait();
         if (!row_ok) continue;
 
         float f[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-
-        // mirror[j]: value for position (col, r) when it differs from the direct one.
-        float mirror[MODE == MODE_AXPBY ? 32 : 1];
-        if (MODE == MODE_AXPBY) {
-          float a[32];
-          load_row32(add_row, col0, p.N, a);
-          if (p.sym_add == ADD_SYMMETRIC) {
+        float a[MODE == MODE_SYRK ? 1 : 32];
+        if constexpr (MODE != MODE_SYRK) {
+          unpack_row32(add_raw, a);
+          if (more) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) f[j] = fmaf(a[j], p.beta, f[j] * p.alpha);
-          } else if (p.sym_add == ADD_ROW_SCALED) {
+            for (int j = 0; j < 16; ++j) add_raw[j] = add_next[j];
+          }
+        }
+
+        // f keeps the product term (alpha * acc for line 2) so that the mirrored element can be
+        // formed from it at store time; `packed` receives the value of position (r, col).
+        uint32_t packed[16];
+        float w_r = 0.f;                 // ADD_ROW_SCALED: 1/s of this thread's row
+        const float* wv = nullptr;       // ADD_ROW_SCALED: the 1/s vector of this matrix
+        if constexpr (MODE == MODE_AXPBY) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] *= p.alpha;
+          if constexpr (ADD == ADD_ROW_SCALED) {
             // The addend is S * w (rows scaled by w = 1/s), S symmetric and given unscaled:
             // position (r, col) takes bf16(S[r,col] * w[r]) and its mirror bf16(S[r,col] * w[col]),
             // bit for bit what the materialised scaled matrix holds at (r, col) and (col, r).
-            const float* wv = p.row_scale + static_cast<long long>(tc.batch) * p.scale_bs;
-            const float w_r = wv[r];
-            float w_c[32];
-            if (col0 + 32 <= p.N) {
-              const float4* w4 = reinterpret_cast<const float4*>(wv + col0);
+            wv = p.row_scale + static_cast<long long>(tc.batch) * p.scale_bs;
+            w_r = wv[r];
 #pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const float4 q4 = __ldg(w4 + i);
-                w_c[4 * i] = q4.x; w_c[4 * i + 1] = q4.y; w_c[4 * i + 2] = q4.z; w_c[4 * i + 3] = q4.w;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) w_c[j] = (col0 + j < p.N) ? __ldg(wv + col0 + j) : 0.f;
-            }
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float prod = f[j] * p.alpha;
-              const float direct = __bfloat162float(__float2bfloat16_rn(a[j] * w_r));
-              const float mirrored = __bfloat162float(__float2bfloat16_rn(a[j] * w_c[j]));
-              f[j] = fmaf(direct, p.beta, prod);
-              mirror[j] = fmaf(mirrored, p.beta, prod);
+            for (int j = 0; j < 16; ++j) {
+              const float d0 = __bfloat162float(__float2bfloat16_rn(a[2 * j] * w_r));
+              const float d1 = __bfloat162float(__float2bfloat16_rn(a[2 * j + 1] * w_r));
+              packed[j] = pack_bf16x2(fmaf(d0, p.beta, f[2 * j]), fmaf(d1, p.beta, f[2 * j + 1]));
             }
           } else {
-            // The product alpha*A*A^T is symmetric, the addend beta*A need not be: the
-            // mirrored position takes its own addend A[col, r].
-            const unsigned short* add_s = reinterpret_cast<const unsigned short*>(add_b);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int col = col0 + j;
-              const float prod = f[j] * p.alpha;
-              f[j] = fmaf(a[j], p.beta, prod);
-              float at = 0.f;
-              if (col < r && col < p.N)
-                at = bf16_bits_to_float(__ldg(add_s + static_cast<long long>(col) * p.ldadd + r));
-              mirror[j] = fmaf(at, p.beta, prod);
-            }
+            for (int j = 0; j < 16; ++j)
+              packed[j] = pack_bf16x2(fmaf(a[2 * j], p.beta, f[2 * j]), fmaf(a[2 * j + 1], p.beta, f[2 * j + 1]));
           }
-        } else if (MODE == MODE_BX) {
-          float a[32];
-          load_row32(add_row, col0, p.N, a);
+        } else if constexpr (MODE == MODE_BX) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) f[j] = fmaf(a[j], p.alpha, f[j]);
+          for (int j = 0; j < 16; ++j)
+            packed[j] = pack_bf16x2(fmaf(a[2 * j], p.alpha, f[2 * j]), fmaf(a[2 * j + 1], p.alpha, f[2 * j + 1]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) packed[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
         }
 
-        uint32_t packed[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) packed[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
-
-        if (MODE == MODE_BX) {
+        if constexpr (MODE == MODE_BX) {
           store_row32(out_row, col0, p.N, packed);
         } else {
           // Lower triangle (col <= r) is stored from here.
           int col_end = r + 1 < p.N ? r + 1 : p.N;
           store_row32(out_row, col0, col_end, packed);
-          // Mirror: element (r, col) with col < r also lands at (col, r). Lanes hold
-          // consecutive r, so each of these stores is a contiguous run across the warp.
-          unsigned short* out_s = reinterpret_cast<unsigned short*>(out_b);
-          const bool own_mirror = (MODE == MODE_AXPBY) && p.sym_add != ADD_SYMMETRIC;
+
+          // Mirror: element (r, col) with col < r also lands at (col, r). `mp` holds the values
+          // for the mirrored positions; they differ from `packed` only when line 2's addend is
+          // not symmetric.
+          uint32_t mp[16];
+          bool mirror_is_direct = true;
+          if constexpr (MODE == MODE_AXPBY) {
+            if constexpr (ADD == ADD_ROW_SCALED) {
+              mirror_is_direct = false;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int col = col0 + j;
-            if (col < r && col < p.N) {
-              unsigned short bits;
-              if (own_mirror) {
-                bits = __bfloat16_as_ushort(__float2bfloat16_rn(mirror[MODE == MODE_AXPBY ? j : 0]));
-              } else {
-                const uint32_t w = packed[j >> 1];
-                bits = static_cast<unsigned short>((j & 1) ? (w >> 16) : (w & 0xffffu));
+              for (int j = 0; j < 16; ++j) {
+                // w[col] is the same address for every lane: one broadcast load.
+                const int col = col0 + 2 * j;
+                const float w0 = col < p.N ? __ldg(wv + col) : 0.f;
+                const float w1 = col + 1 < p.N ? __ldg(wv + col + 1) : 0.f;
+                const float m0 = __bfloat162float(__float2bfloat16_rn(a[2 * j] * w0));
+                const float m1 = __bfloat162float(__float2bfloat16_rn(a[2 * j + 1] * w1));
+                mp[j] = pack_bf16x2(fmaf(m0, p.beta, f[2 * j]), fmaf(m1, p.beta, f[2 * j + 1]));
               }
-              out_s[static_cast<long long>(col) * p.ldo + r] = bits;
+            } else if constexpr (ADD == ADD_GENERIC) {
+              // The product alpha*A*A^T is symmetric, the addend beta*A need not be: the
+              // mirrored position takes its own addend A[col, r].
+              mirror_is_direct = false;
+              const unsigned short* add_s = reinterpret_cast<const unsigned short*>(add_b);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int col = col0 + 2 * j;
+                float t0 = 0.f, t1 = 0.f;
+                if (col < r && col < p.N)
+                  t0 = bf16_bits_to_float(__ldg(add_s + static_cast<long long>(col) * p.ldadd + r));
+                if (col + 1 < r && col + 1 < p.N)
+                  t1 = bf16_bits_to_float(__ldg(add_s + static_cast<long long>(col + 1) * p.ldadd + r));
+                mp[j] = pack_bf16x2(fmaf(t0, p.beta, f[2 * j]), fmaf(t1, p.beta, f[2 * j + 1]));
+              }
+            }
+          }
+          if (mirror_is_direct) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) mp[j] = packed[j];
+          }
+
+          unsigned short* out_s = reinterpret_cast<unsigned short*>(out_b);
+          if (col0 + 32 <= row_base && col0 + 32 <= p.N && r_warp_max < p.M) {
+            // The whole 32 x 32 block is strictly below the diagonal and inside the matrix (the
+            // same for every lane). Neighbouring lanes hold neighbouring rows, that is, adjacent
+            // elements of a mirrored row: each lane pair swaps one packed word so that the even
+            // lane stores rows (r, r+1) of column col0+2j and the odd lane those of col0+2j+1,
+            // four bytes per store instead of two.
+            const bool odd = lane & 1;
+            unsigned short* dst = out_s + static_cast<long long>(col0 + (odd ? 1 : 0)) * p.ldo + (r & ~1);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const uint32_t other = __shfl_xor_sync(0xffffffffu, mp[j], 1);
+              const uint32_t word = odd ? __byte_perm(other, mp[j], 0x7632) : __byte_perm(mp[j], other, 0x5410);
+              *reinterpret_cast<uint32_t*>(dst + static_cast<long long>(2 * j) * p.ldo) = word;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = col0 + j;
+              if (col < r && col < p.N) {
+                const uint32_t w = mp[j >> 1];
+                out_s[static_cast<long long>(col) * p.ldo + r] =
+                    static_cast<unsigned short>((j & 1) ? (w >> 16) : (w & 0xffffu));
+              }
             }
           }
         }
@@ -553,11 +618,12 @@ int encode_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, i
   return OK;
 }
 
+constexpr int kKernelSlots = 3 * 2 * 3 * 3;  // mode x CTAs per tile x epilogue warps x addend mode
 struct DeviceInfo {
   int sm_count = 0;
   int cc_major = 0;
-  bool attr_set[6] = {false, false, false, false, false, false};
-  int max_clusters[6] = {0, 0, 0, 0, 0, 0};
+  bool attr_set[kKernelSlots] = {};
+  int max_clusters[kKernelSlots] = {};
 };
 DeviceInfo g_dev[64];
 std::mutex g_dev_mu;
@@ -577,16 +643,27 @@ int forced_ctas() {
 // progress while a GEMM runs (a collective's copy kernels in the distributed step).
 std::atomic<int> g_reserved_sms{0};
 
-template <int MODE, bool B_MN, int CTAS>
+// Epilogue warps forced by the environment variable MUON_B200_NS_EPI_WARPS (4, 8 or 16; read
+// once; meant for A/B measurements), 0 = pick per launch.
+int forced_epi_warps() {
+  static int v = [] {
+    const char* e = std::getenv("MUON_B200_NS_EPI_WARPS");
+    int x = e ? std::atoi(e) : 0;
+    return (x == 4 || x == 8 || x == 16) ? x : 0;
+  }();
+  return v;
+}
+
+template <int MODE, bool B_MN, int CTAS, int EW, int ADD>
 int launch_instance(int dev, int sms, const CUtensorMap& ta, const CUtensorMap& tb,
                     const GemmParams& p, cudaStream_t stream) {
   using C = Cfg<CTAS>;
-  auto kern = ns_gemm_kernel<MODE, B_MN, CTAS>;
-  const int slot = MODE * 2 + (CTAS - 1);
+  auto kern = ns_gemm_kernel<MODE, B_MN, CTAS, EW, ADD>;
+  const int slot = ((MODE * 2 + (CTAS - 1)) * 3 + (EW == 4 ? 0 : EW == 8 ? 1 : 2)) * 3 + ADD;
   const long long total = (long long)p.tiles_per_batch * p.batch;
 
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.blockDim = dim3(num_threads(EW));
   cfg.dynamicSmemBytes = C::SMEM_TOTAL;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -629,13 +706,34 @@ int launch_instance(int dev, int sms, const CUtensorMap& ta, const CUtensorMap& 
     const double flops = MODE == MODE_BX ? 2.0 * m * k * n * b : m * (m + 1.0) * k * b;
     const int64_t tag = ((int64_t)p.M << 40) | ((int64_t)(MODE == MODE_BX ? p.N : p.K) << 16) | ((int64_t)(p.batch & 0xfff) << 4) |
                         (p.sym_add == ADD_SYMMETRIC ? 1 : 0) | (CTAS == 2 ? 2 : 0) |
-                        (p.sym_add == ADD_ROW_SCALED ? 4 : 0);
+                        (p.sym_add == ADD_ROW_SCALED ? 4 : 0) | (EW >= 8 ? 8 : 0);
     LaunchScope scope(MODE == MODE_SYRK ? K_NS_LINE1 : MODE == MODE_AXPBY ? K_NS_LINE2 : K_NS_LINE3,
                       flops, stream, tag);
     MB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, ta, tb, p));
   }
   MB_CUDA_CHECK(cudaGetLastError());
   return OK;
+}
+
+constexpr int kDefaultEpiWarps = 8;
+
+template <int MODE, bool B_MN, int CTAS>
+int launch_epi(int ew, int dev, int sms, const CUtensorMap& ta, const CUtensorMap& tb,
+               const GemmParams& p, cudaStream_t stream) {
+  if constexpr (MODE == MODE_AXPBY) {
+    if (p.sym_add == ADD_ROW_SCALED)
+      return ew == 4 ? launch_instance<MODE, B_MN, CTAS, 4, ADD_ROW_SCALED>(dev, sms, ta, tb, p, stream)
+                     : launch_instance<MODE, B_MN, CTAS, 8, ADD_ROW_SCALED>(dev, sms, ta, tb, p, stream);
+    if (p.sym_add == ADD_GENERIC)
+      return ew == 4 ? launch_instance<MODE, B_MN, CTAS, 4, ADD_GENERIC>(dev, sms, ta, tb, p, stream)
+                     : launch_instance<MODE, B_MN, CTAS, 8, ADD_GENERIC>(dev, sms, ta, tb, p, stream);
+    return ew == 4 ? launch_instance<MODE, B_MN, CTAS, 4, ADD_SYMMETRIC>(dev, sms, ta, tb, p, stream)
+                   : launch_instance<MODE, B_MN, CTAS, 8, ADD_SYMMETRIC>(dev, sms, ta, tb, p, stream);
+  } else {
+    if (ew == 4) return launch_instance<MODE, B_MN, CTAS, 4, ADD_SYMMETRIC>(dev, sms, ta, tb, p, stream);
+    if (ew == 16) return launch_instance<MODE, B_MN, CTAS, 16, ADD_SYMMETRIC>(dev, sms, ta, tb, p, stream);
+    return launch_instance<MODE, B_MN, CTAS, 8, ADD_SYMMETRIC>(dev, sms, ta, tb, p, stream);
+  }
 }
 
 }  // namespace
@@ -742,17 +840,20 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
   if ((long long)p.tiles_per_batch * batch > (1ll << 30))
     return set_error(ERR_UNSUPPORTED, "too many output tiles");
 
+  int ew = forced_epi_warps();
+  if (ew == 0) ew = kDefaultEpiWarps;
+  if (mode == MODE_AXPBY && ew > 8) ew = 8;  // line 2's epilogue needs more registers per thread
   if (ctas == 2) {
     switch (mode) {
-      case MODE_SYRK: return launch_instance<MODE_SYRK, false, 2>(dev, sms, ta, tb, p, stream);
-      case MODE_AXPBY: return launch_instance<MODE_AXPBY, false, 2>(dev, sms, ta, tb, p, stream);
-      default: return launch_instance<MODE_BX, true, 2>(dev, sms, ta, tb, p, stream);
+      case MODE_SYRK: return launch_epi<MODE_SYRK, false, 2>(ew, dev, sms, ta, tb, p, stream);
+      case MODE_AXPBY: return launch_epi<MODE_AXPBY, false, 2>(ew, dev, sms, ta, tb, p, stream);
+      default: return launch_epi<MODE_BX, true, 2>(ew, dev, sms, ta, tb, p, stream);
     }
   }
   switch (mode) {
-    case MODE_SYRK: return launch_instance<MODE_SYRK, false, 1>(dev, sms, ta, tb, p, stream);
-    case MODE_AXPBY: return launch_instance<MODE_AXPBY, false, 1>(dev, sms, ta, tb, p, stream);
-    default: return launch_instance<MODE_BX, true, 1>(dev, sms, ta, tb, p, stream);
+    case MODE_SYRK: return launch_epi<MODE_SYRK, false, 1>(ew, dev, sms, ta, tb, p, stream);
+    case MODE_AXPBY: return launch_epi<MODE_AXPBY, false, 1>(ew, dev, sms, ta, tb, p, stream);
+    default: return launch_epi<MODE_BX, true, 1>(ew, dev, sms, ta, tb, p, stream);
   }
 }
 
