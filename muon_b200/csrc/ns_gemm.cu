@@ -20,7 +20,7 @@
 // instead stores every computed tile and then its transpose (muon.py:534-544): its
 // output for a non-symmetric A depends on tile shape and store order.
 //
-// Roles inside a CTA (64 + 32 * EW threads, EW = 4, 8 or 16 epilogue warps):
+// Roles inside a CTA (64 + 32 * EW threads, EW = 4 or 8 epilogue warps):
 //   warp 0      TMA producer: fills a ring of {A tile, B tile} stages in shared memory
 //   warp 1      MMA issuer: tcgen05.mma, K = 16 per instruction, accumulators double-buffered
 //               in TMEM (2 x 256 columns)
@@ -74,7 +74,10 @@ struct Cfg {
   static constexpr int A_STAGE_BYTES = BM * BK * 2;       // 16 KiB
   static constexpr int B_STAGE_BYTES = B_ROWS * BK * 2;   // 32 / 16 KiB
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-  static constexpr int SMEM_TOTAL = STAGES * STAGE_BYTES + SMEM_BARRIER_BYTES + 1024;  // + align
+  // operand ring + barriers + one epilogue staging buffer per epilogue warp + alignment slack
+  static constexpr int smem_total(int epi_warps) {
+    return STAGES * STAGE_BYTES + SMEM_BARRIER_BYTES + epi_warps * 32 * 64 + 1024;
+  }
 };
 
 struct TileCoord {
@@ -178,6 +181,75 @@ __device__ __forceinline__ void store_row32(__nv_bfloat16* dst, int col0, int co
   }
 }
 
+// ---------------------------------------------------------------------------
+// Per-warp staging buffer: 32 rows x 64 bytes of shared memory, the four 16-byte pieces of a
+// row XOR-swizzled by the row pair. The accumulator arrives with one row per thread, so a
+// thread's 64 bytes of a row are contiguous but the rows of a warp are a pitch apart: stored
+// straight from registers, every 16-byte store instruction touches 32 different lines. Passing
+// the block through this buffer changes the mapping to four lanes per row, eight rows per
+// instruction (8 x 64 contiguous bytes), for the stores and for the addend loads alike.
+//   "row"  pattern: lane l owns row l, pieces 0..3
+//   "coal" pattern: instruction i, lane l -> row 8i + l/4, piece l%4
+// Both patterns are free of bank conflicts with this swizzle.
+// ---------------------------------------------------------------------------
+constexpr int STAGING_BYTES_PER_WARP = 32 * 64;
+
+__device__ __forceinline__ uint32_t stage_addr(uint32_t base, int row, int piece) {
+  return base + row * 64 + ((piece ^ ((row >> 1) & 3)) << 4);
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+__device__ __forceinline__ void lds128(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) {
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr)
+               : "memory");
+}
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void stage_put_row(uint32_t base, int lane, const uint32_t (&w)[16]) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+    sts128(stage_addr(base, lane, k), w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
+}
+__device__ __forceinline__ void stage_get_row(uint32_t base, int lane, uint32_t (&w)[16]) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+    lds128(stage_addr(base, lane, k), w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
+}
+__device__ __forceinline__ void stage_put_coal(uint32_t base, int lane, const uint32_t (&w)[16]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    sts128(stage_addr(base, 8 * i + (lane >> 2), lane & 3), w[4 * i], w[4 * i + 1], w[4 * i + 2],
+           w[4 * i + 3]);
+}
+__device__ __forceinline__ void stage_get_coal(uint32_t base, int lane, uint32_t (&w)[16]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    lds128(stage_addr(base, 8 * i + (lane >> 2), lane & 3), w[4 * i], w[4 * i + 1], w[4 * i + 2],
+           w[4 * i + 3]);
+}
+// A 32 x 32 bf16 block at (row0, col0) of a matrix with pitch ld, in the "coal" pattern. The
+// block must lie inside the matrix; col0 is a multiple of 32 and ld of 8, so every access is
+// 16-byte aligned.
+__device__ __forceinline__ void block_load_coal(const __nv_bfloat16* base, long long ld, int row0,
+                                                int col0, int lane, uint32_t (&w)[16]) {
+  const __nv_bfloat16* ptr = base + (row0 + (lane >> 2)) * ld + col0 + (lane & 3) * 8;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint4 q = __ldg(reinterpret_cast<const uint4*>(ptr + 8 * i * ld));
+    w[4 * i] = q.x; w[4 * i + 1] = q.y; w[4 * i + 2] = q.z; w[4 * i + 3] = q.w;
+  }
+}
+__device__ __forceinline__ void block_store_coal(__nv_bfloat16* base, long long ld, int row0, int col0,
+                                                 int lane, const uint32_t (&w)[16]) {
+  __nv_bfloat16* ptr = base + (row0 + (lane >> 2)) * ld + col0 + (lane & 3) * 8;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    *reinterpret_cast<uint4*>(ptr + 8 * i * ld) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+}
+
 // ADD: how line 2's addend is formed (AddendMode); the other two lines pass ADD_SYMMETRIC.
 template <int MODE, bool B_MN, int CTAS, int EW, int ADD>
 __global__ void __launch_bounds__(num_threads(EW), 1)
@@ -197,6 +269,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
   const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
+  const uint32_t stage_area = bar_base + SMEM_BARRIER_BYTES;  // EW staging buffers of the epilogue
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(
       smem_gen + STAGES * C::STAGE_BYTES + 8 * (2 * STAGES + 4));
@@ -407,34 +480,57 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int col0 = tc.tn * BN + c * 32;
         return col0 < p.N && (MODE == MODE_BX || col0 <= r_warp_max);
       };
-      // Addend of the chunk about to be processed, fetched one chunk ahead.
-      uint32_t add_raw[MODE == MODE_SYRK ? 1 : 16];
+      // Global memory is accessed through the staging buffer when the chunk's whole 32 x 32 block
+      // lies inside the matrix (warp-uniform); ragged edges use one row per thread.
+      const bool rows_full = r_warp_max < p.M;
+      auto chunk_full = [&](int c) { return rows_full && tc.tn * BN + c * 32 + 32 <= p.N; };
+      const uint32_t stage = stage_area + (warp - 2) * STAGING_BYTES_PER_WARP;
+
+      // Addend of the chunk about to be processed, fetched one chunk ahead ("coal" pattern for
+      // a full chunk, this thread's own row otherwise). (Two buffers taking turns instead of the
+      // copy below were measured: no faster, and 25 registers more.)
+      uint32_t add_raw[MODE == MODE_SYRK ? 1 : 16] = {};
       if constexpr (MODE != MODE_SYRK) {
-        if (row_ok && chunk_live(c_begin))
-          load_row32_raw(add_row, tc.tn * BN + c_begin * 32, p.N, add_raw);
+        if (chunk_live(c_begin)) {
+          const int col0 = tc.tn * BN + c_begin * 32;
+          if (chunk_full(c_begin)) block_load_coal(add_b, p.ldadd, row_base, col0, lane, add_raw);
+          else if (row_ok) load_row32_raw(add_row, col0, p.N, add_raw);
+        }
       }
 
 #pragma unroll 1
       for (int c = c_begin; c < c_begin + CHUNKS; ++c) {
         if (!chunk_live(c)) break;
         const int col0 = tc.tn * BN + c * 32;
+        const bool full = chunk_full(c);
         uint32_t v[32];
         __syncwarp();  // tcgen05.ld is warp-collective: reconverge after the predicated stores
         tmem_ld_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, v);
-        uint32_t add_next[MODE == MODE_SYRK ? 1 : 16];
-        const bool more = MODE != MODE_SYRK && row_ok && c + 1 < c_begin + CHUNKS && chunk_live(c + 1);
+        uint32_t add_next[MODE == MODE_SYRK ? 1 : 16] = {};
+        const bool more = MODE != MODE_SYRK && c + 1 < c_begin + CHUNKS && chunk_live(c + 1);
         if constexpr (MODE != MODE_SYRK) {
-          if (more) load_row32_raw(add_row, col0 + 32, p.N, add_next);
+          if (more) {
+            if (chunk_full(c + 1)) block_load_coal(add_b, p.ldadd, row_base, col0 + 32, lane, add_next);
+            else if (row_ok) load_row32_raw(add_row, col0 + 32, p.N, add_next);
+          }
         }
         tmem_ld_wait();
-        if (!row_ok) continue;
 
         float f[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
         float a[MODE == MODE_SYRK ? 1 : 32];
         if constexpr (MODE != MODE_SYRK) {
-          unpack_row32(add_raw, a);
+          if (full) {
+            uint32_t own[16];
+            stage_put_coal(stage, lane, add_raw);
+            __syncwarp();
+            stage_get_row(stage, lane, own);
+            __syncwarp();
+            unpack_row32(own, a);
+          } else {
+            unpack_row32(add_raw, a);
+          }
           if (more) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) add_raw[j] = add_next[j];
@@ -454,7 +550,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // position (r, col) takes bf16(S[r,col] * w[r]) and its mirror bf16(S[r,col] * w[col]),
             // bit for bit what the materialised scaled matrix holds at (r, col) and (col, r).
             wv = p.row_scale + static_cast<long long>(tc.batch) * p.scale_bs;
-            w_r = wv[r];
+            w_r = row_ok ? wv[r] : 0.f;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const float d0 = __bfloat162float(__float2bfloat16_rn(a[2 * j] * w_r));
@@ -476,12 +572,17 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
 
         if constexpr (MODE == MODE_BX) {
-          store_row32(out_row, col0, p.N, packed);
+          if (full) {
+            uint32_t w[16];
+            stage_put_row(stage, lane, packed);
+            __syncwarp();
+            stage_get_coal(stage, lane, w);
+            __syncwarp();
+            block_store_coal(out_b, p.ldo, row_base, col0, lane, w);
+          } else if (row_ok) {
+            store_row32(out_row, col0, p.N, packed);
+          }
         } else {
-          // Lower triangle (col <= r) is stored from here.
-          int col_end = r + 1 < p.N ? r + 1 : p.N;
-          store_row32(out_row, col0, col_end, packed);
-
           // Mirror: element (r, col) with col < r also lands at (col, r). `mp` holds the values
           // for the mirrored positions; they differ from `packed` only when line 2's addend is
           // not symmetric.
@@ -509,9 +610,9 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               for (int j = 0; j < 16; ++j) {
                 const int col = col0 + 2 * j;
                 float t0 = 0.f, t1 = 0.f;
-                if (col < r && col < p.N)
+                if (row_ok && col < r && col < p.N)
                   t0 = bf16_bits_to_float(__ldg(add_s + static_cast<long long>(col) * p.ldadd + r));
-                if (col + 1 < r && col + 1 < p.N)
+                if (row_ok && col + 1 < r && col + 1 < p.N)
                   t1 = bf16_bits_to_float(__ldg(add_s + static_cast<long long>(col + 1) * p.ldadd + r));
                 mp[j] = pack_bf16x2(fmaf(t0, p.beta, f[2 * j]), fmaf(t1, p.beta, f[2 * j + 1]));
               }
@@ -522,22 +623,36 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             for (int j = 0; j < 16; ++j) mp[j] = packed[j];
           }
 
-          unsigned short* out_s = reinterpret_cast<unsigned short*>(out_b);
-          if (col0 + 32 <= row_base && col0 + 32 <= p.N && r_warp_max < p.M) {
-            // The whole 32 x 32 block is strictly below the diagonal and inside the matrix (the
-            // same for every lane). Neighbouring lanes hold neighbouring rows, that is, adjacent
-            // elements of a mirrored row: each lane pair swaps one packed word so that the even
-            // lane stores rows (r, r+1) of column col0+2j and the odd lane those of col0+2j+1,
-            // four bytes per store instead of two.
-            const bool odd = lane & 1;
-            unsigned short* dst = out_s + static_cast<long long>(col0 + (odd ? 1 : 0)) * p.ldo + (r & ~1);
+          if (full && col0 + 32 <= row_base) {
+            // The whole block is strictly below the diagonal (the same for every lane): it is
+            // stored as it is, and its transpose goes to (col0, row_base). For the transpose
+            // neighbouring lanes, which hold neighbouring rows, swap one packed word per column
+            // pair, so that the even lane holds rows (r, r+1) of column col0+2j and the odd lane
+            // those of column col0+2j+1; these words are written into the buffer as rows col0+2j
+            // and col0+2j+1 of the transposed block.
+            uint32_t w[16];
+            stage_put_row(stage, lane, packed);
+            __syncwarp();
+            stage_get_coal(stage, lane, w);
+            __syncwarp();
+            block_store_coal(out_b, p.ldo, row_base, col0, lane, w);
+            const int odd = lane & 1;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const uint32_t other = __shfl_xor_sync(0xffffffffu, mp[j], 1);
               const uint32_t word = odd ? __byte_perm(other, mp[j], 0x7632) : __byte_perm(mp[j], other, 0x5410);
-              *reinterpret_cast<uint32_t*>(dst + static_cast<long long>(2 * j) * p.ldo) = word;
+              sts32(stage_addr(stage, 2 * j + odd, lane >> 3) + ((lane & 6) << 1), word);
             }
-          } else {
+            __syncwarp();
+            stage_get_coal(stage, lane, w);
+            __syncwarp();
+            block_store_coal(out_b, p.ldo, col0, row_base, lane, w);
+          } else if (row_ok) {
+            // Blocks on the diagonal and ragged edges: one row per thread, the lower triangle
+            // (col <= r) from its own position, the elements with col < r also to (col, r).
+            int col_end = r + 1 < p.N ? r + 1 : p.N;
+            store_row32(out_row, col0, col_end, packed);
+            unsigned short* out_s = reinterpret_cast<unsigned short*>(out_b);
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const int col = col0 + j;
@@ -618,7 +733,7 @@ int encode_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, i
   return OK;
 }
 
-constexpr int kKernelSlots = 3 * 2 * 3 * 3;  // mode x CTAs per tile x epilogue warps x addend mode
+constexpr int kKernelSlots = 3 * 2 * 2 * 3;  // mode x CTAs per tile x epilogue warps x addend mode
 struct DeviceInfo {
   int sm_count = 0;
   int cc_major = 0;
@@ -643,13 +758,13 @@ int forced_ctas() {
 // progress while a GEMM runs (a collective's copy kernels in the distributed step).
 std::atomic<int> g_reserved_sms{0};
 
-// Epilogue warps forced by the environment variable MUON_B200_NS_EPI_WARPS (4, 8 or 16; read
+// Epilogue warps forced by the environment variable MUON_B200_NS_EPI_WARPS (4 or 8; read
 // once; meant for A/B measurements), 0 = pick per launch.
 int forced_epi_warps() {
   static int v = [] {
     const char* e = std::getenv("MUON_B200_NS_EPI_WARPS");
     int x = e ? std::atoi(e) : 0;
-    return (x == 4 || x == 8 || x == 16) ? x : 0;
+    return (x == 4 || x == 8) ? x : 0;
   }();
   return v;
 }
@@ -659,12 +774,12 @@ int launch_instance(int dev, int sms, const CUtensorMap& ta, const CUtensorMap& 
                     const GemmParams& p, cudaStream_t stream) {
   using C = Cfg<CTAS>;
   auto kern = ns_gemm_kernel<MODE, B_MN, CTAS, EW, ADD>;
-  const int slot = ((MODE * 2 + (CTAS - 1)) * 3 + (EW == 4 ? 0 : EW == 8 ? 1 : 2)) * 3 + ADD;
+  const int slot = ((MODE * 2 + (CTAS - 1)) * 2 + (EW == 4 ? 0 : 1)) * 3 + ADD;
   const long long total = (long long)p.tiles_per_batch * p.batch;
 
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(num_threads(EW));
-  cfg.dynamicSmemBytes = C::SMEM_TOTAL;
+  cfg.dynamicSmemBytes = C::smem_total(EW);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -679,7 +794,7 @@ int launch_instance(int dev, int sms, const CUtensorMap& ta, const CUtensorMap& 
     std::lock_guard<std::mutex> lk(g_dev_mu);
     if (!g_dev[dev].attr_set[slot]) {
       MB_CUDA_CHECK(
-          cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_TOTAL));
+          cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_total(EW)));
       if (CTAS == 2) {
         cfg.gridDim = dim3(sms / 2 * 2);
         int n = 0;
@@ -731,7 +846,6 @@ int launch_epi(int ew, int dev, int sms, const CUtensorMap& ta, const CUtensorMa
                    : launch_instance<MODE, B_MN, CTAS, 8, ADD_SYMMETRIC>(dev, sms, ta, tb, p, stream);
   } else {
     if (ew == 4) return launch_instance<MODE, B_MN, CTAS, 4, ADD_SYMMETRIC>(dev, sms, ta, tb, p, stream);
-    if (ew == 16) return launch_instance<MODE, B_MN, CTAS, 16, ADD_SYMMETRIC>(dev, sms, ta, tb, p, stream);
     return launch_instance<MODE, B_MN, CTAS, 8, ADD_SYMMETRIC>(dev, sms, ta, tb, p, stream);
   }
 }
@@ -842,7 +956,6 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
 
   int ew = forced_epi_warps();
   if (ew == 0) ew = kDefaultEpiWarps;
-  if (mode == MODE_AXPBY && ew > 8) ew = 8;  // line 2's epilogue needs more registers per thread
   if (ctas == 2) {
     switch (mode) {
       case MODE_SYRK: return launch_epi<MODE_SYRK, false, 2>(ew, dev, sms, ta, tb, p, stream);
