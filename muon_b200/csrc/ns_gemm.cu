@@ -830,7 +830,7 @@ int launch_instance(int dev, int sms, const CUtensorMap& ta, const CUtensorMap& 
   return OK;
 }
 
-constexpr int kDefaultEpiWarps = 8;
+constexpr int kLongK = 2048;  // from this K on, four epilogue warps (see launch_ns_gemm)
 
 template <int MODE, bool B_MN, int CTAS>
 int launch_epi(int ew, int dev, int sms, const CUtensorMap& ta, const CUtensorMap& tb,
@@ -955,7 +955,11 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
     return set_error(ERR_UNSUPPORTED, "too many output tiles");
 
   int ew = forced_epi_warps();
-  if (ew == 0) ew = kDefaultEpiWarps;
+  // With a long K the MMAs of the next tile hide the epilogue even with four warps, and the
+  // smaller CTA leaves room on the SM (registers, 8 KiB of shared memory) for the HBM-bound
+  // kernels that the engine runs beside the GEMMs. With a short K the epilogue is what a tile
+  // waits for: eight warps.
+  if (ew == 0) ew = K >= kLongK ? 4 : 8;
   if (ctas == 2) {
     switch (mode) {
       case MODE_SYRK: return launch_epi<MODE_SYRK, false, 2>(ew, dev, sms, ta, tb, p, stream);
