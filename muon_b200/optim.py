@@ -132,9 +132,17 @@ def _distributed_muon_group_step(optimizer, group) -> None:
             chunk = _next_chunk(params, owned, done_upto, backend)
             _muon_update_params(optimizer, chunk, group)
             done_upto += len(chunk)
-        if world > 1:  # with one rank the gather would copy each parameter onto itself
-            pending.append(dist.all_gather(params_pad[base_i:base_i + world], params_pad[mine],
-                                           async_op=True))
+        window = params_pad[base_i:base_i + world]
+        if all(w.shape == window[0].shape and w.dtype == window[0].dtype for w in window):
+            pending.append(dist.all_gather(window, params_pad[mine], async_op=True))
+        else:
+            # A window that mixes shapes (the sort puts 3072x768 before 768x3072, and a class
+            # whose count the world size does not divide spills into the next one): all_gather
+            # needs equal sizes (the reference fails here, muon.py:68), so every real parameter
+            # of the window is broadcast from its owner instead. Pad entries carry no data.
+            for r, w in enumerate(window):
+                if base_i + r < len(params):
+                    pending.append(dist.broadcast(w, src=r, async_op=True))
     for work in pending:
         if work is not None:
             work.wait()

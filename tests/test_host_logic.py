@@ -243,6 +243,22 @@ def test_distributed_muon_on_gloo_ranks(tmp_path, world, with_adam):
         assert not torch.equal(g0[0], torch.ones(8))
 
 
+@pytest.mark.parametrize("world,shapes", [
+    (2, [(48, 24)] * 3 + [(24, 48)] * 3 + [(16, 16)]),          # a middle window mixes two shapes
+    (3, [(48, 24)] * 3 + [(24, 48)] + [(16, 16)]),              # the tail window mixes shapes and pads
+])
+def test_distributed_muon_with_mixed_shape_windows(tmp_path, world, shapes):
+    """Windows whose parameters differ in shape cannot go through one all_gather (the reference
+    raises there); they are exchanged by per-parameter broadcasts and give the single-device result."""
+    mp.spawn(_rank_main, args=(world, shapes, str(tmp_path), False), nprocs=world, join=True)
+    outs = [torch.load(f"{tmp_path}/out{r}.pt", weights_only=False) for r in range(world)]
+    ref = _single_device_oracle(shapes)
+    for r, o in enumerate(outs):
+        for p, q in zip(o["params"], ref):
+            assert torch.equal(p, q), f"rank {r} disagrees with the single-device result"
+        assert o["has_state"] == o["owned"]
+
+
 # ------------------------------------------- consolidated checkpoints across world sizes
 CKPT_SHAPES = [(24, 48)] * 6 + [(48, 24)] * 6
 
