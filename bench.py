@@ -55,9 +55,10 @@ WORKLOADS = {
 }
 NS_ITERS = 4  # the reference's live algorithm
 # DRAM bytes (read + write) per matrix element that one launch of the line-3 kernel moved in the
-# ncu capture summarised in profiles/ns_gemm_line3_llama3-8b-4layers.md: 3.723 GB for 8 matrices
-# of 4096 x 14336. Traffic of that kernel grows with the elements a launch covers.
-LINE3_DRAM_BYTES_PER_ELEMENT = 3.723e9 / (8 * 4096 * 14336)
+# ncu capture summarised in profiles/ns_gemm_line3_llama3-8b-4layers.md: 2.120 GB read + 0.925 GB
+# written for 8 matrices of 4096 x 14336. Traffic of that kernel grows with the elements a launch
+# covers.
+LINE3_DRAM_BYTES_PER_ELEMENT = 3.045e9 / (8 * 4096 * 14336)
 
 
 def as_matrices(shapes):
