@@ -48,6 +48,9 @@ WORKLOADS = {
                           "Llama-3-8B hidden weights, 4 of 32 layers, bf16 (small case for profiling)"),
     "llama3-70b-2layers": (LLAMA3_70B_LAYER * 2, torch.bfloat16, 1e-3,
                            "Llama-3-70B hidden weights, 2 of 80 layers, bf16 (the full set needs 8 GPUs)"),
+    "llama3-70b-40layers": (LLAMA3_70B_LAYER * 40, torch.bfloat16, 1e-3,
+                            "Llama-3-70B hidden weights, 40 of 80 layers, bf16 (replicated parameters of all 80 "
+                            "layers are 137 GB per GPU; meant for 8 GPUs)"),
     "gpt2-small-hidden": (GPT2_SMALL_LAYER * 12, torch.float32, 1e-2,
                           "GPT-2 small hidden weights, 72 matrices, fp32"),
     "conv-filters": ([(256, 256, 3, 3)] * 64 + [(128, 128, 3, 3)] * 64, torch.float32, 1.0,
@@ -300,7 +303,7 @@ def run_ours(args):
                          "launches": int(n3), "avg_launch_ms": ms3 / n3 if n3 else None,
                          # average DRAM bytes per launch, scaled from the ncu capture by elements covered
                          "traffic": (LINE3_DRAM_BYTES_PER_ELEMENT * sum(r * c for r, c in mats) * NS_ITERS
-                                     / world / (n3 / args.steps)) if n3 and args.workload.startswith("llama3") else None,
+                                     / world / (n3 / args.steps)) if n3 and args.workload.startswith("llama3-8b") else None,
                          "traffic_algorithmic": ((2 * sum(r * c for r, c in mats) + sum(min(r, c) ** 2 for r, c in mats))
                                                  * 2 * NS_ITERS / world / (n3 / args.steps)) if n3 else None,
                          "rank": 0},
@@ -337,7 +340,7 @@ def reference_sample(workload):
     shapes, dtype, grad_std, _ = WORKLOADS[workload]
     if workload.startswith("llama3"):
         sample = list(LLAMA3_8B_LAYER)
-        text = "one of the 32 layers (7 matrices); scaled to the full step by NS FLOPs"
+        text = "one Llama-3-8B layer (7 matrices; 1 of the 32); scaled to the full step by NS FLOPs"
     else:
         sample = [(768, 768)] * 4 + [(3072, 768), (768, 3072)]
         text = "one GPT-2 small layer (6 matrices); scaled to the full step by NS FLOPs"
