@@ -15,9 +15,18 @@ kernels are Triton kernels that need a GPU.  What pins this restatement:
   (``tests/golden/make_golden.py``), bit for bit;
 * the three GEMM lines are checked against the *real* reference Triton kernels run
   under Triton's CPU interpreter in fp32 (the interpreter cannot run them in bf16);
-* the bf16 Newton-Schulz driver as a whole has no executable reference on CPU:
-  for it **parity is unpinned** and rests on the line-by-line restatement below plus
-  the invariants (singular-value band) the algorithm guarantees.
+* the bf16 Newton-Schulz driver is checked against the *real* reference driver
+  (``zeropower_via_newtonschulz5``, run uncompiled on CPU) calling its real Triton kernels
+  under the interpreter, with the bf16 operands of every kernel call handed over as fp32 and
+  the fp32 result rounded to bf16 once: bit for bit on single-tile cases, call by call (12
+  kernel calls, at most one bf16 step apart on <0.1% of the elements, where fp32 sums taken
+  in another order round the other way) on a multi-tile case, with ``glue="eager"`` and
+  ``mirror="ref_square_tiles"``.  The defaults of this module (``glue="fused"``,
+  ``mirror="product"``: what the CUDA kernels implement) differ from that run by the two
+  documented choices; at 768x768 / 768x3072 by 8.0e-3 / 6.6e-3 relative Frobenius norm,
+  while the reference itself moves by 5.1e-3 / 4.1e-3 between 64- and 128-wide tiles.
+  What no CPU run can pin is the reference as a GPU executes it: compiled glue, autotuned
+  tile shapes and two racing stores on diagonal tiles.
 
 Every function cites the reference lines (``muon.py:<line>``) it follows.
 """
@@ -102,15 +111,20 @@ def ns_line_3(B: Tensor, X: Tensor, a: float) -> Tensor:
 # Newton-Schulz drivers
 # --------------------------------------------------------------------------------------
 def zeropower_via_newtonschulz5(G: Tensor, epsilon: float = 1e-7, *, mirror: str = "product",
-                                dtype: torch.dtype = torch.bfloat16) -> Tensor:
+                                dtype: torch.dtype = torch.bfloat16, glue: str = "fused") -> Tensor:
     """The live algorithm, muon.py:748-799: AOL rescale + 4 iterations.
 
     Rounding points (each ``.to(dtype)``): the cast (:760), every GEMM line's output,
     the row sums s (:779-781, a materialised bf16 tensor), X·rsqrt(s) (:782) and A/s
-    (:785).  The elementwise glue is evaluated in fp32 and rounded once per tensor,
-    which is how the reference's compiled graph evaluates it.
+    (:785).  ``glue="fused"`` (default, what the CUDA kernels implement) evaluates the
+    elementwise glue in fp32 and rounds once per tensor, which is how the reference's compiled
+    graph evaluates it.  ``glue="eager"`` rounds after every torch op (abs, sum, clamp, rsqrt,
+    multiply, divide), which is what the reference does when it runs uncompiled; with
+    ``mirror="ref_square_tiles"`` that variant reproduces the real reference driver executed
+    on CPU (its Triton kernels under the interpreter), which is what pins this function.
     """
     assert G.ndim in (2, 3)
+    assert glue in ("fused", "eager")
     X = G.to(dtype)
     tall = G.size(-2) > G.size(-1)
     if tall:
@@ -118,12 +132,17 @@ def zeropower_via_newtonschulz5(G: Tensor, epsilon: float = 1e-7, *, mirror: str
     X = X.contiguous()
     m1 = "lower" if mirror == "product" else mirror  # line 1's output is symmetric either way
     A = ns_line_1(X, mirror=m1)  # :778
-    s = torch.clamp_min(A.float().abs().sum(dim=-1, keepdim=True), epsilon).to(dtype)  # :779-781
-    X = (X.float() * torch.rsqrt(s.float())).to(dtype)  # :782
-    # :785 (rows only). The quotient is formed as A * (1/s) with a correctly rounded reciprocal:
-    # the reference's compiled division is itself approximate, and this form is the one the
-    # CUDA kernels can reproduce bit for bit in two places.
-    A = (A.float() * (1.0 / s.float())).to(dtype)
+    if glue == "eager":
+        s = torch.clamp_min(A.abs().sum(dim=-1, keepdim=True), epsilon)  # :779-781, every op in dtype
+        X = X * torch.rsqrt(s)  # :782
+        A = A / s  # :785
+    else:
+        s = torch.clamp_min(A.float().abs().sum(dim=-1, keepdim=True), epsilon).to(dtype)  # :779-781
+        X = (X.float() * torch.rsqrt(s.float())).to(dtype)  # :782
+        # :785 (rows only). The quotient is formed as A * (1/s) with a correctly rounded
+        # reciprocal: the reference's compiled division is itself approximate, and this form is
+        # the one the CUDA kernels can reproduce bit for bit in two places.
+        A = (A.float() * (1.0 / s.float())).to(dtype)
     for k, (a, b, c) in enumerate(AOL4_COEFFS):
         if k > 0:
             A = ns_line_1(X, mirror=m1)  # :792

@@ -2,13 +2,17 @@
 
 Run in a container that has the reference checked out:
 
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference [fixture names ...]
 
 What the real reference can execute without a GPU, and what each fixture therefore pins:
 
 * ``adam.pt``        real ``SingleDeviceMuonWithAuxAdam`` Adam groups, 3 steps (muon.py:104-109, :244-258).
 * ``ns_lines_fp32.pt`` the real Triton kernels ``ns_line_1/2/3`` under Triton's CPU interpreter, fp32
                      inputs, tile configs pinned to 64x64x64 (the interpreter cannot execute bf16).
+* ``ns_reference_bf16.pt`` the real ``zeropower_via_newtonschulz5`` driver run uncompiled on CPU, calling
+                     the real Triton kernels under the interpreter with bf16 operands passed as fp32 and
+                     each result rounded to bf16 once (see ``gen_ns_reference_bf16``); one case keeps the
+                     output of each of its 12 kernel calls.
 * ``muon_glue.pt``   real ``SingleDeviceMuon`` / ``muon_update`` (momentum lerps, Nesterov write-back,
                      4-D view, aspect scale, weight decay, apply; muon.py:8-15, :81-101) with
                      ``zeropower_via_newtonschulz5`` replaced by the oracle's restatement, because the
@@ -39,6 +43,15 @@ import muon as ref  # noqa: E402  the real reference module
 from oracle import muon_oracle as orc  # noqa: E402
 
 assert os.path.realpath(ref.__file__).startswith(os.path.realpath(ref_dir)), ref.__file__
+REAL_NS = ref.zeropower_via_newtonschulz5  # gen_muon_glue replaces the module attribute later
+
+
+def _pin_tiles():
+    """One 64 x 64 x 64 configuration per kernel: the autotuner needs a GPU to choose among several."""
+    for k in (ref.ns_line_1_kernel, ref.ns_line_2_kernel, ref.ns_line_3_kernel):
+        k.configs = [c for c in k.configs
+                     if c.kwargs["BLOCK_SIZE_M"] == 64 and c.kwargs["BLOCK_SIZE_N"] == 64
+                     and c.kwargs["BLOCK_SIZE_K"] == 64][:1]
 
 
 def gen_adam():
@@ -71,10 +84,7 @@ def gen_adam():
 
 
 def gen_ns_lines_fp32():
-    for k in (ref.ns_line_1_kernel, ref.ns_line_2_kernel, ref.ns_line_3_kernel):
-        k.configs = [c for c in k.configs
-                     if c.kwargs["BLOCK_SIZE_M"] == 64 and c.kwargs["BLOCK_SIZE_N"] == 64
-                     and c.kwargs["BLOCK_SIZE_K"] == 64][:1]
+    _pin_tiles()
     torch.manual_seed(5)
     cases = []
     for (m, n, batch) in [(96, 160, None), (64, 64, None), (130, 200, None), (72, 136, 2)]:
@@ -85,6 +95,59 @@ def gen_ns_lines_fp32():
         B = ref.ns_line_2(As, alpha=2.4635, beta=-7.0585)
         C = ref.ns_line_3(B, X, 4.0098)
         cases.append(dict(X=X, A=A, As=As, alpha=2.4635, beta=-7.0585, B=B, a=4.0098, C=C, tile=64))
+    return {"cases": cases}
+
+
+def gen_ns_reference_bf16():
+    """The real ``zeropower_via_newtonschulz5`` (muon.py:748-799) executed on CPU: its own driver
+    code (uncompiled, so every torch op rounds to bf16) calling its own Triton kernels under the
+    interpreter. The interpreter cannot compute in bf16, so each kernel call is given its bf16
+    operands converted to fp32 (exact) and its fp32 result is rounded to bf16 once — the kernels'
+    own semantics (fp32 accumulation, one rounding at the store, muon.py:404-405, :531-532,
+    :696-697). Every kernel call's output is recorded so that the restatement can be checked call
+    by call on the reference's own intermediate values."""
+    _pin_tiles()
+    trace = []
+    real = {n: getattr(ref, n) for n in ("ns_line_1", "ns_line_2", "ns_line_3")}
+
+    def through_fp32(name):
+        fn = real[name]
+
+        def wrapped(*args, out=None, **kw):
+            conv = [a.float().contiguous() if torch.is_tensor(a) else a for a in args]
+            res = fn(*conv, **kw).to(torch.bfloat16)
+            scalars = {k: v for k, v in kw.items()}
+            if name == "ns_line_3":
+                scalars["a"] = args[2]
+            trace.append(dict(name=name, scalars=scalars, out=res.clone(),
+                              inputs=[a.clone() for a in args if torch.is_tensor(a)]))
+            if out is not None:
+                out.copy_(res)
+                return out
+            return res
+        return wrapped
+
+    for n in real:
+        setattr(ref, n, through_fp32(n))
+    try:
+        torch.manual_seed(41)
+        cases = []
+        for shape, keep_trace in [((64, 160), False), ((160, 64), False), ((96, 96), False),
+                                  ((2, 72, 136), True), ((130, 200), False)]:
+            trace.clear()
+            G = torch.randn(shape).bfloat16()
+            U = REAL_NS(G)
+            case = dict(G=G, U=U.clone(), tile=64)
+            if keep_trace:
+                # Inputs of a call are outputs of earlier calls, except the rescaled X and A that the
+                # driver's own elementwise code produces (muon.py:779-785): keep those two.
+                case["outputs"] = [dict(name=t["name"], scalars=t["scalars"], out=t["out"]) for t in trace]
+                case["A_rescaled"] = trace[1]["inputs"][0]   # operand of the first ns_line_2
+                case["X_rescaled"] = trace[2]["inputs"][1]   # second operand of the first ns_line_3
+            cases.append(case)
+    finally:
+        for n, f in real.items():
+            setattr(ref, n, f)
     return {"cases": cases}
 
 
@@ -167,8 +230,12 @@ def gen_ns_oracle():
 
 
 if __name__ == "__main__":
+    only = sys.argv[2:]
     for name, fn in [("adam", gen_adam), ("ns_lines_fp32", gen_ns_lines_fp32), ("api", gen_api),
+                     ("ns_reference_bf16", gen_ns_reference_bf16),
                      ("ns_oracle_bf16", gen_ns_oracle), ("muon_glue", gen_muon_glue)]:
+        if only and name not in only:
+            continue
         data = fn()
         path = os.path.join(HERE, f"{name}.pt")
         torch.save(data, path)
