@@ -116,6 +116,28 @@ def test_newton_schulz_aol4(mb, shape):
         assert 0.95 < lo and hi < 1.05
 
 
+def test_newton_schulz_against_outputs_of_the_real_reference(mb, golden):
+    """Fixture `ns_reference_bf16`: outputs of the reference's own driver and kernels run on CPU
+    (tests/golden/make_golden.py). The kernels here follow the documented formula on diagonal
+    tiles and round the glue once, the fixture's run stores transposed diagonal tiles (64 wide)
+    and rounds after every op; on these one-to-three-tile matrices that is most of the matrix, so
+    the distance to the fixture must equal the oracle's own distance to it (the CUDA result sits
+    where the oracle's default sits), and both stay inside the same singular-value band."""
+    for c in golden("ns_reference_bf16")["cases"]:
+        G, U_ref = c["G"], c["U"]
+        U = mb.zeropower_via_newtonschulz5(G.to(DEV)).cpu()
+        O = orc.zeropower_via_newtonschulz5(G)
+        assert U.shape == U_ref.shape
+        d_cuda, d_oracle = orc.rel_fro(U, U_ref), orc.rel_fro(O, U_ref)
+        assert orc.rel_fro(U, O) <= 2e-2
+        assert d_cuda <= 8e-2 and abs(d_cuda - d_oracle) <= 1e-2, (tuple(G.shape), d_cuda, d_oracle)
+        lo, hi = orc.singular_value_band(U)
+        rlo, rhi = orc.singular_value_band(U_ref)
+        assert abs(hi - rhi) <= 0.03, ((lo, hi), (rlo, rhi))
+        if G.shape[-1] != G.shape[-2]:  # a square Gaussian matrix has singular values near zero
+            assert abs(lo - rlo) <= 0.05, ((lo, hi), (rlo, rhi))
+
+
 @pytest.mark.parametrize("shape", [(768, 3072), (3072, 768), (256, 2304), (96, 96)])
 def test_newton_schulz_classic5(mb, shape):
     g = torch.Generator().manual_seed(8)
