@@ -17,6 +17,8 @@ What the real reference can execute without a GPU, and what each fixture therefo
                      4-D view, aspect scale, weight decay, apply; muon.py:8-15, :81-101) with
                      ``zeropower_via_newtonschulz5`` replaced by the oracle's restatement, because the
                      real one needs a GPU. Inputs: fp32 wide, fp32 tall, bf16, 4-D filter with kH > kW.
+* ``distributed.pt`` real distributed ``Muon`` on two gloo CPU ranks (ownership, padding, all_gather,
+                     state on the owner only, a parameter without gradient), NS substituted as above.
 * ``api.pt``         constructor behaviour: sort order, group keys and defaults, assertion cases.
 * ``ns_oracle_bf16.pt`` the oracle's own bf16 Newton-Schulz output on seeded inputs (a drift guard for the
                      restatement itself; NOT produced by the reference).
@@ -229,10 +231,53 @@ def gen_ns_oracle():
     return {"cases": cases}
 
 
+DIST_SHAPES = [(24, 48)] * 4 + [(48, 24)] * 2 + [(16, 16)]
+DIST_WORLD = 2
+
+
+def _dist_rank(rank, world, tmpdir):
+    """One gloo rank of the real distributed ``Muon`` (muon.py:18-70)."""
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    dist.init_process_group("gloo", init_method=f"file://{tmpdir}/pg", rank=rank, world_size=world)
+    try:
+        ref.zeropower_via_newtonschulz5 = orc.zeropower_via_newtonschulz5  # as in gen_muon_glue
+        problem = torch.load(f"{tmpdir}/problem.pt")
+        params = [torch.nn.Parameter(p.clone()) for p in problem["p0"]]
+        opt = ref.Muon(list(params), lr=0.02, weight_decay=0.01, momentum=0.95)
+        for step_grads in problem["grads"]:
+            for i, (p, g) in enumerate(zip(params, step_grads)):
+                p.grad = None if i == problem["no_grad_index"] else g.clone()
+            opt.step()
+        sorted_params = opt.param_groups[0]["params"]
+        torch.save(dict(params=[p.detach().clone() for p in params],
+                        sorted_shapes=[tuple(p.shape) for p in sorted_params],
+                        has_state=[i for i, p in enumerate(sorted_params) if len(opt.state[p]) > 0]),
+                   f"{tmpdir}/out{rank}.pt")
+    finally:
+        dist.destroy_process_group()
+
+
+def gen_distributed():
+    """Real ``Muon`` on two gloo CPU ranks, shape-homogeneous windows (the reference's all_gather
+    rejects mixed ones), one parameter that never receives a gradient, a padded tail window."""
+    import tempfile
+    import torch.multiprocessing as mp
+    torch.manual_seed(61)
+    problem = dict(p0=[torch.randn(s) * 0.02 for s in DIST_SHAPES],
+                   grads=[[torch.randn(s) for s in DIST_SHAPES] for _ in range(2)], no_grad_index=1)
+    with tempfile.TemporaryDirectory() as tmp:
+        torch.save(problem, f"{tmp}/problem.pt")
+        mp.spawn(_dist_rank, args=(DIST_WORLD, tmp), nprocs=DIST_WORLD, join=True)
+        ranks = [torch.load(f"{tmp}/out{r}.pt") for r in range(DIST_WORLD)]
+    return dict(problem, world=DIST_WORLD, ranks=ranks, hyper=dict(lr=0.02, weight_decay=0.01, momentum=0.95))
+
+
 if __name__ == "__main__":
     only = sys.argv[2:]
     for name, fn in [("adam", gen_adam), ("ns_lines_fp32", gen_ns_lines_fp32), ("api", gen_api),
                      ("ns_reference_bf16", gen_ns_reference_bf16),
+                     ("distributed", gen_distributed),
                      ("ns_oracle_bf16", gen_ns_oracle), ("muon_glue", gen_muon_glue)]:
         if only and name not in only:
             continue

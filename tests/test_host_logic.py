@@ -263,6 +263,46 @@ def test_distributed_muon_with_mixed_shape_windows(tmp_path, world, shapes):
         assert o["has_state"] == o["owned"]
 
 
+def _fixture_rank(rank, world, tmpdir, fixture_path):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    dist.init_process_group("gloo", init_method=f"file://{tmpdir}/pg", rank=rank, world_size=world)
+    try:
+        import muon_b200 as mb
+        from muon_b200 import engine as E
+        E._set_backend_for_testing(OracleBackend())
+        fx = torch.load(fixture_path, weights_only=False)
+        params = [torch.nn.Parameter(p.clone()) for p in fx["p0"]]
+        opt = mb.Muon(list(params), **fx["hyper"])
+        for step_grads in fx["grads"]:
+            for i, (p, gr) in enumerate(zip(params, step_grads)):
+                p.grad = None if i == fx["no_grad_index"] else gr.clone()
+            opt.step()
+        sorted_params = opt.param_groups[0]["params"]
+        torch.save(dict(params=[p.detach().clone() for p in params],
+                        sorted_shapes=[tuple(p.shape) for p in sorted_params],
+                        has_state=[i for i, p in enumerate(sorted_params) if len(opt.state[p]) > 0]),
+                   f"{tmpdir}/out{rank}.pt")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_distributed_muon_matches_the_real_reference_class(tmp_path):
+    """Fixture `distributed`: the reference's own `Muon` run on two gloo ranks. Same parameters,
+    same gradients, same world size here: every rank must end with the same parameters bit for
+    bit, the same sort order and momentum state on the same (owned) parameters only."""
+    path = os.path.join(os.path.dirname(__file__), "golden", "distributed.pt")
+    fx = torch.load(path, weights_only=False)
+    world = fx["world"]
+    mp.spawn(_fixture_rank, args=(world, str(tmp_path), path), nprocs=world, join=True)
+    for r in range(world):
+        mine = torch.load(f"{tmp_path}/out{r}.pt", weights_only=False)
+        theirs = fx["ranks"][r]
+        assert mine["sorted_shapes"] == theirs["sorted_shapes"]
+        assert mine["has_state"] == theirs["has_state"]
+        for p, q in zip(mine["params"], theirs["params"]):
+            assert torch.equal(p, q)
+
+
 # ------------------------------------------- consolidated checkpoints across world sizes
 CKPT_SHAPES = [(24, 48)] * 6 + [(48, 24)] * 6
 
