@@ -17,6 +17,8 @@ What the real reference can execute without a GPU, and what each fixture therefo
                      4-D view, aspect scale, weight decay, apply; muon.py:8-15, :81-101) with
                      ``zeropower_via_newtonschulz5`` replaced by the oracle's restatement, because the
                      real one needs a GPU. Inputs: fp32 wide, fp32 tall, bf16, 4-D filter with kH > kW.
+* ``config1_reference.pt`` real ``SingleDeviceMuon`` for 3 steps on one fp32 768 x 3072 parameter with the real
+                     Newton-Schulz driver and kernels executed as for ``ns_reference_bf16.pt``; rows kept.
 * ``distributed.pt`` real distributed ``Muon`` on two gloo CPU ranks (ownership, padding, all_gather,
                      state on the owner only, a parameter without gradient), NS substituted as above.
 * ``api.pt``         constructor behaviour: sort order, group keys and defaults, assertion cases.
@@ -100,57 +102,107 @@ def gen_ns_lines_fp32():
     return {"cases": cases}
 
 
-def gen_ns_reference_bf16():
-    """The real ``zeropower_via_newtonschulz5`` (muon.py:748-799) executed on CPU: its own driver
-    code (uncompiled, so every torch op rounds to bf16) calling its own Triton kernels under the
-    interpreter. The interpreter cannot compute in bf16, so each kernel call is given its bf16
-    operands converted to fp32 (exact) and its fp32 result is rounded to bf16 once — the kernels'
-    own semantics (fp32 accumulation, one rounding at the store, muon.py:404-405, :531-532,
-    :696-697). Every kernel call's output is recorded so that the restatement can be checked call
-    by call on the reference's own intermediate values."""
-    _pin_tiles()
-    trace = []
-    real = {n: getattr(ref, n) for n in ("ns_line_1", "ns_line_2", "ns_line_3")}
+class kernels_through_fp32:
+    """While active, the reference's ``ns_line_1/2/3`` launchers receive their bf16 operands
+    converted to fp32 (exact) and their fp32 result is rounded to bf16 once — the kernels' own
+    semantics (fp32 accumulation, one rounding at the store, muon.py:404-405, :531-532, :696-697),
+    executable by the Triton interpreter, which cannot compute in bf16. Every call is recorded."""
 
-    def through_fp32(name):
-        fn = real[name]
+    NAMES = ("ns_line_1", "ns_line_2", "ns_line_3")
 
+    def __init__(self, keep_inputs=False):
+        self.trace, self.keep_inputs = [], keep_inputs
+
+    def _wrap(self, name, fn):
         def wrapped(*args, out=None, **kw):
             conv = [a.float().contiguous() if torch.is_tensor(a) else a for a in args]
             res = fn(*conv, **kw).to(torch.bfloat16)
-            scalars = {k: v for k, v in kw.items()}
+            scalars = dict(kw)
             if name == "ns_line_3":
                 scalars["a"] = args[2]
-            trace.append(dict(name=name, scalars=scalars, out=res.clone(),
-                              inputs=[a.clone() for a in args if torch.is_tensor(a)]))
+            rec = dict(name=name, scalars=scalars, out=res.clone())
+            if self.keep_inputs:
+                rec["inputs"] = [a.clone() for a in args if torch.is_tensor(a)]
+            self.trace.append(rec)
             if out is not None:
                 out.copy_(res)
                 return out
             return res
         return wrapped
 
-    for n in real:
-        setattr(ref, n, through_fp32(n))
-    try:
+    def __enter__(self):
+        _pin_tiles()
+        self.real = {n: getattr(ref, n) for n in self.NAMES}
+        self.real_ns = ref.zeropower_via_newtonschulz5
+        for n, f in self.real.items():
+            setattr(ref, n, self._wrap(n, f))
+        ref.zeropower_via_newtonschulz5 = REAL_NS
+        return self
+
+    def __exit__(self, *exc):
+        for n, f in self.real.items():
+            setattr(ref, n, f)
+        ref.zeropower_via_newtonschulz5 = self.real_ns
+
+
+def gen_ns_reference_bf16():
+    """The real ``zeropower_via_newtonschulz5`` (muon.py:748-799) executed on CPU: its own driver
+    code (uncompiled, so every torch op rounds to bf16) calling its own Triton kernels under the
+    interpreter (see ``kernels_through_fp32``). For one case every kernel call's output is kept, so
+    that the restatement can be checked call by call on the reference's own intermediate values."""
+    with kernels_through_fp32(keep_inputs=True) as k:
         torch.manual_seed(41)
         cases = []
         for shape, keep_trace in [((64, 160), False), ((160, 64), False), ((96, 96), False),
                                   ((2, 72, 136), True), ((130, 200), False)]:
-            trace.clear()
+            k.trace.clear()
             G = torch.randn(shape).bfloat16()
             U = REAL_NS(G)
             case = dict(G=G, U=U.clone(), tile=64)
             if keep_trace:
                 # Inputs of a call are outputs of earlier calls, except the rescaled X and A that the
                 # driver's own elementwise code produces (muon.py:779-785): keep those two.
-                case["outputs"] = [dict(name=t["name"], scalars=t["scalars"], out=t["out"]) for t in trace]
-                case["A_rescaled"] = trace[1]["inputs"][0]   # operand of the first ns_line_2
-                case["X_rescaled"] = trace[2]["inputs"][1]   # second operand of the first ns_line_3
+                case["outputs"] = [dict(name=t["name"], scalars=t["scalars"], out=t["out"]) for t in k.trace]
+                case["A_rescaled"] = k.trace[1]["inputs"][0]   # operand of the first ns_line_2
+                case["X_rescaled"] = k.trace[2]["inputs"][1]   # second operand of the first ns_line_3
             cases.append(case)
-    finally:
-        for n, f in real.items():
-            setattr(ref, n, f)
     return {"cases": cases}
+
+
+CONFIG1 = dict(shape=(768, 3072), seed=0, steps=3, lr=0.02, weight_decay=0.01, momentum=0.95, row_stride=96)
+
+
+def config1_problem():
+    """One fp32 parameter 768 x 3072 (randn * 0.02), gradients ~N(0, 1), seed 0: the first
+    configuration the benchmark definition lists. Regenerated from the seed by the tests."""
+    g = torch.Generator().manual_seed(CONFIG1["seed"])
+    p0 = torch.randn(CONFIG1["shape"], generator=g) * 0.02
+    grads = [torch.randn(CONFIG1["shape"], generator=g) for _ in range(CONFIG1["steps"])]
+    return p0, grads
+
+
+def gen_config1_reference():
+    """Real ``SingleDeviceMuon`` (muon.py:73-101) for three steps on that parameter with the real
+    Newton-Schulz driver and kernels (interpreter, see ``kernels_through_fp32``): momentum, Nesterov
+    blend, NS, aspect scale, weight decay and apply, all the reference's own code. Takes about a
+    quarter of an hour. Kept: every 96th row of the parameter, the momentum and the mutated
+    gradient after each step (the full tensors are 9 MB each), and norms of the full tensors."""
+    p0, grads = config1_problem()
+    s = CONFIG1["row_stride"]
+    p = torch.nn.Parameter(p0.clone())
+    steps = []
+    with kernels_through_fp32():
+        opt = ref.SingleDeviceMuon([p], lr=CONFIG1["lr"], weight_decay=CONFIG1["weight_decay"],
+                                   momentum=CONFIG1["momentum"])
+        for g in grads:
+            p.grad = g.clone()
+            opt.step()
+            mom = opt.state[p]["momentum_buffer"]
+            steps.append(dict(p_rows=p.detach()[::s].clone(), momentum_rows=mom[::s].clone(),
+                              grad_after_rows=p.grad[::s].clone(),
+                              p_norm=p.detach().double().norm().item(), momentum_norm=mom.double().norm().item()))
+            print("config1 step done", flush=True)
+    return dict(config=CONFIG1, p0_rows=p0[::s].clone(), grad_rows=[g[::s].clone() for g in grads], steps=steps)
 
 
 def gen_muon_glue():
@@ -277,7 +329,7 @@ if __name__ == "__main__":
     only = sys.argv[2:]
     for name, fn in [("adam", gen_adam), ("ns_lines_fp32", gen_ns_lines_fp32), ("api", gen_api),
                      ("ns_reference_bf16", gen_ns_reference_bf16),
-                     ("distributed", gen_distributed),
+                     ("distributed", gen_distributed), ("config1_reference", gen_config1_reference),
                      ("ns_oracle_bf16", gen_ns_oracle), ("muon_glue", gen_muon_glue)]:
         if only and name not in only:
             continue

@@ -378,3 +378,28 @@ def test_distributed_classes_world_size_one(mb, tmp_path):
         assert [tuple(p.shape) for p in oa.param_groups[0]["params"]] == sorted(shapes, reverse=True)
     finally:
         dist.destroy_process_group()
+
+
+def test_config1_three_steps_against_the_real_reference(mb, golden):
+    """`SingleDeviceMuon` on one fp32 768 x 3072 parameter for three steps, against what the real
+    reference (its classes, its Newton-Schulz driver and kernels, run on CPU) produced for the same
+    seeded parameter and gradients (fixture `config1_reference`): updated parameters within 1e-3
+    relative error, momentum and the in-place mutated gradient to fp32 rounding."""
+    fx = golden("config1_reference")
+    cfg = fx["config"]
+    g = torch.Generator().manual_seed(cfg["seed"])
+    p0 = torch.randn(cfg["shape"], generator=g) * 0.02
+    grads = [torch.randn(cfg["shape"], generator=g) for _ in range(cfg["steps"])]
+    s = cfg["row_stride"]
+    assert torch.equal(p0[::s], fx["p0_rows"]) and all(torch.equal(a[::s], r) for a, r in zip(grads, fx["grad_rows"]))
+    p = torch.nn.Parameter(p0.clone().to(DEV))
+    opt = mb.SingleDeviceMuon([p], lr=cfg["lr"], weight_decay=cfg["weight_decay"], momentum=cfg["momentum"])
+    for grad, step in zip(grads, fx["steps"]):
+        p.grad = grad.clone().to(DEV)
+        opt.step()
+        rows = p.detach()[::s].cpu()
+        assert orc.rel_fro(rows, step["p_rows"]) <= 1e-3
+        assert abs(p.detach().double().norm().item() / step["p_norm"] - 1) <= 1e-4
+        assert orc.rel_fro(rows - p0[::s], step["p_rows"] - p0[::s]) <= 2e-2  # the accumulated update alone
+        torch.testing.assert_close(opt.state[p]["momentum_buffer"][::s].cpu(), step["momentum_rows"], rtol=1e-5, atol=1e-7)
+        torch.testing.assert_close(p.grad[::s].cpu(), step["grad_after_rows"], rtol=1e-5, atol=1e-7)

@@ -176,3 +176,34 @@ def test_ownership_helpers():
     assert order[1] < order[2]  # stable
     assert orc.padded_length(8, 4) == 12 and orc.padded_length(7, 4) == 8
     assert [orc.owner_of(i, 4) for i in range(6)] == [0, 1, 2, 3, 0, 1]
+
+
+def config1_problem(cfg):
+    """The seeded parameter and gradients of tests/golden/make_golden.py:config1_problem."""
+    g = torch.Generator().manual_seed(cfg["seed"])
+    p0 = torch.randn(cfg["shape"], generator=g) * 0.02
+    grads = [torch.randn(cfg["shape"], generator=g) for _ in range(cfg["steps"])]
+    return p0, grads
+
+
+def test_config1_three_steps_match_the_real_reference(golden):
+    """One fp32 768 x 3072 parameter, three `SingleDeviceMuon` steps of the real reference with its
+    real Newton-Schulz driver and kernels (fixture `config1_reference`) against the restatement with
+    its defaults: parameters within 1e-3 relative error, momentum and the mutated gradient bit for
+    bit (neither depends on Newton-Schulz)."""
+    fx = golden("config1_reference")
+    cfg = fx["config"]
+    p0, grads = config1_problem(cfg)
+    s = cfg["row_stride"]
+    assert torch.equal(p0[::s], fx["p0_rows"]) and all(torch.equal(g[::s], r) for g, r in zip(grads, fx["grad_rows"]))
+    p, mom = p0.clone(), torch.zeros_like(p0)
+    for g, step in zip(grads, fx["steps"]):
+        g = g.clone()
+        orc.muon_param_step(p, g, mom, cfg["lr"], cfg["weight_decay"], cfg["momentum"])
+        assert torch.equal(mom[::s], step["momentum_rows"])
+        assert torch.equal(g[::s], step["grad_after_rows"])
+        assert orc.rel_fro(p[::s], step["p_rows"]) <= 1e-3
+        assert abs(p.double().norm().item() / step["p_norm"] - 1) <= 1e-4
+        # the update itself (what Newton-Schulz contributes), not diluted by the parameter
+        upd, upd_ref = p[::s] - p0[::s], step["p_rows"] - p0[::s]
+        assert orc.rel_fro(upd, upd_ref) <= 2e-2
