@@ -26,7 +26,11 @@ kernels are Triton kernels that need a GPU.  What pins this restatement:
   documented choices; at 768x768 / 768x3072 by 8.0e-3 / 6.6e-3 relative Frobenius norm,
   while the reference itself moves by 5.1e-3 / 4.1e-3 between 64- and 128-wide tiles.
   What no CPU run can pin is the reference as a GPU executes it: compiled glue, autotuned
-  tile shapes and two racing stores on diagonal tiles.
+  tile shapes and two racing stores on diagonal tiles;
+* ``muon_param_step`` end to end: three steps of the real ``SingleDeviceMuon`` with the real
+  Newton-Schulz driver and kernels (executed as above) on one fp32 768x3072 parameter; the
+  defaults of this module give the same parameters to 2e-4 relative;
+* the distributed class against the real ``Muon`` run on two gloo CPU ranks.
 
 Every function cites the reference lines (``muon.py:<line>``) it follows.
 """
