@@ -88,6 +88,10 @@ class PeerPush:
             self.close()
             return
         self.nbytes = [e[2] for e in exported]
+        # The peers hold the addresses exported above: a parameter whose storage is replaced later
+        # (`p.data = ...`, a `.to()` of the module) would silently stop receiving its updates.
+        self._params = list(params)
+        self._exported_ptrs = [p.data_ptr() for p in params]
         self._token = torch.zeros(1, device=self.device)
         self.index = {id(p): i for i, p in enumerate(params)}
         # Peers in the order r+1, r+2, ... so that ranks do not all start on the same receiver.
@@ -120,6 +124,12 @@ class PeerPush:
 
     def begin_step(self) -> None:
         """All ranks are inside step() (stream-ordered after their earlier work) from here on."""
+        for i, p in enumerate(self._params):
+            if p.data_ptr() != self._exported_ptrs[i]:
+                raise RuntimeError(
+                    f"muon_b200: the storage of parameter {i} {tuple(p.shape)} was replaced after the "
+                    "optimizer mapped it into the other ranks (copy-engine exchange); keep parameter "
+                    "storages in place, or set MUON_B200_EXCHANGE=nccl")
         dist.all_reduce(self._token)
 
     def push(self, updated, ready=None) -> None:
