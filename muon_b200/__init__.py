@@ -5,6 +5,7 @@ Drop-in for the public names of thib-s/Muon's ``muon`` module. All arithmetic ru
 importing this package fails if that library has not been built.
 """
 from ._lib import MuonB200Error, device_status  # noqa: F401  (import fails loudly without the library)
+from .backward_overlap import StepInBackward  # noqa: F401
 from .checkpoint import consolidated_state_dict, load_consolidated_state_dict  # noqa: F401
 from .engine import get_backend, get_ns_mode, mark_grad_ready, set_ns_mode  # noqa: F401
 from .ops import (  # noqa: F401
@@ -27,5 +28,5 @@ __all__ = [
     "muon_update", "adam_update", "zeropower_via_newtonschulz5",
     "ns_line_1", "ns_line_2", "ns_line_3",
     "set_ns_mode", "get_ns_mode", "get_backend", "device_status", "MuonB200Error",
-    "mark_grad_ready", "consolidated_state_dict", "load_consolidated_state_dict",
+    "mark_grad_ready", "StepInBackward", "consolidated_state_dict", "load_consolidated_state_dict",
 ]

@@ -357,3 +357,51 @@ def test_consolidated_checkpoint_survives_a_world_size_change(tmp_path):
         got = torch.load(f"{tmp_path}/final{r}.pt", weights_only=False)
         for p, q in zip(got, ref):
             assert torch.equal(p, q), f"rank {r} after resume differs from the uninterrupted run"
+
+
+# --------------------------------------------------- updates started from the backward pass
+def test_step_in_backward_gives_the_result_of_a_plain_step():
+    """StepInBackward starts the update of a same-shape set when the backward pass has delivered
+    its last gradient; parameters without gradient and Adam groups are finished in step(). The
+    result equals optimizer.step() after the backward pass, bit for bit, over three steps."""
+    import muon_b200 as mb
+    from muon_b200 import engine as E
+    prev = E._set_backend_for_testing(OracleBackend())
+    try:
+        shapes = [(24, 48)] * 3 + [(48, 24)] * 2 + [(16, 16)]
+        g = torch.Generator().manual_seed(3)
+        p0 = [torch.randn(s, generator=g) * 0.02 for s in shapes]
+        weights = [[torch.randn(s, generator=g) for s in shapes] for _ in range(3)]
+
+        def make():
+            ps = [torch.nn.Parameter(p.clone()) for p in p0]
+            gain = torch.nn.Parameter(torch.ones(8))
+            opt = mb.SingleDeviceMuonWithAuxAdam([dict(params=ps, use_muon=True, lr=0.02, weight_decay=0.01),
+                                                  dict(params=[gain], use_muon=False, lr=1e-3)])
+            return ps, gain, opt
+
+        def loss_of(ps, gain, w, skip):
+            # gradient of parameter i is w[i] * (sum of gain); parameter `skip` takes no part
+            return sum((p * wi).sum() for i, (p, wi) in enumerate(zip(ps, w)) if i != skip) * gain.sum()
+
+        ps_a, gain_a, opt_a = make()
+        ps_b, gain_b, opt_b = make()
+        overlap = mb.StepInBackward(opt_b)
+        for step, w in enumerate(weights):
+            skip = 1 if step == 1 else -1
+            for q in ps_a + [gain_a] + ps_b + [gain_b]:
+                q.grad = None
+            loss_of(ps_a, gain_a, w, skip).backward()
+            opt_a.step()
+            loss_of(ps_b, gain_b, w, skip).backward()
+            if skip < 0:  # every set was updated inside backward(): nothing is waiting
+                assert all(e["done"] for e in overlap._sets)
+            overlap.step()
+            for x, y in zip(ps_a + [gain_a], ps_b + [gain_b]):
+                assert torch.equal(x, y)
+        assert not torch.equal(ps_a[0], p0[0])
+        with pytest.raises(TypeError):
+            mb.StepInBackward(torch.optim.SGD([torch.nn.Parameter(torch.zeros(2))], lr=0.1))
+        overlap.remove()
+    finally:
+        E._set_backend_for_testing(prev)
