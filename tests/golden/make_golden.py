@@ -302,22 +302,40 @@ def _dist_rank(rank, world, tmpdir):
                 p.grad = None if i == problem["no_grad_index"] else g.clone()
             opt.step()
         sorted_params = opt.param_groups[0]["params"]
-        torch.save(dict(params=[p.detach().clone() for p in params],
-                        sorted_shapes=[tuple(p.shape) for p in sorted_params],
-                        has_state=[i for i, p in enumerate(sorted_params) if len(opt.state[p]) > 0]),
-                   f"{tmpdir}/out{rank}.pt")
+        out = dict(params=[p.detach().clone() for p in params],
+                   sorted_shapes=[tuple(p.shape) for p in sorted_params],
+                   has_state=[i for i, p in enumerate(sorted_params) if len(opt.state[p]) > 0])
+        # the same problem through MuonWithAuxAdam (muon.py:112-199), with 1-D gains in an Adam group
+        params = [torch.nn.Parameter(p.clone()) for p in problem["p0"]]
+        gains = [torch.nn.Parameter(g.clone()) for g in problem["gains0"]]
+        aux = ref.MuonWithAuxAdam([dict(params=list(params), use_muon=True, lr=0.02, weight_decay=0.01),
+                                   dict(params=gains, use_muon=False, lr=3e-3, weight_decay=0.01)])
+        for step_grads, gain_grads in zip(problem["grads"], problem["gain_grads"]):
+            for i, (p, g) in enumerate(zip(params, step_grads)):
+                p.grad = None if i == problem["no_grad_index"] else g.clone()
+            for q, g in zip(gains, gain_grads):
+                q.grad = g.clone()
+            aux.step()
+        sorted_params = aux.param_groups[0]["params"]
+        out["aux"] = dict(params=[p.detach().clone() for p in params], gains=[q.detach().clone() for q in gains],
+                          has_state=[i for i, p in enumerate(sorted_params) if len(aux.state[p]) > 0],
+                          adam_steps=[aux.state[q]["step"] for q in gains])
+        torch.save(out, f"{tmpdir}/out{rank}.pt")
     finally:
         dist.destroy_process_group()
 
 
 def gen_distributed():
-    """Real ``Muon`` on two gloo CPU ranks, shape-homogeneous windows (the reference's all_gather
-    rejects mixed ones), one parameter that never receives a gradient, a padded tail window."""
+    """Real ``Muon`` and real ``MuonWithAuxAdam`` on two gloo CPU ranks, shape-homogeneous windows
+    (the reference's all_gather rejects mixed ones), one parameter that never receives a gradient,
+    a padded tail window, two 1-D Adam parameters."""
     import tempfile
     import torch.multiprocessing as mp
     torch.manual_seed(61)
     problem = dict(p0=[torch.randn(s) * 0.02 for s in DIST_SHAPES],
                    grads=[[torch.randn(s) for s in DIST_SHAPES] for _ in range(2)], no_grad_index=1)
+    problem["gains0"] = [torch.ones(48), torch.randn(24)]
+    problem["gain_grads"] = [[torch.randn(48) * 0.1, torch.randn(24) * 0.1] for _ in range(2)]
     with tempfile.TemporaryDirectory() as tmp:
         torch.save(problem, f"{tmp}/problem.pt")
         mp.spawn(_dist_rank, args=(DIST_WORLD, tmp), nprocs=DIST_WORLD, join=True)

@@ -278,16 +278,30 @@ def _fixture_rank(rank, world, tmpdir, fixture_path):
                 p.grad = None if i == fx["no_grad_index"] else gr.clone()
             opt.step()
         sorted_params = opt.param_groups[0]["params"]
-        torch.save(dict(params=[p.detach().clone() for p in params],
-                        sorted_shapes=[tuple(p.shape) for p in sorted_params],
-                        has_state=[i for i, p in enumerate(sorted_params) if len(opt.state[p]) > 0]),
-                   f"{tmpdir}/out{rank}.pt")
+        out = dict(params=[p.detach().clone() for p in params],
+                   sorted_shapes=[tuple(p.shape) for p in sorted_params],
+                   has_state=[i for i, p in enumerate(sorted_params) if len(opt.state[p]) > 0])
+        params = [torch.nn.Parameter(p.clone()) for p in fx["p0"]]
+        gains = [torch.nn.Parameter(g.clone()) for g in fx["gains0"]]
+        aux = mb.MuonWithAuxAdam([dict(params=list(params), use_muon=True, lr=0.02, weight_decay=0.01),
+                                  dict(params=gains, use_muon=False, lr=3e-3, weight_decay=0.01)])
+        for step_grads, gain_grads in zip(fx["grads"], fx["gain_grads"]):
+            for i, (p, gr) in enumerate(zip(params, step_grads)):
+                p.grad = None if i == fx["no_grad_index"] else gr.clone()
+            for q, gr in zip(gains, gain_grads):
+                q.grad = gr.clone()
+            aux.step()
+        sorted_params = aux.param_groups[0]["params"]
+        out["aux"] = dict(params=[p.detach().clone() for p in params], gains=[q.detach().clone() for q in gains],
+                          has_state=[i for i, p in enumerate(sorted_params) if len(aux.state[p]) > 0],
+                          adam_steps=[aux.state[q]["step"] for q in gains])
+        torch.save(out, f"{tmpdir}/out{rank}.pt")
     finally:
         dist.destroy_process_group()
 
 
 def test_distributed_muon_matches_the_real_reference_class(tmp_path):
-    """Fixture `distributed`: the reference's own `Muon` run on two gloo ranks. Same parameters,
+    """Fixture `distributed`: the reference's own `Muon` and `MuonWithAuxAdam` run on two gloo ranks. Same parameters,
     same gradients, same world size here: every rank must end with the same parameters bit for
     bit, the same sort order and momentum state on the same (owned) parameters only."""
     path = os.path.join(os.path.dirname(__file__), "golden", "distributed.pt")
@@ -300,6 +314,11 @@ def test_distributed_muon_matches_the_real_reference_class(tmp_path):
         assert mine["sorted_shapes"] == theirs["sorted_shapes"]
         assert mine["has_state"] == theirs["has_state"]
         for p, q in zip(mine["params"], theirs["params"]):
+            assert torch.equal(p, q)
+        # the same problem through MuonWithAuxAdam, with an Adam group of 1-D parameters
+        assert mine["aux"]["has_state"] == theirs["aux"]["has_state"]
+        assert mine["aux"]["adam_steps"] == theirs["aux"]["adam_steps"]
+        for p, q in zip(mine["aux"]["params"] + mine["aux"]["gains"], theirs["aux"]["params"] + theirs["aux"]["gains"]):
             assert torch.equal(p, q)
 
 
