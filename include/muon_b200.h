@@ -158,8 +158,11 @@ int muon_b200_ns_run(void* workspace, int batch, int64_t m, int64_t n, int mode,
  * 64 MiB array built into the library instead of a caller workspace. This entry point has no
  * counterpart in the reference.
  *   x    bf16 [batch, m, n], m <= n, pitch ldx, batch pitch x_bs (elements); not modified.
- *   out  bf16 [batch, m, n], pitch ldo, batch pitch o_bs; receives the result; must not alias x.
+ *   out  bf16 [batch, m, n], pitch ldo, batch pitch o_bs; receives the result; its byte range
+ *        must not overlap x's (checked; with an even step count out doubles as a work buffer).
  * Pointers 16-byte aligned, pitches multiples of 8 and >= n. Other arguments as muon_b200_ns_run.
+ * The device that `stream` belongs to must be the current device of the calling thread: the
+ * built-in array is looked up for the current device.
  * Limits and caveats:
  *   - every GPU on which the library is loaded holds the 64 MiB until the process exits;
  *   - a problem needing more than muon_b200_ns_static_scratch_bytes() is rejected with

@@ -13,8 +13,8 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libmuon_b200.so")
-SOURCES = ("api.cu", "ns_gemm.cu", "elementwise.cu", "profiling.cu", "peer.cu", "no_alloc.cu")
-HEADERS = ("common.cuh", "ns_gemm.h", "elementwise.h", "profiling.h", os.path.join("..", "..", "include", "muon_b200.h"))
+SOURCES = ("api.cu", "ns_driver.cu", "ns_gemm.cu", "elementwise.cu", "profiling.cu", "peer.cu", "no_alloc.cu")
+HEADERS = ("common.cuh", "ns_driver.h", "ns_gemm.h", "elementwise.h", "profiling.h", os.path.join("..", "..", "include", "muon_b200.h"))
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

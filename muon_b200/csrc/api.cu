@@ -5,6 +5,7 @@
 
 #include "common.cuh"
 #include "elementwise.h"
+#include "ns_driver.h"
 #include "ns_gemm.h"
 #include "profiling.h"
 
@@ -34,17 +35,6 @@ inline int64_t round_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 inline cudaStream_t as_stream(muon_b200_stream_t s) { return static_cast<cudaStream_t>(s); }
 inline __nv_bfloat16* bf(void* p) { return static_cast<__nv_bfloat16*>(p); }
 inline const __nv_bfloat16* bf(const void* p) { return static_cast<const __nv_bfloat16*>(p); }
-
-constexpr int kFroChunksMax = 296;
-
-int fro_chunks(int64_t m) { return (int)(m < kFroChunksMax ? m : kFroChunksMax); }
-
-// Coefficient tables (a, b, c) per iteration.
-const float kAol4[4][3] = {{4.0098f, -7.0585f, 2.4635f},   // muon.py:754-759
-                           {3.4585f, -5.5479f, 2.5959f},
-                           {2.7573f, -3.2939f, 1.4254f},
-                           {2.7215f, -3.0494f, 1.3169f}};
-const float kClassic[3] = {3.4445f, -4.7750f, 2.0315f};    // muon.py:276
 
 int check_dtype(int dtype) {
   if (dtype != DT_F32 && dtype != DT_BF16)
@@ -168,75 +158,26 @@ int muon_b200_ns_run(void* workspace, int batch, int64_t m, int64_t n, int mode,
   if (!workspace) return set_error(ERR_INVALID_ARG, "workspace is NULL");
   if (reinterpret_cast<uintptr_t>(workspace) & 255)
     return set_error(ERR_ALIGNMENT, "NS workspace must be 256-byte aligned");
-  if (mode != MUON_B200_NS_AOL4 && mode != MUON_B200_NS_CLASSIC5)
-    return set_error(ERR_INVALID_ARG, "unknown NS mode %d", mode);
-  if (steps < 0 || steps > 64) return set_error(ERR_INVALID_ARG, "NS steps out of range: %d", steps);
-  if (steps == 0) steps = (mode == MUON_B200_NS_AOL4) ? 4 : 5;
-  if (!coeffs && mode == MUON_B200_NS_AOL4 && steps > 4)
-    return set_error(ERR_INVALID_ARG, "the AOL table has 4 iterations; pass coeffs for %d", steps);
+  int rc = ns_check_mode(mode, &steps, coeffs);
+  if (rc != OK) return rc;
   muon_b200_ns_layout l;
-  int rc = muon_b200_ns_workspace_layout(batch, m, n, &l);
+  rc = muon_b200_ns_workspace_layout(batch, m, n, &l);
   if (rc != OK) return rc;
   char* ws = static_cast<char*>(workspace);
-  __nv_bfloat16* X = bf(static_cast<void*>(ws + l.x_offset_bytes));
-  __nv_bfloat16* C = bf(static_cast<void*>(ws + l.c_offset_bytes));
-  __nv_bfloat16* A = bf(static_cast<void*>(ws + l.a_offset_bytes));
-  __nv_bfloat16* B = bf(static_cast<void*>(ws + l.b_offset_bytes));
-  float* partials = reinterpret_cast<float*>(ws + l.partials_offset_bytes);
-  cudaStream_t st = as_stream(stream);
-
-  int slot = 0;
-  bool have_gram = false;
-  if (mode == MUON_B200_NS_AOL4) {
-    // Gram matrix once, shared by the rescale and the first iteration (muon.py:778-785).
-    rc = launch_ns_gemm(MODE_SYRK, X, l.ldn, l.x_bs, X, l.ldn, l.x_bs, A, l.ldm, l.a_bs, batch, m,
-                        m, n, 1.f, 0.f, 1, st);
-    if (rc != OK) return rc;
-    // A / s is written into slot C (free until the first line 3 writes it, and m <= n) with
-    // A's pitches, so the symmetric unscaled A and s remain for line 2's epilogue.
-    rc = launch_aol_rescale(X, l.ldn, l.x_bs, A, C, l.ldm, l.a_bs, partials, l.ldm, (int)m, (int)n,
-                            batch, eps, st);
-    if (rc != OK) return rc;
-    have_gram = true;
-  } else {
-    rc = launch_fro_normalize(X, l.ldn, l.x_bs, (int)m, (int)n, batch, eps, partials,
-                              fro_chunks(m), st);
-    if (rc != OK) return rc;
-  }
-  for (int k = 0; k < steps; ++k) {
-    float a, b, c;
-    if (coeffs) {
-      a = coeffs[3 * k]; b = coeffs[3 * k + 1]; c = coeffs[3 * k + 2];
-    } else if (mode == MUON_B200_NS_AOL4) {
-      a = kAol4[k][0]; b = kAol4[k][1]; c = kAol4[k][2];
-    } else {
-      a = kClassic[0]; b = kClassic[1]; c = kClassic[2];
-    }
-    if (!have_gram) {
-      rc = launch_ns_gemm(MODE_SYRK, X, l.ldn, l.x_bs, X, l.ldn, l.x_bs, A, l.ldm, l.a_bs, batch,
-                          m, m, n, 1.f, 0.f, 1, st);
-      if (rc != OK) return rc;
-    }
-    if (have_gram) {
-      // First AOL iteration: the operand is A / s (rows scaled, not symmetric, in slot C); the
-      // addend beta * (A / s) is rebuilt per element from the symmetric A and s.
-      rc = launch_ns_gemm(MODE_AXPBY, C, l.ldm, l.a_bs, C, l.ldm, l.a_bs, B, l.ldm, l.a_bs, batch,
-                          m, m, m, c, b, ADD_ROW_SCALED, st, A, partials, l.ldm);
-    } else {
-      // A comes straight from line 1 and is exactly symmetric.
-      rc = launch_ns_gemm(MODE_AXPBY, A, l.ldm, l.a_bs, A, l.ldm, l.a_bs, B, l.ldm, l.a_bs, batch,
-                          m, m, m, c, b, ADD_SYMMETRIC, st);
-    }
-    have_gram = false;
-    if (rc != OK) return rc;
-    rc = launch_ns_gemm(MODE_BX, B, l.ldm, l.a_bs, X, l.ldn, l.x_bs, C, l.ldn, l.x_bs, batch, m, n,
-                        m, a, 0.f, 0, st);
-    if (rc != OK) return rc;
-    __nv_bfloat16* t = X; X = C; C = t;
-    slot ^= 1;
-  }
-  if (result_slot) *result_slot = slot;
-  return OK;
+  NsBuffers buf{};
+  buf.x[0] = bf(static_cast<void*>(ws + l.x_offset_bytes));
+  buf.x[1] = bf(static_cast<void*>(ws + l.c_offset_bytes));
+  buf.ldx[0] = buf.ldx[1] = l.ldn;
+  buf.x_bs[0] = buf.x_bs[1] = l.x_bs;
+  buf.A = bf(static_cast<void*>(ws + l.a_offset_bytes));
+  // A / s lives in slot C: it is free until the first line 3 writes it, and m <= n.
+  buf.A_scaled = buf.x[1];
+  buf.B = bf(static_cast<void*>(ws + l.b_offset_bytes));
+  buf.ldm = l.ldm;
+  buf.a_bs = l.a_bs;
+  buf.fscratch = reinterpret_cast<float*>(ws + l.partials_offset_bytes);
+  buf.f_bs = l.ldm;
+  return ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, as_stream(stream), result_slot);
 }
 
 int muon_b200_prologue(void* const* grads, void* const* moms, int count, int64_t rows,

@@ -123,6 +123,18 @@ __device__ __forceinline__ bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t
   return true;
 }
 
+// ---- programmatic dependent launch ---------------------------------------------
+// A kernel launched with cudaLaunchAttributeProgrammaticStreamSerialization may start while the
+// kernel before it in the stream is still running; griddep_wait() then blocks until that kernel
+// has completed and its writes are visible. griddep_launch_dependents() tells the scheduler that
+// the kernel after this one may start being launched. Both are no-ops for ordinary launches.
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ---- thread-block cluster ----------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_cta_rank() {
   uint32_t r;

@@ -130,6 +130,7 @@ prologue_kernel(const PrologueArgs a) {
   const long long total = tiles_per * a.count;
   const int tx = threadIdx.x & 15;
   const int ty = threadIdx.x >> 4;
+  griddep_launch_dependents();  // line 1 may set itself up while this kernel drains
   const float w1 = a.w_mom;  // float(1 - beta)
   const float w2 = a.beta;   // float(beta)
 
@@ -390,6 +391,9 @@ aol_rescale_kernel(__nv_bfloat16* X, long long ldx, long long x_bs, const __nv_b
                    int m, int n, int batch, float eps) {
   __shared__ float warp_sums[kThreads / 32];
   __shared__ float s_bcast;
+  // Launched as a programmatic dependent of line 1 and followed by line 2 (see common.cuh).
+  griddep_launch_dependents();
+  griddep_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long rows_total = (long long)m * batch;
   for (long long row = blockIdx.x; row < rows_total; row += gridDim.x) {
@@ -645,8 +649,17 @@ int launch_aol_rescale(__nv_bfloat16* X, long long ldx, long long x_bs, const __
   if (grid < 0) return ERR_UNSUPPORTED;
   // read + write A (m x m) and X (m x n), bf16
   LaunchScope scope(K_AOL_RESCALE, 4.0 * m * ((double)m + n) * batch, stream);
-  aol_rescale_kernel<<<grid, kThreads, 0, stream>>>(X, ldx, x_bs, A, A_out, lda, a_bs, svec, s_bs, m, n,
-                                                     batch, eps);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dependent_launch_enabled() ? 1 : 0;
+  MB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, aol_rescale_kernel, X, ldx, x_bs, A, A_out, lda, a_bs, svec, s_bs,
+                                   m, n, batch, eps));
   MB_CUDA_CHECK(cudaGetLastError());
   return OK;
 }

@@ -17,6 +17,7 @@
 
 #include "common.cuh"
 #include "elementwise.h"
+#include "ns_driver.h"
 #include "ns_gemm.h"
 
 #include <mutex>
@@ -52,17 +53,13 @@ int scratch_for_current_device(unsigned char** out) {
 
 inline int64_t round_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
-const float kAol4[4][3] = {{4.0098f, -7.0585f, 2.4635f},
-                           {3.4585f, -5.5479f, 2.5959f},
-                           {2.7573f, -3.2939f, 1.4254f},
-                           {2.7215f, -3.0494f, 1.3169f}};
-const float kClassic[3] = {3.4445f, -4.7750f, 2.0315f};
-constexpr int kFroChunksMax = 296;
-
-struct Slot {
-  __nv_bfloat16* p;
-  int64_t ld, bs;
-};
+// Byte range [lo, hi) that a [batch, m, n] bf16 tensor with the given pitches touches.
+void byte_range(const void* p, int64_t ld, int64_t bs, int batch, int64_t m, int64_t n,
+                uintptr_t* lo, uintptr_t* hi) {
+  const int64_t last = (int64_t)(batch - 1) * bs + (m - 1) * ld + n;  // one past the last element
+  *lo = reinterpret_cast<uintptr_t>(p);
+  *hi = *lo + (uintptr_t)last * 2;
+}
 
 }  // namespace
 
@@ -83,19 +80,16 @@ int muon_b200_ns_run_static(const void* x, int64_t ldx, int64_t x_bs, void* out,
                             int64_t o_bs, int batch, int64_t m, int64_t n, int mode, int steps,
                             const float* coeffs, float eps, muon_b200_stream_t stream) {
   if (!x || !out) return set_error(ERR_INVALID_ARG, "ns_run_static: null pointer");
-  if (x == out) return set_error(ERR_INVALID_ARG, "ns_run_static: out must not alias x");
   if (batch < 1 || m < 1 || n < m)
     return set_error(ERR_INVALID_ARG, "ns_run_static needs batch >= 1 and 1 <= m <= n");
-  if (mode != MUON_B200_NS_AOL4 && mode != MUON_B200_NS_CLASSIC5)
-    return set_error(ERR_INVALID_ARG, "unknown NS mode %d", mode);
-  if (steps < 0 || steps > 64) return set_error(ERR_INVALID_ARG, "NS steps out of range: %d", steps);
-  if (steps == 0) steps = (mode == MUON_B200_NS_AOL4) ? 4 : 5;
-  if (!coeffs && mode == MUON_B200_NS_AOL4 && steps > 4)
-    return set_error(ERR_INVALID_ARG, "the AOL table has 4 iterations; pass coeffs for %d", steps);
+  int rc = ns_check_mode(mode, &steps, coeffs);
+  if (rc != OK) return rc;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) ||
       (ldx % 8) || (ldo % 8) || (x_bs % 8) || (o_bs % 8) || ldx < n || ldo < n)
     return set_error(ERR_ALIGNMENT,
                      "ns_run_static: x and out must be 16-byte aligned with pitches %% 8 == 0 and >= n");
+  if (batch > 1 && (x_bs < (m - 1) * ldx + n || o_bs < (m - 1) * ldo + n))
+    return set_error(ERR_INVALID_ARG, "ns_run_static: batch pitch shorter than one matrix");
   const int64_t need = muon_b200_ns_static_required_bytes(batch, m, n);
   if (need > (int64_t)kStaticScratchBytes)
     return set_error(ERR_UNSUPPORTED,
@@ -103,74 +97,52 @@ int muon_b200_ns_run_static(const void* x, int64_t ldx, int64_t x_bs, void* out,
                      "array holds %lld; use muon_b200_ns_run with a caller workspace",
                      batch, (long long)m, (long long)n, (long long)need,
                      (long long)kStaticScratchBytes);
+  {
+    // With an even iteration count `out` is the ping-pong buffer and is written while x is
+    // still being copied in, so any overlap of the two ranges (not only x == out) corrupts x.
+    uintptr_t xl, xh, ol, oh;
+    byte_range(x, ldx, x_bs, batch, m, n, &xl, &xh);
+    byte_range(out, ldo, o_bs, batch, m, n, &ol, &oh);
+    if (xl < oh && ol < xh)
+      return set_error(ERR_INVALID_ARG, "ns_run_static: out must not overlap x");
+  }
   unsigned char* base = nullptr;
-  int rc = scratch_for_current_device(&base);
+  rc = scratch_for_current_device(&base);
   if (rc != OK) return rc;
 
   const int64_t ldn = round_up(n, 8), ldm = round_up(m, 8);
   const int64_t xs = round_up(batch * m * ldn * 2, 256);
   const int64_t as = round_up(batch * m * ldm * 2, 256);
-  const int64_t a_bs = m * ldm;
-  Slot S{reinterpret_cast<__nv_bfloat16*>(base), ldn, m * ldn};
-  __nv_bfloat16* A = reinterpret_cast<__nv_bfloat16*>(base + xs);
-  __nv_bfloat16* As = reinterpret_cast<__nv_bfloat16*>(base + xs + as);  // row-scaled copy of A
-  __nv_bfloat16* B = reinterpret_cast<__nv_bfloat16*>(base + xs + 2 * as);
-  float* fscratch = reinterpret_cast<float*>(base + xs + 3 * as);
-  Slot O{static_cast<__nv_bfloat16*>(out), ldo, o_bs};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
   // The iteration ping-pongs between two buffers and must end in `out`: with an even number of
   // iterations it starts there, with an odd number it starts in the built-in buffer.
-  Slot cur = (steps % 2 == 0) ? O : S;
-  Slot oth = (steps % 2 == 0) ? S : O;
+  const int o = (steps % 2 == 0) ? 0 : 1;  // index of `out` among the two iterate buffers
+  NsBuffers buf{};
+  buf.x[o] = static_cast<__nv_bfloat16*>(out);
+  buf.ldx[o] = ldo;
+  buf.x_bs[o] = o_bs;
+  buf.x[o ^ 1] = reinterpret_cast<__nv_bfloat16*>(base);
+  buf.ldx[o ^ 1] = ldn;
+  buf.x_bs[o ^ 1] = m * ldn;
+  buf.A = reinterpret_cast<__nv_bfloat16*>(base + xs);
+  buf.A_scaled = reinterpret_cast<__nv_bfloat16*>(base + xs + as);  // row-scaled copy of A
+  buf.B = reinterpret_cast<__nv_bfloat16*>(base + xs + 2 * as);
+  buf.ldm = ldm;
+  buf.a_bs = m * ldm;
+  buf.fscratch = reinterpret_cast<float*>(base + xs + 3 * as);
+  buf.f_bs = ldm;
   for (int b = 0; b < batch; ++b)
-    MB_CUDA_CHECK(cudaMemcpy2DAsync(cur.p + (int64_t)b * cur.bs, (size_t)cur.ld * 2,
+    MB_CUDA_CHECK(cudaMemcpy2DAsync(buf.x[0] + (int64_t)b * buf.x_bs[0], (size_t)buf.ldx[0] * 2,
                                     static_cast<const __nv_bfloat16*>(x) + (int64_t)b * x_bs,
                                     (size_t)ldx * 2, (size_t)n * 2, (size_t)m,
                                     cudaMemcpyDeviceToDevice, st));
-
   // Nothing in the scratch has to start at zero: A, B, the scaled copy, the row scales and the
   // ping-pong buffer are each written in full before they are read.
-  bool have_gram = false;
-  if (mode == MUON_B200_NS_AOL4) {
-    rc = launch_ns_gemm(MODE_SYRK, cur.p, cur.ld, cur.bs, cur.p, cur.ld, cur.bs, A, ldm, a_bs, batch,
-                        m, m, n, 1.f, 0.f, ADD_SYMMETRIC, st);
-    if (rc != OK) return rc;
-    rc = launch_aol_rescale(cur.p, cur.ld, cur.bs, A, As, ldm, a_bs, fscratch, ldm, (int)m, (int)n,
-                            batch, eps, st);
-    if (rc != OK) return rc;
-    have_gram = true;
-  } else {
-    const int chunks = (int)(m < kFroChunksMax ? m : kFroChunksMax);
-    rc = launch_fro_normalize(cur.p, cur.ld, cur.bs, (int)m, (int)n, batch, eps, fscratch, chunks, st);
-    if (rc != OK) return rc;
-  }
-  for (int k = 0; k < steps; ++k) {
-    float a, b, c;
-    if (coeffs) {
-      a = coeffs[3 * k]; b = coeffs[3 * k + 1]; c = coeffs[3 * k + 2];
-    } else if (mode == MUON_B200_NS_AOL4) {
-      a = kAol4[k][0]; b = kAol4[k][1]; c = kAol4[k][2];
-    } else {
-      a = kClassic[0]; b = kClassic[1]; c = kClassic[2];
-    }
-    if (have_gram) {
-      rc = launch_ns_gemm(MODE_AXPBY, As, ldm, a_bs, As, ldm, a_bs, B, ldm, a_bs, batch, m, m, m, c,
-                          b, ADD_ROW_SCALED, st, A, fscratch, ldm);
-    } else {
-      rc = launch_ns_gemm(MODE_SYRK, cur.p, cur.ld, cur.bs, cur.p, cur.ld, cur.bs, A, ldm, a_bs,
-                          batch, m, m, n, 1.f, 0.f, ADD_SYMMETRIC, st);
-      if (rc != OK) return rc;
-      rc = launch_ns_gemm(MODE_AXPBY, A, ldm, a_bs, A, ldm, a_bs, B, ldm, a_bs, batch, m, m, m, c, b,
-                          ADD_SYMMETRIC, st);
-    }
-    have_gram = false;
-    if (rc != OK) return rc;
-    rc = launch_ns_gemm(MODE_BX, B, ldm, a_bs, cur.p, cur.ld, cur.bs, oth.p, oth.ld, oth.bs, batch, m,
-                        n, m, a, 0.f, ADD_GENERIC, st);
-    if (rc != OK) return rc;
-    Slot t = cur; cur = oth; oth = t;
-  }
+  int where = 0;
+  rc = ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, st, &where);
+  if (rc != OK) return rc;
+  if (where != o) return set_error(ERR_CUDA, "ns_run_static: result landed in the wrong buffer");
   return OK;
 }
 

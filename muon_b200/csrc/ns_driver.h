@@ -1,0 +1,39 @@
+// The Newton-Schulz iteration as a sequence of kernel launches over caller-chosen buffers.
+// Shared by muon_b200_ns_run (buffers inside a caller workspace) and muon_b200_ns_run_static
+// (buffers inside the library's built-in scratch), so that the coefficient tables and the
+// launch order exist once.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace mb {
+
+constexpr int kFroChunksMax = 296;  // partial sums per matrix of the Frobenius reduction
+
+struct NsBuffers {
+  // The iterate ping-pongs between x[0] (holds the input on entry) and x[1]; both are
+  // [batch, m, n] bf16 with their own pitches (elements).
+  __nv_bfloat16* x[2];
+  int64_t ldx[2], x_bs[2];
+  // Square scratch matrices [batch, m, ldm]: the Gram matrix A, its row-scaled copy (AOL mode
+  // only; may alias x[1], which is not written before the first line 3) and B.
+  __nv_bfloat16* A;
+  __nv_bfloat16* A_scaled;
+  __nv_bfloat16* B;
+  int64_t ldm, a_bs;
+  // fp32 scratch, per matrix max(ldm, kFroChunksMax) floats: row scales 1/s or Frobenius partials.
+  float* fscratch;
+  int64_t f_bs;
+};
+
+// steps > 0; coeffs is NULL (the mode's table) or steps triples (a, b, c). On success
+// *result_index tells which of x[0] / x[1] holds the result (steps % 2).
+int ns_iterate(const NsBuffers& buf, int batch, int64_t m, int64_t n, int mode, int steps,
+               const float* coeffs, float eps, cudaStream_t stream, int* result_index);
+
+// Argument checks shared by both entry points: fills in the default step count.
+int ns_check_mode(int mode, int* steps, const float* coeffs);
+
+}  // namespace mb

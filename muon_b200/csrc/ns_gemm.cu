@@ -309,6 +309,13 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
 
+  // Everything above (barriers, tensor memory, descriptor prefetch) touches no memory that an
+  // earlier kernel writes, so with a programmatic dependent launch it overlaps the tail of the
+  // kernel before this one in the stream; all global-memory traffic comes after the wait. The
+  // kernel after this one may start its own set-up on every SM this grid leaves.
+  griddep_launch_dependents();
+  griddep_wait();
+
   const int k_blocks = (p.K + BK - 1) / BK;
   const int total_tiles = p.tiles_per_batch * p.batch;
   const int work0 = blockIdx.x / CTAS;
@@ -754,6 +761,18 @@ int forced_ctas() {
   return v;
 }
 
+// Programmatic dependent launch of the GEMMs (MUON_B200_PDL=0 switches it off; read once; meant
+// for A/B measurements).
+}  // namespace
+bool dependent_launch_enabled() {
+  static bool v = [] {
+    const char* e = std::getenv("MUON_B200_PDL");
+    return !(e && (e[0] == '0' || e[0] == 'n' || e[0] == 'f'));
+  }();
+  return v;
+}
+namespace {
+
 // SMs the persistent GEMM grids leave free, for kernels of other streams that must make
 // progress while a GEMM runs (a collective's copy kernels in the distributed step).
 std::atomic<int> g_reserved_sms{0};
@@ -781,13 +800,15 @@ int launch_instance(int dev, int sms, const CUtensorMap& ta, const CUtensorMap& 
   cfg.blockDim = dim3(num_threads(EW));
   cfg.dynamicSmemBytes = C::smem_total(EW);
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = CTAS;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = dependent_launch_enabled() ? 2 : 1;
 
   int max_units;  // co-resident CTAs (CTAS = 1) or clusters (CTAS = 2)
   {

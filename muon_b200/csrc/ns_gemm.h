@@ -37,6 +37,8 @@ struct GemmParams {
 };
 
 int device_sm_count(int* sm_count_out);
+// Whether kernels that support it are launched with programmatic stream serialization.
+bool dependent_launch_enabled();
 void set_reserved_sms(int n);
 int get_reserved_sms();
 

@@ -19,6 +19,35 @@ struct Interval {
 };
 std::vector<Interval> g_intervals;
 std::mutex g_mu;
+// Intervals folded away by compact(): per-kind totals that the next timing_collect adds in.
+double g_folded_ms[K_KIND_COUNT] = {};
+double g_folded_work[K_KIND_COUNT] = {};
+int64_t g_folded_launches[K_KIND_COUNT] = {};
+constexpr size_t kMaxPendingIntervals = 1 << 16;
+
+// Called with g_mu held once the list is long: intervals whose stop event has completed are
+// added to the per-kind totals and their events destroyed, so a run that enables timing and
+// never collects keeps a bounded number of events and a bounded list.
+void compact_locked() {
+  size_t kept = 0;
+  for (size_t i = 0; i < g_intervals.size(); ++i) {
+    const Interval& iv = g_intervals[i];
+    float t = 0.f;
+    if (cudaEventQuery(iv.stop) == cudaSuccess && cudaEventElapsedTime(&t, iv.start, iv.stop) == cudaSuccess) {
+      if (iv.kind >= 0 && iv.kind < K_KIND_COUNT) {
+        g_folded_ms[iv.kind] += t;
+        g_folded_work[iv.kind] += iv.work;
+        g_folded_launches[iv.kind] += 1;
+      }
+      cudaEventDestroy(iv.start);
+      cudaEventDestroy(iv.stop);
+    } else {
+      (void)cudaGetLastError();  // cudaErrorNotReady is not an error here
+      g_intervals[kept++] = iv;
+    }
+  }
+  g_intervals.resize(kept);
+}
 }  // namespace
 
 LaunchScope::LaunchScope(int kind, double work, cudaStream_t stream, int64_t tag)
@@ -40,20 +69,30 @@ LaunchScope::~LaunchScope() {
   cudaEventRecord(stop, stream_);
   std::lock_guard<std::mutex> lk(g_mu);
   g_intervals.push_back({kind_, work_, tag_, start_, stop});
+  if (g_intervals.size() >= kMaxPendingIntervals) compact_locked();
 }
 
 void timing_enable(bool on) { g_timing.store(on); }
 
 int timing_collect(double* ms, double* work, int64_t* launches, int n_kinds) {
   std::vector<Interval> taken;
-  {
-    std::lock_guard<std::mutex> lk(g_mu);
-    taken.swap(g_intervals);
-  }
   for (int k = 0; k < n_kinds; ++k) {
     ms[k] = 0.0;
     work[k] = 0.0;
     launches[k] = 0;
+  }
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    taken.swap(g_intervals);
+    for (int k = 0; k < K_KIND_COUNT; ++k) {
+      if (k < n_kinds) {
+        ms[k] = g_folded_ms[k];
+        work[k] = g_folded_work[k];
+        launches[k] = g_folded_launches[k];
+      }
+      g_folded_ms[k] = g_folded_work[k] = 0.0;
+      g_folded_launches[k] = 0;
+    }
   }
   int rc = OK;
   for (const Interval& iv : taken) {

@@ -34,6 +34,10 @@ class LaunchScope {
   cudaEvent_t start_ = nullptr;
 };
 
+// While timing is on every launch keeps two events until it is collected. Once 65536 launches
+// are pending, those that have completed are folded into per-kind totals (which the next
+// timing_collect adds in; timing_collect_records no longer lists them), so a long run that
+// never collects holds a bounded number of events.
 void timing_enable(bool on);
 // Waits for all recorded intervals, adds them up per kind and forgets them.
 int timing_collect(double* ms, double* work, int64_t* launches, int n_kinds);

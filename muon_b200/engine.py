@@ -64,7 +64,13 @@ def mark_grad_ready(tensor: Tensor, event: "torch.cuda.Event | None" = None) -> 
     group, so Newton-Schulz of the gradients that arrived first runs while later ones are still
     in flight. Gradients without a mark are assumed ready in the order of step()'s own stream,
     which is the reference's behaviour. A mark is consumed by the step that uses it."""
-    g = tensor.grad if isinstance(tensor, torch.nn.Parameter) and tensor.grad is not None else tensor
+    if isinstance(tensor, torch.nn.Parameter):
+        if tensor.grad is None:
+            raise ValueError("mark_grad_ready: the parameter has no gradient yet; allocate p.grad (or pass "
+                             "the gradient tensor itself) before marking it")
+        g = tensor.grad
+    else:
+        g = tensor
     _require_cuda(g, "gradient")
     if event is None:
         event = torch.cuda.Event()

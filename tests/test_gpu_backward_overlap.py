@@ -1,14 +1,11 @@
-"""StepInBackward on a GPU: updates enqueued from the backward pass on a side stream must leave
-the parameters bit-identical to optimizer.step() after the backward pass.
-
-The CUDA branch of StepInBackward (side stream, record_stream, hooks running on the autograd
-thread) has not yet been run on a GPU: the CPU test in test_host_logic.py covers the bookkeeping,
-and this test is allowed to fail until it has been seen passing on a B200."""
+"""StepInBackward on a GPU: updates enqueued from the backward pass on a side stream (hooks
+running on the autograd thread, gradients kept alive with record_stream) must leave the parameters
+bit-identical to optimizer.step() after the backward pass. The bookkeeping alone is covered on CPU
+in test_host_logic.py."""
 import pytest
 import torch
 
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.xfail(strict=False, reason="CUDA branch of StepInBackward not yet run on a GPU")]
+pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 

@@ -1,7 +1,13 @@
 """The benchmark configurations as parity cases: GPT-2-small-shaped hidden weights with aux Adam
 (reduced to 2 of 12 layers so that the CPU oracle finishes in seconds), batched conv filters
-(8 + 8 of the 64 + 64), and — at the full Llama-3-8B sizes, where the oracle would take minutes —
-size-independent properties of the orthogonalised update."""
+(8 + 8 of the 64 + 64), and the Llama-3-8B / 70B matrix shapes: against the CPU oracle matrix by
+matrix (a few seconds each on the host cores), as one grouped launch, as a whole layer through the
+optimizer, and through size-independent properties of the orthogonalised update.
+
+Tolerances: Newton-Schulz output rel-Fro <= 2e-2 against the oracle with singular values in the
+same band; updated fp32 parameters <= 1e-3; the accumulated update alone (p - p0, which is ~3% of
+the parameter) <= 2e-2; bf16 parameters <= 4e-3 (they carry 2^-9 rounding themselves, and one step's
+update is about one bf16 ulp of the parameter, so "the update alone" is only meaningful in fp32)."""
 import pytest
 import torch
 
@@ -60,8 +66,10 @@ def test_gpt2_small_hidden_weights_with_aux_adam(mb, tmp_path):
             for q, gr, m, v in zip(ref_g, gg, ma, va):
                 orc.adam_param_step(q, gr.clone(), m, v, step, 3e-4, 0, (0.9, 0.95), 1e-10)
         assert [tuple(p.shape) for p in sorted_hidden] == sorted([tuple(s) for s in shapes], reverse=True)
-        for p in hidden:
+        for p, start in zip(hidden, p0):
             assert orc.rel_fro(p.detach().cpu(), ref[id(p)]) <= 1e-3, tuple(p.shape)
+            # the accumulated update alone
+            assert orc.rel_fro(p.detach().cpu() - start, ref[id(p)] - start) <= 2e-2, tuple(p.shape)
         for p, q in zip(gains, ref_g):
             assert torch.allclose(p.detach().cpu(), q, rtol=1e-5, atol=1e-7)
     finally:
@@ -85,8 +93,9 @@ def test_batched_conv_filters(mb):
     after = mb._lib.launch_counts()
     assert after["prologue"] - before["prologue"] == 4  # 2 steps x 2 shape classes
     assert after["ns_line3"] - before["ns_line3"] == 16  # 2 steps x 2 classes x 4 iterations
-    for p, r in zip(params, ref_p):
+    for p, r, start in zip(params, ref_p, p0):
         assert p.shape == r.shape and orc.rel_fro(p.detach().cpu(), r) <= 1e-3
+        assert orc.rel_fro(p.detach().cpu() - start, r - start) <= 2e-2  # the accumulated update alone
 
 
 def _spectral_norm_sym(S, iters=40):
@@ -128,6 +137,72 @@ def test_llama3_shapes_properties(mb, shape):
     # a square input is iterated as it is, so the identity only holds up to rounding there)
     if shape[0] != shape[1]:
         assert torch.equal(mb.zeropower_via_newtonschulz5(G.T.contiguous()), U.T)
+
+
+def _sv_band_gpu(U):
+    """(min, max) singular value of a wide or tall matrix from the eigenvalues of its fp32 Gram
+    matrix, on the GPU (an SVD of 4096 x 14336 on the host takes most of a minute)."""
+    Uf = U.to(DEV).float()
+    gram = Uf @ Uf.mT if Uf.shape[-2] <= Uf.shape[-1] else Uf.mT @ Uf
+    ev = torch.linalg.eigvalsh(gram).clamp_min(0).sqrt()
+    return float(ev.min()), float(ev.max())
+
+
+LLAMA_ORACLE_SHAPES = [(1024, 4096), (4096, 4096), (4096, 14336), (14336, 4096), (1024, 8192), (8192, 8192),
+                       (3, 1024, 4096), (3, 4096, 4096)]
+
+
+@pytest.mark.parametrize("shape", LLAMA_ORACLE_SHAPES)
+def test_llama3_shapes_against_the_oracle(mb, shape):
+    """The matrices of a Llama-3-8B layer and the two 70B shapes whose oracle run stays within
+    seconds, bf16 gradients ~N(0, 1e-3), single and as one grouped launch of three: Newton-Schulz
+    output within 2e-2 (rel-Fro) of the CPU oracle, singular values in the same band."""
+    g = torch.Generator().manual_seed(4100 + len(shape) * 7 + shape[-1] // 64 + shape[-2])
+    G = (torch.randn(shape, generator=g) * 1e-3).bfloat16()
+    before = dict(mb._lib.launch_counts())
+    U = mb.zeropower_via_newtonschulz5(G.to(DEV))
+    after = mb._lib.launch_counts()
+    assert after["ns_line3"] - before["ns_line3"] == 4  # one launch per iteration, batch included
+    ref = orc.zeropower_via_newtonschulz5(G)
+    assert U.shape == G.shape and U.dtype == torch.bfloat16
+    for k in range(shape[0] if len(shape) == 3 else 1):
+        u, r = (U[k], ref[k]) if len(shape) == 3 else (U, ref)
+        err = orc.rel_fro(u.cpu(), r)
+        assert err <= 2e-2, (shape, k, err)
+        if shape[-1] != shape[-2]:
+            (lo, hi), (rlo, rhi) = _sv_band_gpu(u), _sv_band_gpu(r)
+            assert abs(hi - rhi) <= 0.02 and abs(lo - rlo) <= 0.05, ((lo, hi), (rlo, rhi))
+            assert 0.95 < lo and hi < 1.05
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_one_llama3_8b_layer_through_the_optimizer(mb, dtype):
+    """q, o 4096 x 4096; k, v 1024 x 4096; gate, up 14336 x 4096; down 4096 x 14336 through
+    SingleDeviceMuon (grouped by shape, tall ones transposed on the fly), against the oracle's
+    per-parameter step. fp32 parameters: two steps, parameters <= 1e-3 and the accumulated update
+    alone <= 2e-2. bf16 parameters (the benchmark's dtype): one step, parameters <= 4e-3 and the
+    momentum buffer to one bf16 ulp."""
+    shapes = [(4096, 4096), (4096, 4096), (1024, 4096), (1024, 4096), (14336, 4096), (14336, 4096), (4096, 14336)]
+    steps = 2 if dtype == torch.float32 else 1
+    g = torch.Generator().manual_seed(4200)
+    p0 = [(torch.randn(s, generator=g) * 0.02).to(dtype) for s in shapes]
+    params = [torch.nn.Parameter(p.clone().to(DEV)) for p in p0]
+    opt = mb.SingleDeviceMuon(params, lr=0.02, weight_decay=0.01, momentum=0.95)
+    ref_p = [p.clone() for p in p0]
+    ref_m = [torch.zeros_like(p) for p in p0]
+    for _ in range(steps):
+        grads = [(torch.randn(s, generator=g) * 1e-3).to(dtype) for s in shapes]
+        _step_both(mb, opt, params, ref_p, ref_m, grads, 0.02, 0.01)
+    for p, r, start, m in zip(params, ref_p, p0, ref_m):
+        got = p.detach().cpu()
+        if dtype == torch.float32:
+            assert orc.rel_fro(got, r) <= 1e-3, tuple(p.shape)
+            assert orc.rel_fro(got - start, r - start) <= 2e-2, tuple(p.shape)
+            assert torch.allclose(opt.state[p]["momentum_buffer"].cpu(), m, rtol=2e-6, atol=1e-9)
+        else:
+            assert orc.rel_fro(got, r) <= 4e-3, tuple(p.shape)
+            mom = opt.state[p]["momentum_buffer"].cpu().float()
+            assert ((mom - m.float()).abs() <= m.float().abs() * 2 ** -7 + 1e-12).all()
 
 
 def test_gradients_arriving_on_a_copy_stream(mb):

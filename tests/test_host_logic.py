@@ -73,6 +73,8 @@ def test_no_cpu_fallback():
         muon_b200.adam_update(torch.randn(4), torch.zeros(4), torch.zeros(4), 1, (0.9, 0.95), 1e-10)
     with pytest.raises(RuntimeError, match="no CPU implementation"):
         muon_b200.mark_grad_ready(p)  # readiness marks are CUDA events: CPU gradients have none
+    with pytest.raises(ValueError, match="no gradient"):
+        muon_b200.mark_grad_ready(torch.nn.Parameter(torch.randn(4, 4)))  # nothing would consume the mark
     from muon_b200 import engine
     assert not engine._grad_ready
 
