@@ -65,6 +65,19 @@ int muon_b200_device_status(int* status_out, int reset);
 int muon_b200_set_reserved_sms(int n);
 int muon_b200_get_reserved_sms(void);
 
+/* A short Newton-Schulz run (a few matrices of a few hundred rows) is thirteen kernels of a few
+ * microseconds each; issued one by one they cost more host time than device time. By default
+ * muon_b200_ns_run (and muon_b200_muon_step, which calls it) therefore captures its launch
+ * sequence into a CUDA graph the first time it sees a given workspace address, batch, shape,
+ * mode and coefficient list, and replays the graph afterwards; runs with more than about 2 TFLOP
+ * of work, streams that are themselves being captured and per-kernel timing use plain launches.
+ * Graph instantiation allocates driver resources (this is the other exception to "never
+ * allocates"; muon_b200_ns_run_static never uses it). Process-wide switch, default on; the
+ * environment variable MUON_B200_GRAPH=0 sets the default to off. No counterpart in the
+ * reference, whose driver is compiled by torch.compile (muon.py:748). */
+int muon_b200_set_graph_replay(int on);
+int muon_b200_get_graph_replay(void);
+
 /* ---- Peer memory for the distributed step's exchange ---------------------------------
  * These four are the exceptions to "never allocates, never maps": they create and remove
  * address-space mappings of OTHER processes' device memory. They have no counterpart in the

@@ -45,6 +45,8 @@ PROTOTYPES = {
     "muon_b200_device_status": (c_int, [POINTER(c_int), c_int]),
     "muon_b200_set_reserved_sms": (c_int, [c_int]),
     "muon_b200_get_reserved_sms": (c_int, []),
+    "muon_b200_set_graph_replay": (c_int, [c_int]),
+    "muon_b200_get_graph_replay": (c_int, []),
     "muon_b200_ns_run_static": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int,
                                         c_int64, c_int64, c_int, c_int, POINTER(c_float), c_float,
                                         c_void_p]),

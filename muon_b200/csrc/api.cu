@@ -80,6 +80,13 @@ int muon_b200_set_reserved_sms(int n) {
 
 int muon_b200_get_reserved_sms(void) { return get_reserved_sms(); }
 
+int muon_b200_set_graph_replay(int on) {
+  set_graph_replay(on != 0);
+  return OK;
+}
+
+int muon_b200_get_graph_replay(void) { return graph_replay_enabled() ? 1 : 0; }
+
 int muon_b200_kernel_kinds(void) { return K_KIND_COUNT; }
 
 int muon_b200_launch_counts(int64_t* counts, int n_kinds) {
@@ -177,7 +184,7 @@ int muon_b200_ns_run(void* workspace, int batch, int64_t m, int64_t n, int mode,
   buf.a_bs = l.a_bs;
   buf.fscratch = reinterpret_cast<float*>(ws + l.partials_offset_bytes);
   buf.f_bs = l.ldm;
-  return ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, as_stream(stream), result_slot);
+  return ns_iterate_replayed(buf, batch, m, n, mode, steps, coeffs, eps, as_stream(stream), result_slot);
 }
 
 int muon_b200_prologue(void* const* grads, void* const* moms, int count, int64_t rows,

@@ -7,6 +7,13 @@
 #include "elementwise.h"
 #include "ns_driver.h"
 #include "ns_gemm.h"
+#include "profiling.h"
+
+#include <atomic>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <vector>
 
 namespace mb {
 
@@ -84,6 +91,136 @@ int ns_iterate(const NsBuffers& buf, int batch, int64_t m, int64_t n, int mode, 
     cur ^= 1;
   }
   if (result_index) *result_index = cur;
+  return OK;
+}
+
+// ---------------------------------------------------------------------------
+// Graph replay
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr int kGraphMaxSteps = 8;         // longer coefficient lists are launched directly
+constexpr double kGraphMaxFlops = 2e12;   // above ~1.5 ms of device work the launches are hidden
+constexpr size_t kGraphCacheEntries = 128;
+
+struct GraphKey {  // plain data, compared with memcmp: keep it free of padding garbage (memset)
+  NsBuffers buf;
+  int64_t m, n;
+  int batch, mode, steps, has_coeffs, device, reserved_sms;
+  float eps;
+  float coeffs[3 * kGraphMaxSteps];
+};
+
+struct GraphEntry {
+  GraphKey key;
+  cudaGraphExec_t exec = nullptr;  // nullptr: capture failed once, launch directly from now on
+  int64_t counts[K_KIND_COUNT] = {};
+  int result_index = 0;
+  uint64_t last_use = 0;
+};
+
+std::mutex g_graph_mu;
+std::vector<GraphEntry> g_graphs;
+uint64_t g_graph_clock = 0;
+cudaStream_t g_capture_stream[64] = {};
+std::atomic<int> g_graph_on{-1};  // -1: not decided yet (environment), 0 / 1
+
+}  // namespace
+
+void set_graph_replay(bool on) { g_graph_on.store(on ? 1 : 0); }
+
+bool graph_replay_enabled() {
+  int v = g_graph_on.load();
+  if (v < 0) {
+    const char* e = std::getenv("MUON_B200_GRAPH");
+    v = (e && (e[0] == '0' || e[0] == 'n' || e[0] == 'f')) ? 0 : 1;
+    g_graph_on.store(v);
+  }
+  return v == 1;
+}
+
+int ns_iterate_replayed(const NsBuffers& buf, int batch, int64_t m, int64_t n, int mode, int steps,
+                        const float* coeffs, float eps, cudaStream_t stream, int* result_index) {
+  const double flops = (double)batch * steps * ((double)m * (m + 1) * n + (double)m * m * (m + 1) + 2.0 * m * m * n);
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  if (!graph_replay_enabled() || timing_enabled() || steps > kGraphMaxSteps || flops > kGraphMaxFlops ||
+      cudaStreamIsCapturing(stream, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) {
+    (void)cudaGetLastError();
+    return ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, stream, result_index);
+  }
+  int dev = 0;
+  MB_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, stream, result_index);
+
+  GraphKey key;
+  std::memset(&key, 0, sizeof(key));
+  key.buf = buf;
+  key.m = m; key.n = n; key.batch = batch; key.mode = mode; key.steps = steps;
+  key.has_coeffs = coeffs ? 1 : 0;
+  key.device = dev;
+  key.reserved_sms = get_reserved_sms();
+  key.eps = eps;
+  if (coeffs) std::memcpy(key.coeffs, coeffs, sizeof(float) * 3 * steps);
+
+  std::lock_guard<std::mutex> lk(g_graph_mu);
+  GraphEntry* hit = nullptr;
+  for (GraphEntry& e : g_graphs)
+    if (std::memcmp(&e.key, &key, sizeof(key)) == 0) { hit = &e; break; }
+  if (hit) {
+    hit->last_use = ++g_graph_clock;
+    if (!hit->exec) return ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, stream, result_index);
+    MB_CUDA_CHECK(cudaGraphLaunch(hit->exec, stream));
+    add_launch_counts(hit->counts);
+    if (result_index) *result_index = hit->result_index;
+    return OK;
+  }
+
+  // First use: capture the launch sequence on the library's own stream (the caller's may be the
+  // legacy default stream, which cannot be captured). Thread-local mode: other threads' CUDA
+  // calls do not disturb the capture. Nothing executes until the graph is launched below.
+  if (!g_capture_stream[dev])
+    MB_CUDA_CHECK(cudaStreamCreateWithFlags(&g_capture_stream[dev], cudaStreamNonBlocking));
+  GraphEntry fresh;
+  fresh.key = key;
+  fresh.last_use = ++g_graph_clock;
+  cudaGraph_t graph = nullptr;
+  int rc = OK;
+  if (cudaStreamBeginCapture(g_capture_stream[dev], cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+    set_launch_recorder(fresh.counts);
+    rc = ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, g_capture_stream[dev], &fresh.result_index);
+    set_launch_recorder(nullptr);
+    const cudaError_t ended = cudaStreamEndCapture(g_capture_stream[dev], &graph);
+    // The launches above were only recorded: take them out of the process totals again; the
+    // replay below (or the direct launch) counts them.
+    int64_t undo[K_KIND_COUNT];
+    for (int k = 0; k < K_KIND_COUNT; ++k) undo[k] = -fresh.counts[k];
+    add_launch_counts(undo);
+    if (rc != OK) {
+      // A launcher refused (bad argument, or a call the capture does not allow): nothing to
+      // cache; the direct launch reports the error, if it is one, against the caller's stream.
+      if (graph) cudaGraphDestroy(graph);
+      (void)cudaGetLastError();
+      return ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, stream, result_index);
+    }
+    if (ended != cudaSuccess || !graph ||
+        cudaGraphInstantiate(&fresh.exec, graph, 0) != cudaSuccess) {
+      fresh.exec = nullptr;
+    }
+    if (graph) cudaGraphDestroy(graph);
+  }
+  (void)cudaGetLastError();
+  if (g_graphs.size() >= kGraphCacheEntries) {
+    size_t oldest = 0;
+    for (size_t i = 1; i < g_graphs.size(); ++i)
+      if (g_graphs[i].last_use < g_graphs[oldest].last_use) oldest = i;
+    if (g_graphs[oldest].exec) cudaGraphExecDestroy(g_graphs[oldest].exec);
+    g_graphs.erase(g_graphs.begin() + oldest);
+  }
+  g_graphs.push_back(fresh);
+  if (!fresh.exec) return ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, stream, result_index);
+  MB_CUDA_CHECK(cudaGraphLaunch(fresh.exec, stream));
+  add_launch_counts(fresh.counts);
+  if (result_index) *result_index = fresh.result_index;
   return OK;
 }
 

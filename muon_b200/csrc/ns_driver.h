@@ -33,6 +33,20 @@ struct NsBuffers {
 int ns_iterate(const NsBuffers& buf, int batch, int64_t m, int64_t n, int mode, int steps,
                const float* coeffs, float eps, cudaStream_t stream, int* result_index);
 
+// Same launch sequence, replayed from a CUDA graph when that pays: a short iteration (a few
+// matrices of a few hundred rows) is thirteen kernels of microseconds each, and issuing them one
+// by one costs more host time than they take on the device. The first call for a given set of
+// buffers, sizes and coefficients captures the sequence on a stream the library owns (nothing
+// runs during capture), instantiates the graph and launches it on `stream`; later calls only
+// launch it. Falls back to ns_iterate when the work is large enough to hide its launches, when
+// per-kernel timing is on, when `stream` is itself being captured, or when graph replay is
+// switched off (set_graph_replay(false) or MUON_B200_GRAPH=0). Graph instantiation allocates
+// driver-side resources, so callers that must not allocate use ns_iterate.
+int ns_iterate_replayed(const NsBuffers& buf, int batch, int64_t m, int64_t n, int mode, int steps,
+                        const float* coeffs, float eps, cudaStream_t stream, int* result_index);
+void set_graph_replay(bool on);
+bool graph_replay_enabled();
+
 // Argument checks shared by both entry points: fills in the default step count.
 int ns_check_mode(int mode, int* steps, const float* coeffs);
 

@@ -10,15 +10,17 @@
 // (muon.py:404-405, :528-532, :696-697).
 //
 // Lines 1 and 2 only visit output tiles that touch the lower triangle. Inside such a
-// tile the products with row >= col are computed once, stored at (row, col) and
+// tile the values with row >= col are computed once, stored at (row, col) and
 // mirrored to (col, row); nothing above the diagonal is stored from its own position,
-// so the result is deterministic. The product part is therefore exactly symmetric.
-// Line 2's addend beta*A is taken per position (A[row, col] below the diagonal,
-// A[col, row] for the mirrored element), so the kernel computes alpha*A*A^T + beta*A as
-// the reference documents it (muon.py:483-486) even when A is not symmetric, which
-// happens in the first iteration (A/s scales rows only, muon.py:785). The reference
-// instead stores every computed tile and then its transpose (muon.py:534-544): its
-// output for a non-symmetric A depends on tile shape and store order.
+// so the result is deterministic.
+// Line 2 with a non-symmetric A (first iteration: A/s scales rows only, muon.py:785):
+// the reference stores every computed tile and then its transpose (muon.py:534-544), so
+// outside the tiles on the diagonal its output is the finished lower-triangle value,
+// addend beta*A[row, col] included, mirrored; on a diagonal tile the transposed store
+// lands last and the tile ends up holding its own transpose. With the 64 x 64 tiles its
+// autotuner picks on a B200 for every m <= 1024 that result is deterministic, and it is
+// what this kernel reproduces: finished values mirrored everywhere, the two addends
+// swapped inside the 64 x 64 blocks of the diagonal.
 //
 // Roles inside a CTA (64 + 32 * EW threads, EW = 4 or 8 epilogue warps):
 //   warp 0      TMA producer: fills a ring of {A tile, B tile} stages in shared memory
@@ -554,8 +556,8 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           for (int j = 0; j < 32; ++j) f[j] *= p.alpha;
           if constexpr (ADD == ADD_ROW_SCALED) {
             // The addend is S * w (rows scaled by w = 1/s), S symmetric and given unscaled:
-            // position (r, col) takes bf16(S[r,col] * w[r]) and its mirror bf16(S[r,col] * w[col]),
-            // bit for bit what the materialised scaled matrix holds at (r, col) and (col, r).
+            // bf16(S[r,col] * w[r]) is bit for bit what the materialised scaled matrix holds at
+            // (r, col), bf16(S[r,col] * w[col]) what it holds at (col, r).
             wv = p.row_scale + static_cast<long long>(tc.batch) * p.scale_bs;
             w_r = row_ok ? wv[r] : 0.f;
 #pragma unroll
@@ -590,44 +592,45 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             store_row32(out_row, col0, p.N, packed);
           }
         } else {
-          // Mirror: element (r, col) with col < r also lands at (col, r). `mp` holds the values
-          // for the mirrored positions; they differ from `packed` only when line 2's addend is
-          // not symmetric.
+          // Mirror: element (r, col) with col < r also lands at (col, r), with the same finished
+          // value (addend included), which is what the reference's transposed store of every
+          // off-diagonal tile leaves (muon.py:541-544). `mp` holds the values for the mirrored
+          // positions.
           uint32_t mp[16];
-          bool mirror_is_direct = true;
-          if constexpr (MODE == MODE_AXPBY) {
-            if constexpr (ADD == ADD_ROW_SCALED) {
-              mirror_is_direct = false;
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                // w[col] is the same address for every lane: one broadcast load.
-                const int col = col0 + 2 * j;
-                const float w0 = col < p.N ? __ldg(wv + col) : 0.f;
-                const float w1 = col + 1 < p.N ? __ldg(wv + col + 1) : 0.f;
-                const float m0 = __bfloat162float(__float2bfloat16_rn(a[2 * j] * w0));
-                const float m1 = __bfloat162float(__float2bfloat16_rn(a[2 * j + 1] * w1));
-                mp[j] = pack_bf16x2(fmaf(m0, p.beta, f[2 * j]), fmaf(m1, p.beta, f[2 * j + 1]));
-              }
-            } else if constexpr (ADD == ADD_GENERIC) {
-              // The product alpha*A*A^T is symmetric, the addend beta*A need not be: the
-              // mirrored position takes its own addend A[col, r].
-              mirror_is_direct = false;
-              const unsigned short* add_s = reinterpret_cast<const unsigned short*>(add_b);
+          for (int j = 0; j < 16; ++j) mp[j] = packed[j];
+          if constexpr (MODE == MODE_AXPBY && ADD != ADD_SYMMETRIC) {
+            // A not symmetric (first iteration, A / s). On a 64 x 64 tile of the diagonal the
+            // reference stores the tile and then its transpose over it, so position (r, col)
+            // ends up with the value computed for (col, r), i.e. with the addend beta * A[col, r],
+            // and (col, r) with the one computed for (r, col). Both 32 x 32 blocks of this chunk
+            // lie in one such tile or outside all of them: the test is the same for every lane.
+            if ((row_base >> 6) == (col0 >> 6)) {
+              if constexpr (ADD == ADD_ROW_SCALED) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const int col = col0 + 2 * j;
-                float t0 = 0.f, t1 = 0.f;
-                if (row_ok && col < r && col < p.N)
-                  t0 = bf16_bits_to_float(__ldg(add_s + static_cast<long long>(col) * p.ldadd + r));
-                if (row_ok && col + 1 < r && col + 1 < p.N)
-                  t1 = bf16_bits_to_float(__ldg(add_s + static_cast<long long>(col + 1) * p.ldadd + r));
-                mp[j] = pack_bf16x2(fmaf(t0, p.beta, f[2 * j]), fmaf(t1, p.beta, f[2 * j + 1]));
+                for (int j = 0; j < 16; ++j) {
+                  // A[col, r] = S[r, col] * w[col]; w[col] is one broadcast load for the warp.
+                  const int col = col0 + 2 * j;
+                  const float w0 = col < p.N ? __ldg(wv + col) : 0.f;
+                  const float w1 = col + 1 < p.N ? __ldg(wv + col + 1) : 0.f;
+                  const float m0 = __bfloat162float(__float2bfloat16_rn(a[2 * j] * w0));
+                  const float m1 = __bfloat162float(__float2bfloat16_rn(a[2 * j + 1] * w1));
+                  packed[j] = pack_bf16x2(fmaf(m0, p.beta, f[2 * j]), fmaf(m1, p.beta, f[2 * j + 1]));
+                }
+              } else {
+                const unsigned short* add_s = reinterpret_cast<const unsigned short*>(add_b);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  const int col = col0 + 2 * j;
+                  float t0 = a[2 * j], t1 = a[2 * j + 1];
+                  if (row_ok && col < r && col < p.N)
+                    t0 = bf16_bits_to_float(__ldg(add_s + static_cast<long long>(col) * p.ldadd + r));
+                  if (row_ok && col + 1 < r && col + 1 < p.N)
+                    t1 = bf16_bits_to_float(__ldg(add_s + static_cast<long long>(col + 1) * p.ldadd + r));
+                  packed[j] = pack_bf16x2(fmaf(t0, p.beta, f[2 * j]), fmaf(t1, p.beta, f[2 * j + 1]));
+                }
               }
             }
-          }
-          if (mirror_is_direct) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) mp[j] = packed[j];
           }
 
           if (full && col0 + 32 <= row_base) {

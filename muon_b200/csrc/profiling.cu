@@ -19,6 +19,7 @@ struct Interval {
 };
 std::vector<Interval> g_intervals;
 std::mutex g_mu;
+thread_local int64_t* t_recorder = nullptr;
 // Intervals folded away by compact(): per-kind totals that the next timing_collect adds in.
 double g_folded_ms[K_KIND_COUNT] = {};
 double g_folded_work[K_KIND_COUNT] = {};
@@ -53,6 +54,7 @@ void compact_locked() {
 LaunchScope::LaunchScope(int kind, double work, cudaStream_t stream, int64_t tag)
     : kind_(kind), work_(work), stream_(stream), tag_(tag) {
   g_counts[kind].fetch_add(1, std::memory_order_relaxed);
+  if (t_recorder) t_recorder[kind] += 1;
   if (g_timing.load(std::memory_order_relaxed)) {
     if (cudaEventCreate(&start_) == cudaSuccess) cudaEventRecord(start_, stream_);
     else start_ = nullptr;
@@ -73,6 +75,12 @@ LaunchScope::~LaunchScope() {
 }
 
 void timing_enable(bool on) { g_timing.store(on); }
+bool timing_enabled() { return g_timing.load(std::memory_order_relaxed); }
+void set_launch_recorder(int64_t* recorder) { t_recorder = recorder; }
+void add_launch_counts(const int64_t* counts) {
+  for (int k = 0; k < K_KIND_COUNT; ++k)
+    if (counts[k]) g_counts[k].fetch_add(counts[k], std::memory_order_relaxed);
+}
 
 int timing_collect(double* ms, double* work, int64_t* launches, int n_kinds) {
   std::vector<Interval> taken;

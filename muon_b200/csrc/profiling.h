@@ -39,6 +39,12 @@ class LaunchScope {
 // timing_collect adds in; timing_collect_records no longer lists them), so a long run that
 // never collects holds a bounded number of events.
 void timing_enable(bool on);
+bool timing_enabled();
+// While a recorder is installed on the calling thread, every LaunchScope it creates adds one to
+// recorder[kind] (used to remember which kernels a captured graph holds). Pass nullptr to remove.
+void set_launch_recorder(int64_t* recorder);
+// Adds per-kind launch counts (a replayed graph's kernels) to the process totals.
+void add_launch_counts(const int64_t* counts);
 // Waits for all recorded intervals, adds them up per kind and forgets them.
 int timing_collect(double* ms, double* work, int64_t* launches, int n_kinds);
 // Same, but one entry per launch (in launch order), at most `max_records`.

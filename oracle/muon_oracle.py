@@ -87,15 +87,19 @@ def ns_line_1(X: Tensor, *, mirror: str = "lower", tile: int = 64) -> Tensor:
     return _mirror(P, mirror, tile).to(X.dtype)
 
 
-def ns_line_2(A: Tensor, alpha: float, beta: float, *, mirror: str = "product", tile: int = 64) -> Tensor:
+def ns_line_2(A: Tensor, alpha: float, beta: float, *, mirror: str = "ref_square_tiles", tile: int = 64) -> Tensor:
     """B = alpha · A · Aᵀ + beta · A (muon.py:464-544).  Note Aᵀ: the kernel reads its
     second operand through swapped strides (muon.py:507-508).
 
-    ``mirror="product"`` (default, the rule of the CUDA kernel): the product A·Aᵀ is
-    computed for row >= col and mirrored, the addend beta·A is taken at each position —
-    i.e. the documented formula (muon.py:483-486) evaluated for any A.  The other
-    policies mirror the finished value, addend included, see ``_mirror``; they differ
-    from "product" only when A is not symmetric (first iteration, muon.py:785).
+    ``mirror="ref_square_tiles"`` with 64-wide tiles (default, and the rule of the CUDA
+    kernel): what the reference's two stores per tile (muon.py:534-544) leave with the
+    64 x 64 tiles its autotuner picks on a B200 for every m <= 1024 — finished values,
+    addend included, mirrored from below the diagonal; diagonal tiles hold their own
+    transpose.  Measured on a B200 (``tests/golden/make_reference_b200.py`` records the
+    pattern the reference leaves for a non-symmetric input).  ``mirror="product"`` mirrors
+    only the product A·Aᵀ and takes the addend beta·A at each position, i.e. the documented
+    formula (muon.py:483-486) evaluated for any A.  The policies differ only when A is not
+    symmetric (first iteration, muon.py:785).
     """
     Af = A.float()
     if mirror == "product":
@@ -114,7 +118,7 @@ def ns_line_3(B: Tensor, X: Tensor, a: float) -> Tensor:
 # --------------------------------------------------------------------------------------
 # Newton-Schulz drivers
 # --------------------------------------------------------------------------------------
-def zeropower_via_newtonschulz5(G: Tensor, epsilon: float = 1e-7, *, mirror: str = "product",
+def zeropower_via_newtonschulz5(G: Tensor, epsilon: float = 1e-7, *, mirror: str = "ref_square_tiles",
                                 dtype: torch.dtype = torch.bfloat16, glue: str = "fused") -> Tensor:
     """The live algorithm, muon.py:748-799: AOL rescale + 4 iterations.
 

@@ -118,11 +118,11 @@ def test_newton_schulz_aol4(mb, shape):
 
 def test_newton_schulz_against_outputs_of_the_real_reference(mb, golden):
     """Fixture `ns_reference_bf16`: outputs of the reference's own driver and kernels run on CPU
-    (tests/golden/make_golden.py). The kernels here follow the documented formula on diagonal
-    tiles and round the glue once, the fixture's run stores transposed diagonal tiles (64 wide)
-    and rounds after every op; on these one-to-three-tile matrices that is most of the matrix, so
-    the distance to the fixture must equal the oracle's own distance to it (the CUDA result sits
-    where the oracle's default sits), and both stay inside the same singular-value band."""
+    (tests/golden/make_golden.py) with 64-wide tiles, the tile shape its autotuner also picks on a
+    B200. The kernels here store what those tiles leave (finished values mirrored, diagonal tiles
+    transposed) and round the glue once where the fixture's uncompiled run rounds after every op:
+    within 2e-2 of the fixture on these one-to-three-tile matrices (the oracle's defaults are
+    6e-3 .. 9e-3 away from it), and never further from it than the oracle by more than 5e-3."""
     for c in golden("ns_reference_bf16")["cases"]:
         G, U_ref = c["G"], c["U"]
         U = mb.zeropower_via_newtonschulz5(G.to(DEV)).cpu()
@@ -130,7 +130,7 @@ def test_newton_schulz_against_outputs_of_the_real_reference(mb, golden):
         assert U.shape == U_ref.shape
         d_cuda, d_oracle = orc.rel_fro(U, U_ref), orc.rel_fro(O, U_ref)
         assert orc.rel_fro(U, O) <= 2e-2
-        assert d_cuda <= 8e-2 and abs(d_cuda - d_oracle) <= 1e-2, (tuple(G.shape), d_cuda, d_oracle)
+        assert d_cuda <= 2e-2 and d_cuda - d_oracle <= 5e-3, (tuple(G.shape), d_cuda, d_oracle)
         lo, hi = orc.singular_value_band(U)
         rlo, rhi = orc.singular_value_band(U_ref)
         assert abs(hi - rhi) <= 0.03, ((lo, hi), (rlo, rhi))
