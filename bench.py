@@ -68,7 +68,8 @@ WORKLOADS = {
     "conv-filters": ([(256, 256, 3, 3)] * 64 + [(128, 128, 3, 3)] * 64, torch.float32, 1.0,
                      "conv filters, 64 x 256x256x3x3 + 64 x 128x128x3x3, fp32"),
 }
-NS_ITERS = {"aol4": 4, "classic5": 5}  # the reference's live algorithm / its commented block
+# the reference's live algorithm / its commented block / the live algorithm with e4m3 Gram products
+NS_ITERS = {"aol4": 4, "classic5": 5, "aol4_fp8": 4}
 # The three small benchmark configurations, reported under `other_configs` at N = 1:
 # name -> (workload, optimizer class, number of 768-element gain vectors given to Adam,
 #          lower bound in ms at the measured peaks: NS FLOPs at the burst GEMM rate + elementwise
@@ -493,7 +494,8 @@ def cpu_sample_step(shapes_sample, dtype, grad_std, threads, ns_mode="aol4"):
     import functools
     from oracle import muon_oracle as orc
     torch.set_num_threads(threads)
-    ns = orc.zeropower_via_newtonschulz5 if ns_mode == "aol4" else functools.partial(orc.zeropower_classic5, fused=True)
+    ns = {"aol4": orc.zeropower_via_newtonschulz5, "aol4_fp8": orc.zeropower_aol4_fp8,
+          "classic5": functools.partial(orc.zeropower_classic5, fused=True)}[ns_mode]
     items = []
     for i, s in enumerate(shapes_sample):
         g = torch.Generator().manual_seed(4000 + i)
@@ -572,7 +574,8 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="llama3-8b-hidden")
     ap.add_argument("--ns-mode", choices=sorted(NS_ITERS), default="aol4",
                     help="aol4: the algorithm the reference executes; classic5: the Frobenius-normalised "
-                         "quintic iteration of its commented block (1.25x the NS FLOPs)")
+                         "quintic iteration of its commented block (1.25x the NS FLOPs); aol4_fp8: aol4 with "
+                         "the symmetric products of iterations 2..4 on e4m3 operands")
     ap.add_argument("--reference-gpu", choices=["recorded", "live"], default="recorded",
                     help="live: time the unmodified reference from baseline/_ref on this GPU (minutes)")
     ap.add_argument("--no-other-configs", action="store_true",

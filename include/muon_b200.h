@@ -31,15 +31,31 @@ extern "C" {
 #define MUON_B200_ERR_UNSUPPORTED (-4)
 #define MUON_B200_ERR_DEVICE_TIMEOUT (-5)
 
-/* Element types of parameters, gradients and optimizer state. */
+/* Element types. Parameters, gradients and optimizer state (prologue, epilogue, muon_step, adam)
+ * are float32 or bfloat16; the reference's elementwise code would also run on float16 and
+ * float64 parameters (muon.py:9-10, :66-67, :105-109), which this library does not implement.
+ * The input of muon_b200_zeropower and muon_b200_cast_bf16 may be any of the four, like the
+ * cast at muon.py:760. */
 #define MUON_B200_F32 0
 #define MUON_B200_BF16 1
+#define MUON_B200_F16 2
+#define MUON_B200_F64 3
 
 /* Newton-Schulz variants. AOL4 is what the reference executes (muon.py:748-799);
  * CLASSIC5 is the Frobenius-normalised quintic iteration the reference documents in
  * its commented block (muon.py:263-291). */
 #define MUON_B200_NS_AOL4 0
 #define MUON_B200_NS_CLASSIC5 1
+/* AOL4 with the two symmetric products of iterations 2..4 taken in 8-bit floating point (e4m3,
+ * fp32 accumulation, twice the tensor-core rate): line 1 multiplies e4m3(X * 2^k), line 2 is
+ * rewritten as c*E*E + (b + 2c)*A - c*I with E = A - I so that only the small matrix E is
+ * quantised; the first iteration (which fixes the row scales) and every line 3 stay in bf16.
+ * No counterpart in the reference. Its output differs from AOL4's by about 1e-2 relative
+ * Frobenius norm on wide and tall matrices (singular values within [0.97, 1.035] instead of
+ * [0.985, 1.015]) and by up to 4e-2 on square ones; matrices with fewer than 1024 columns
+ * (after transposing tall ones) are iterated in bf16 in this mode too, because the rounding noise
+ * of an e4m3 Gram entry only averages out over a long row. It is off unless asked for. */
+#define MUON_B200_NS_AOL4_FP8 2
 
 /* Upper bound on tensors per call of the multi-tensor entry points is unlimited;
  * internally they are processed in launches of this many. */
@@ -151,18 +167,49 @@ typedef struct muon_b200_ns_layout {
   int64_t x_offset_bytes, c_offset_bytes, a_offset_bytes, b_offset_bytes, partials_offset_bytes;
   int64_t ldn, x_bs; /* pitch and batch pitch of X and C, in elements */
   int64_t ldm, a_bs; /* pitch and batch pitch of A and B, in elements */
+  /* MUON_B200_NS_AOL4_FP8 only (0 otherwise): the e4m3 copies of X ([batch, m, ld8n] bytes) and of
+   * A - I ([batch, m, ld8m] bytes) that the iteration keeps beside the bf16 matrices */
+  int64_t x8_offset_bytes, e8_offset_bytes, ld8n, ld8m;
 } muon_b200_ns_layout;
 
+/* Layout for MUON_B200_NS_AOL4 / MUON_B200_NS_CLASSIC5 (they need the same workspace). */
 int muon_b200_ns_workspace_layout(int batch, int64_t m, int64_t n, muon_b200_ns_layout* out);
+/* Layout for a given mode: MUON_B200_NS_AOL4_FP8 needs about a quarter more. */
+int muon_b200_ns_workspace_layout_mode(int batch, int64_t m, int64_t n, int mode, muon_b200_ns_layout* out);
 
 /* Orthogonalises the `batch` matrices already stored (bf16, m x n, m <= n) in slot X of
- * `workspace`. mode is MUON_B200_NS_AOL4 or MUON_B200_NS_CLASSIC5; steps = 0 picks the
- * mode's default (4 / 5); coeffs is NULL or steps triples (a, b, c); eps is the clamp
+ * `workspace` (laid out by muon_b200_ns_workspace_layout_mode for the same mode). mode is one of
+ * the MUON_B200_NS_* constants; steps = 0 picks the mode's default (4, or 5 for CLASSIC5); coeffs is NULL or steps triples (a, b, c); eps is the clamp
  * (AOL) or the additive term (classic). On return *result_slot is 0 if the result is in
  * slot X and 1 if it is in slot C. `workspace` must be 256-byte aligned.
  * Replaces zeropower_via_newtonschulz5 (muon.py:748-799) from line 778 on. */
 int muon_b200_ns_run(void* workspace, int batch, int64_t m, int64_t n, int mode, int steps,
                      const float* coeffs, float eps, int* result_slot, muon_b200_stream_t stream);
+
+/* The whole of zeropower_via_newtonschulz5 (muon.py:748-799) in one call, with caller-owned input
+ * and output: g is [batch, rows, cols] of element type dtype (MUON_B200_F32/BF16/F16/F64), pitch ldg
+ * and batch pitch g_bs in elements, and is not modified. It is cast to bf16 (muon.py:760),
+ * transposed when rows > cols (muon.py:761-762) and orthogonalised; out receives the result of the
+ * m x n problem, m = min(rows, cols), n = max(rows, cols), as bf16 [batch, m, n] with pitch ldo >= n
+ * and batch pitch o_bs (multiples of 8, out 16-byte aligned) -- for rows > cols that is the
+ * transpose of the reference's return value, exactly the buffer its final .mT is a view of
+ * (muon.py:797-798). scratch: 256-byte aligned, at least
+ * muon_b200_zeropower_scratch_bytes(batch, rows, cols, mode) bytes, contents irrelevant before and
+ * after. mode, steps, coeffs, eps as for muon_b200_ns_run; graph replay applies when the same
+ * buffers come back. */
+int muon_b200_zeropower(const void* g, int dtype, int64_t rows, int64_t cols, int64_t ldg, int64_t g_bs,
+                        int batch, void* out, int64_t ldo, int64_t o_bs, void* scratch,
+                        int64_t scratch_bytes, int mode, int steps, const float* coeffs, float eps,
+                        muon_b200_stream_t stream);
+int64_t muon_b200_zeropower_scratch_bytes(int batch, int64_t rows, int64_t cols, int mode);
+
+/* dst = bf16(float(src) * scale), src [batch, rows, cols] of element type dtype, dst bf16
+ * [batch, rows, cols] or, with transpose != 0, [batch, cols, rows]; pitches in elements. src and
+ * dst may be the same bf16 buffer when transpose == 0 (used for the aspect scale of muon.py:14).
+ * Replaces G.to(torch.bfloat16), .mT and .contiguous() (muon.py:760-764). */
+int muon_b200_cast_bf16(const void* src, int dtype, int64_t rows, int64_t cols, int64_t ld_src,
+                        int64_t src_bs, void* dst, int64_t ld_dst, int64_t dst_bs, int batch,
+                        int transpose, float scale, muon_b200_stream_t stream);
 
 /* Newton-Schulz for callers that cannot allocate device memory: hosts whose allocator is
  * frozen while the step runs (memory-planned graphs, fixed-budget real-time loops) and
@@ -210,6 +257,17 @@ int muon_b200_prologue(void* const* grads, void* const* moms, int count, int64_t
 int muon_b200_epilogue(void* const* params, int count, int64_t rows, int64_t cols, int dtype,
                        const void* u, int64_t ldu, int64_t u_bs, int u_transposed, double lr,
                        double weight_decay, double scale, muon_b200_stream_t stream);
+
+/* The same update, with every new parameter value also stored into n_peers (0..7) other copies of
+ * the parameter: peer_params[r * count + i] is the address, valid on the current device, of
+ * parameter i in peer r's memory (from muon_b200_ipc_open, or any peer-accessible allocation of
+ * the same layout). The stores are plain global stores issued by the kernel that computes the
+ * value, so the exchange of the distributed step rides on the update itself and is complete when
+ * the kernel is. Replaces the update and the all_gather that follows it (muon.py:66-68). */
+int muon_b200_epilogue_push(void* const* params, void* const* peer_params, int n_peers, int count,
+                            int64_t rows, int64_t cols, int dtype, const void* u, int64_t ldu,
+                            int64_t u_bs, int u_transposed, double lr, double weight_decay,
+                            double scale, muon_b200_stream_t stream);
 
 /* Whole Muon update of `count` same-shape parameters: prologue -> NS -> epilogue, using
  * `workspace` (>= muon_b200_ns_workspace_layout(count, min(rows,cols), max(rows,cols))

@@ -12,8 +12,8 @@ from ctypes import POINTER, c_char_p, c_double, c_float, c_int, c_int64, c_void_
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG_DIR, "libmuon_b200.so")
 
-F32, BF16 = 0, 1
-NS_AOL4, NS_CLASSIC5 = 0, 1
+F32, BF16, F16, F64 = 0, 1, 2, 3
+NS_AOL4, NS_CLASSIC5, NS_AOL4_FP8 = 0, 1, 2
 
 ERR_NAMES = {
     -1: "INVALID_ARG",
@@ -35,7 +35,8 @@ class MuonB200Error(RuntimeError):
 class NsLayout(ctypes.Structure):
     _fields_ = [(name, c_int64) for name in (
         "total_bytes", "x_offset_bytes", "c_offset_bytes", "a_offset_bytes", "b_offset_bytes",
-        "partials_offset_bytes", "ldn", "x_bs", "ldm", "a_bs")]
+        "partials_offset_bytes", "ldn", "x_bs", "ldm", "a_bs", "x8_offset_bytes", "e8_offset_bytes",
+        "ld8n", "ld8m")]
 
 
 # name -> (restype, argtypes); mirrors include/muon_b200.h one to one.
@@ -50,6 +51,12 @@ PROTOTYPES = {
     "muon_b200_ns_run_static": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int,
                                         c_int64, c_int64, c_int, c_int, POINTER(c_float), c_float,
                                         c_void_p]),
+    "muon_b200_zeropower": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p,
+                                    c_int64, c_int64, c_void_p, c_int64, c_int, c_int, POINTER(c_float),
+                                    c_float, c_void_p]),
+    "muon_b200_zeropower_scratch_bytes": (c_int64, [c_int, c_int64, c_int64, c_int]),
+    "muon_b200_cast_bf16": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int64,
+                                    c_int64, c_int, c_int, c_float, c_void_p]),
     "muon_b200_ns_static_scratch_bytes": (c_int64, []),
     "muon_b200_ns_static_required_bytes": (c_int64, [c_int, c_int64, c_int64]),
     "muon_b200_ipc_export": (c_int, [c_void_p, c_void_p, POINTER(c_int64), POINTER(c_int64)]),
@@ -69,6 +76,7 @@ PROTOTYPES = {
     "muon_b200_ns_line3": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p,
                                    c_int64, c_int64, c_int, c_int64, c_int64, c_float, c_void_p]),
     "muon_b200_ns_workspace_layout": (c_int, [c_int, c_int64, c_int64, POINTER(NsLayout)]),
+    "muon_b200_ns_workspace_layout_mode": (c_int, [c_int, c_int64, c_int64, c_int, POINTER(NsLayout)]),
     "muon_b200_ns_run": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int, POINTER(c_float),
                                  c_float, POINTER(c_int), c_void_p]),
     "muon_b200_prologue": (c_int, [POINTER(c_void_p), POINTER(c_void_p), c_int, c_int64, c_int64,
@@ -76,6 +84,9 @@ PROTOTYPES = {
                                    c_void_p]),
     "muon_b200_epilogue": (c_int, [POINTER(c_void_p), c_int, c_int64, c_int64, c_int, c_void_p,
                                    c_int64, c_int64, c_int, c_double, c_double, c_double, c_void_p]),
+    "muon_b200_epilogue_push": (c_int, [POINTER(c_void_p), POINTER(c_void_p), c_int, c_int, c_int64, c_int64,
+                                        c_int, c_void_p, c_int64, c_int64, c_int, c_double, c_double,
+                                        c_double, c_void_p]),
     "muon_b200_muon_step": (c_int, [POINTER(c_void_p), POINTER(c_void_p), POINTER(c_void_p), c_int,
                                     c_int64, c_int64, c_int, c_double, c_double, c_double, c_int,
                                     c_double, c_int, c_int, POINTER(c_float), c_float, c_void_p,
@@ -154,7 +165,7 @@ def timing_collect_records(max_records: int = 1 << 16) -> list:
     return [(KERNEL_KINDS[kinds[i]], tags[i], ms[i], work[i]) for i in range(n.value)]
 
 
-def ns_layout(batch: int, m: int, n: int) -> NsLayout:
+def ns_layout(batch: int, m: int, n: int, mode: int = NS_AOL4) -> NsLayout:
     out = NsLayout()
-    check(lib.muon_b200_ns_workspace_layout(batch, m, n, ctypes.byref(out)))
+    check(lib.muon_b200_ns_workspace_layout_mode(batch, m, n, mode, ctypes.byref(out)))
     return out

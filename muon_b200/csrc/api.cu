@@ -136,6 +136,10 @@ int muon_b200_ns_line3(const void* b, int64_t ldb, int64_t b_bs, const void* x, 
 }
 
 int muon_b200_ns_workspace_layout(int batch, int64_t m, int64_t n, muon_b200_ns_layout* out) {
+  return muon_b200_ns_workspace_layout_mode(batch, m, n, MUON_B200_NS_AOL4, out);
+}
+
+int muon_b200_ns_workspace_layout_mode(int batch, int64_t m, int64_t n, int mode, muon_b200_ns_layout* out) {
   if (!out) return set_error(ERR_INVALID_ARG, "layout output is NULL");
   if (batch < 1 || m < 1 || n < 1)
     return set_error(ERR_INVALID_ARG, "workspace layout needs batch, m, n >= 1");
@@ -156,6 +160,14 @@ int muon_b200_ns_workspace_layout(int batch, int64_t m, int64_t n, muon_b200_ns_
   // fp32 scratch per matrix: Frobenius partial sums (classic) or the AOL row sums s (m floats).
   const int64_t per_matrix = l.ldm > kFroChunksMax ? l.ldm : kFroChunksMax;
   l.total_bytes = l.partials_offset_bytes + round_up((int64_t)batch * per_matrix * 4, 256);
+  l.x8_offset_bytes = l.e8_offset_bytes = 0;
+  l.ld8n = fp8_pitch(n);
+  l.ld8m = fp8_pitch(m);
+  if (mode == MUON_B200_NS_AOL4_FP8) {
+    l.x8_offset_bytes = l.total_bytes;
+    l.e8_offset_bytes = l.x8_offset_bytes + round_up(batch * m * l.ld8n, 256);
+    l.total_bytes += ns_fp8_extra_bytes(batch, m, n);
+  }
   *out = l;
   return OK;
 }
@@ -168,10 +180,18 @@ int muon_b200_ns_run(void* workspace, int batch, int64_t m, int64_t n, int mode,
   int rc = ns_check_mode(mode, &steps, coeffs);
   if (rc != OK) return rc;
   muon_b200_ns_layout l;
-  rc = muon_b200_ns_workspace_layout(batch, m, n, &l);
+  rc = muon_b200_ns_workspace_layout_mode(batch, m, n, mode, &l);
   if (rc != OK) return rc;
   char* ws = static_cast<char*>(workspace);
   NsBuffers buf{};
+  if (mode == MUON_B200_NS_AOL4_FP8) {
+    buf.x8 = reinterpret_cast<uint8_t*>(ws + l.x8_offset_bytes);
+    buf.e8 = reinterpret_cast<uint8_t*>(ws + l.e8_offset_bytes);
+    buf.ld8n = l.ld8n;
+    buf.ld8m = l.ld8m;
+    buf.x8_bs = m * l.ld8n;
+    buf.e8_bs = m * l.ld8m;
+  }
   buf.x[0] = bf(static_cast<void*>(ws + l.x_offset_bytes));
   buf.x[1] = bf(static_cast<void*>(ws + l.c_offset_bytes));
   buf.ldx[0] = buf.ldx[1] = l.ldn;
@@ -185,6 +205,49 @@ int muon_b200_ns_run(void* workspace, int batch, int64_t m, int64_t n, int mode,
   buf.fscratch = reinterpret_cast<float*>(ws + l.partials_offset_bytes);
   buf.f_bs = l.ldm;
   return ns_iterate_replayed(buf, batch, m, n, mode, steps, coeffs, eps, as_stream(stream), result_slot);
+}
+
+int64_t muon_b200_zeropower_scratch_bytes(int batch, int64_t rows, int64_t cols, int mode) {
+  return rows <= cols ? ns_scratch_bytes(batch, rows, cols, mode) : ns_scratch_bytes(batch, cols, rows, mode);
+}
+
+int muon_b200_zeropower(const void* g, int dtype, int64_t rows, int64_t cols, int64_t ldg, int64_t g_bs,
+                        int batch, void* out, int64_t ldo, int64_t o_bs, void* scratch,
+                        int64_t scratch_bytes, int mode, int steps, const float* coeffs, float eps,
+                        muon_b200_stream_t stream) {
+  if (!g || !out || !scratch) return set_error(ERR_INVALID_ARG, "zeropower: null pointer");
+  if (dtype < DT_F32 || dtype > DT_F64) return set_error(ERR_INVALID_ARG, "zeropower: unknown element type %d", dtype);
+  if (batch < 1 || rows < 1 || cols < 1 || rows > INT32_MAX || cols > INT32_MAX)
+    return set_error(ERR_INVALID_ARG, "zeropower needs batch, rows, cols >= 1");
+  int rc = ns_check_mode(mode, &steps, coeffs);
+  if (rc != OK) return rc;
+  const int64_t m = rows <= cols ? rows : cols, n = rows <= cols ? cols : rows;
+  if ((reinterpret_cast<uintptr_t>(out) & 15) || (ldo % 8) || (o_bs % 8) || ldo < n ||
+      (batch > 1 && o_bs < (m - 1) * ldo + n))
+    return set_error(ERR_ALIGNMENT, "zeropower: out must be 16-byte aligned with pitches %% 8 == 0 and >= n");
+  if (ldg < cols || (batch > 1 && g_bs < (rows - 1) * ldg + cols))
+    return set_error(ERR_INVALID_ARG, "zeropower: input pitch shorter than a row or a matrix");
+  if (reinterpret_cast<uintptr_t>(scratch) & 255)
+    return set_error(ERR_ALIGNMENT, "zeropower: scratch must be 256-byte aligned");
+  const int64_t need = ns_scratch_bytes(batch, m, n, mode);
+  if (scratch_bytes < need)
+    return set_error(ERR_INVALID_ARG, "zeropower: scratch too small: %lld bytes given, %lld needed",
+                     (long long)scratch_bytes, (long long)need);
+  return ns_run_with_scratch(g, dtype, rows, cols, ldg, g_bs, bf(out), ldo, o_bs,
+                             static_cast<unsigned char*>(scratch), batch, mode, steps, coeffs, eps,
+                             /*replay=*/true, as_stream(stream));
+}
+
+int muon_b200_cast_bf16(const void* src, int dtype, int64_t rows, int64_t cols, int64_t ld_src,
+                        int64_t src_bs, void* dst, int64_t ld_dst, int64_t dst_bs, int batch,
+                        int transpose, float scale, muon_b200_stream_t stream) {
+  if (!src || !dst) return set_error(ERR_INVALID_ARG, "cast: null pointer");
+  if (batch < 1 || rows < 1 || cols < 1 || rows > INT32_MAX || cols > INT32_MAX)
+    return set_error(ERR_INVALID_ARG, "cast needs batch, rows, cols >= 1");
+  if (ld_src < cols || ld_dst < (transpose ? rows : cols))
+    return set_error(ERR_INVALID_ARG, "cast: pitch shorter than a row");
+  return launch_cast_bf16(src, dtype, ld_src, src_bs, bf(dst), ld_dst, dst_bs, (int)rows, (int)cols, batch,
+                          transpose ? 1 : 0, scale, as_stream(stream));
 }
 
 int muon_b200_prologue(void* const* grads, void* const* moms, int count, int64_t rows,
@@ -225,24 +288,37 @@ int muon_b200_prologue(void* const* grads, void* const* moms, int count, int64_t
   return OK;
 }
 
-int muon_b200_epilogue(void* const* params, int count, int64_t rows, int64_t cols, int dtype,
-                       const void* u, int64_t ldu, int64_t u_bs, int u_transposed, double lr,
-                       double weight_decay, double scale, muon_b200_stream_t stream) {
+int muon_b200_epilogue_push(void* const* params, void* const* peer_params, int n_peers, int count,
+                            int64_t rows, int64_t cols, int dtype, const void* u, int64_t ldu,
+                            int64_t u_bs, int u_transposed, double lr, double weight_decay,
+                            double scale, muon_b200_stream_t stream) {
   int rc = check_dtype(dtype);
   if (rc != OK) return rc;
   if (!params || !u) return set_error(ERR_INVALID_ARG, "null pointer passed to epilogue");
   if (count < 1 || rows < 1 || cols < 1 || rows > INT32_MAX || cols > INT32_MAX)
     return set_error(ERR_INVALID_ARG, "epilogue needs count, rows, cols >= 1");
+  if (n_peers < 0 || n_peers > kMaxPeers || (n_peers > 0 && !peer_params))
+    return set_error(ERR_INVALID_ARG, "epilogue: between 0 and %d peer copies per parameter (got %d)",
+                     kMaxPeers, n_peers);
   if ((reinterpret_cast<uintptr_t>(u) & 15) || (ldu % 8) || (u_bs % 8))
     return set_error(ERR_ALIGNMENT, "epilogue U must be 16-byte aligned with pitches %% 8 == 0");
   const int vec = dtype == DT_F32 ? 4 : 8;
   for (int base = 0; base < count; base += kMaxTensors) {
     const int n = count - base < kMaxTensors ? count - base : kMaxTensors;
     EpilogueArgs a{};
+    EpiloguePeers peers{};
+    peers.n_peers = n_peers;
+    bool aligned = (cols % vec == 0) && all_aligned16(params + base, n);
     for (int i = 0; i < n; ++i) {
       if (!params[base + i])
         return set_error(ERR_INVALID_ARG, "epilogue tensor %d has a null pointer", base + i);
       a.param[i] = params[base + i];
+      for (int r = 0; r < n_peers; ++r) {
+        void* q = peer_params[(int64_t)r * count + base + i];
+        if (!q) return set_error(ERR_INVALID_ARG, "epilogue tensor %d has a null peer pointer", base + i);
+        peers.param[r][i] = q;
+        aligned = aligned && (reinterpret_cast<uintptr_t>(q) & 15) == 0;
+      }
     }
     a.u = bf(u) + (int64_t)base * u_bs;
     a.u_bs = u_bs;
@@ -250,14 +326,21 @@ int muon_b200_epilogue(void* const* params, int count, int64_t rows, int64_t col
     a.count = n;
     a.rows = (int)rows;
     a.cols = (int)cols;
-    a.vec_ok = (cols % vec == 0) && all_aligned16(params + base, n);
+    a.vec_ok = aligned;
     a.scale = (float)scale;
     a.decay = (float)(1.0 - lr * weight_decay);
     a.neg_lr = (float)(-lr);
-    rc = launch_epilogue(a, dtype, u_transposed ? 1 : 0, as_stream(stream));
+    rc = launch_epilogue(a, dtype, u_transposed ? 1 : 0, as_stream(stream), n_peers > 0 ? &peers : nullptr);
     if (rc != OK) return rc;
   }
   return OK;
+}
+
+int muon_b200_epilogue(void* const* params, int count, int64_t rows, int64_t cols, int dtype,
+                       const void* u, int64_t ldu, int64_t u_bs, int u_transposed, double lr,
+                       double weight_decay, double scale, muon_b200_stream_t stream) {
+  return muon_b200_epilogue_push(params, nullptr, 0, count, rows, cols, dtype, u, ldu, u_bs, u_transposed,
+                                 lr, weight_decay, scale, stream);
 }
 
 int muon_b200_muon_step(void* const* params, void* const* grads, void* const* moms, int count,
@@ -272,7 +355,7 @@ int muon_b200_muon_step(void* const* params, void* const* grads, void* const* mo
   const int64_t m = tall ? cols : rows;
   const int64_t n = tall ? rows : cols;
   muon_b200_ns_layout l;
-  int rc = muon_b200_ns_workspace_layout(count, m, n, &l);
+  int rc = muon_b200_ns_workspace_layout_mode(count, m, n, ns_mode, &l);
   if (rc != OK) return rc;
   if (workspace_bytes < l.total_bytes)
     return set_error(ERR_INVALID_ARG, "workspace too small: %lld bytes given, %lld needed",

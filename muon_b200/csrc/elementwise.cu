@@ -5,6 +5,8 @@
 // launch instead of one per parameter.
 #include "common.cuh"
 #include "elementwise.h"
+
+#include <cuda_fp16.h>
 #include "ns_gemm.h"
 #include "profiling.h"
 
@@ -265,10 +267,12 @@ prologue_kernel(const PrologueArgs a) {
 //   p  = T(p * (1 - lr*wd))         (p.mul_)
 //   p  = T(p - lr * U')             (p.add_(update, alpha=-lr))
 // U is [rows, cols] or, for tall parameters, stored transposed as [cols, rows].
+// With PUSH the new value also goes to the same element of every peer copy (the exchange of
+// the distributed step, reference dist.all_gather at muon.py:68, done by the producing kernel).
 // ---------------------------------------------------------------------------
-template <typename T, bool TRANSPOSE>
+template <typename T, bool TRANSPOSE, bool PUSH>
 __global__ void __launch_bounds__(kThreads)
-epilogue_kernel(const EpilogueArgs a) {
+epilogue_kernel(const EpilogueArgs a, const EpiloguePeers peers) {
   constexpr int V = Vec<T>::N;
   constexpr int kTileCols = 16 * V;
   __shared__ __nv_bfloat16 tile[TRANSPOSE ? kTileCols : 1][TRANSPOSE ? kTileRows + 2 : 1];
@@ -363,10 +367,19 @@ epilogue_kernel(const EpilogueArgs a) {
         }
         if (full) {
           Vec<T>::store(p + off, pv);
+          if (PUSH) {
+            for (int r = 0; r < peers.n_peers; ++r) Vec<T>::store(static_cast<T*>(peers.param[r][ti]) + off, pv);
+          }
         } else {
 #pragma unroll
           for (int j = 0; j < V; ++j)
-            if (c0 + j < a.cols) p[off + j] = from_f<T>(pv[j]);
+            if (c0 + j < a.cols) {
+              p[off + j] = from_f<T>(pv[j]);
+              if (PUSH) {
+                for (int r = 0; r < peers.n_peers; ++r)
+                  static_cast<T*>(peers.param[r][ti])[off + j] = from_f<T>(pv[j]);
+              }
+            }
         }
       }
      }
@@ -376,14 +389,17 @@ epilogue_kernel(const EpilogueArgs a) {
 }
 
 // ---------------------------------------------------------------------------
-// AOL rescale (reference muon.py:779-785), one CTA per matrix row i:
-//   s_i  = bf16( max( sum_j |A_ij|, eps ) )
-//   X_i: = bf16( X_i: * rsqrt(s_i) )
-//   A_i: = bf16( A_i: * (1/s_i) )      (rows only, exactly as the reference does; the
-//                                       quotient is formed with the correctly rounded
-//                                       reciprocal so that other kernels can rebuild it)
+// AOL rescale (reference muon.py:779-785), one CTA per matrix row i, with the rounding points of
+// the reference's compiled graph (one reduction kernel that also divides, one pointwise kernel
+// that reads the stored sums):
+//   s_i  = sum_j |A_ij|                         (fp32)
+//   A_i: = bf16( A_i: * (1 / max(s_i, eps)) )   (rows only, exactly as the reference does; the
+//                                                quotient uses the unrounded fp32 sum and is formed
+//                                                with the correctly rounded reciprocal, so that
+//                                                other kernels can rebuild it bit for bit)
+//   X_i: = bf16( X_i: * rsqrt(max(bf16(s_i), eps)) )   (the sums are materialised in bf16)
 // The scaled A goes to A_out (same pitches; may be A itself) so that the symmetric,
-// unscaled A stays available; 1/s goes to svec (one float per row) when given.
+// unscaled A stays available; 1/max(s_i, eps) goes to svec (one float per row) when given.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads)
 aol_rescale_kernel(__nv_bfloat16* X, long long ldx, long long x_bs, const __nv_bfloat16* A,
@@ -418,13 +434,13 @@ aol_rescale_kernel(__nv_bfloat16* X, long long ldx, long long x_bs, const __nv_b
     if (threadIdx.x == 0) {
       float s = 0.f;
       for (int w = 0; w < kThreads / 32; ++w) s += warp_sums[w];
-      s_bcast = bf16_round(fmaxf(s, eps));
-      if (svec) svec[(long long)b * s_bs + i] = __frcp_rn(s_bcast);
+      s_bcast = s;
+      if (svec) svec[(long long)b * s_bs + i] = __frcp_rn(fmaxf(s, eps));
     }
     __syncthreads();
     const float s = s_bcast;
-    const float rs = rsqrtf(s);
-    const float w = __frcp_rn(s);  // A / s is evaluated as A * (1/s), one rounding each
+    const float rs = rsqrtf(fmaxf(bf16_round(s), eps));
+    const float w = __frcp_rn(fmaxf(s, eps));  // A / s is evaluated as A * (1/s), one rounding each
     for (int j = threadIdx.x * 8; j < mv; j += kThreads * 8) {
       float v[8];
       Vec<__nv_bfloat16>::load(arow + j, v);
@@ -589,6 +605,61 @@ adam_kernel(const AdamArgs a) {
   }
 }
 
+// ---------------------------------------------------------------------------
+// Cast (+ transposition, + scale) into bf16: the entry of zeropower_via_newtonschulz5
+// (X = G.to(bfloat16), X.mT for tall inputs, .contiguous(); muon.py:760-764) and the aspect
+// scale of muon_update (muon.py:14). 32 x 32 tiles through shared memory when transposing.
+// ---------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float load_as_float(const T* p);
+template <>
+__device__ __forceinline__ float load_as_float<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float load_as_float<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <>
+__device__ __forceinline__ float load_as_float<__half>(const __half* p) { return __half2float(*p); }
+template <>
+__device__ __forceinline__ float load_as_float<double>(const double* p) {
+  // double -> bf16 in one rounding would need a 64-bit path; going through float first rounds
+  // twice, which differs from the direct conversion only on exact ties of the float rounding.
+  return static_cast<float>(*p);
+}
+
+template <typename T, bool TRANSPOSE>
+__global__ void __launch_bounds__(kThreads)
+cast_bf16_kernel(const T* src, long long ld_src, long long src_bs, __nv_bfloat16* dst, long long ld_dst,
+                 long long dst_bs, int rows, int cols, int batch, float scale) {
+  __shared__ __nv_bfloat16 tile[TRANSPOSE ? 32 : 1][TRANSPOSE ? 34 : 1];
+  const int tiles_c = (cols + 31) / 32, tiles_r = (rows + 31) / 32;
+  const long long per = (long long)tiles_c * tiles_r, total = per * batch;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8 threads
+  for (long long t = blockIdx.x; t < total; t += gridDim.x) {
+    const int b = (int)(t / per);
+    const long long rem = t - (long long)b * per;
+    const int tr = (int)(rem / tiles_c), tcn = (int)(rem - (long long)tr * tiles_c);
+    const T* s = src + (long long)b * src_bs;
+    __nv_bfloat16* d = dst + (long long)b * dst_bs;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int r = tr * 32 + ty + 8 * k, c = tcn * 32 + tx;
+      if (r < rows && c < cols) {
+        const __nv_bfloat16 v = __float2bfloat16_rn(load_as_float<T>(s + (long long)r * ld_src + c) * scale);
+        if (TRANSPOSE) tile[tx][ty + 8 * k] = v;
+        else d[(long long)r * ld_dst + c] = v;
+      }
+    }
+    if (TRANSPOSE) {
+      __syncthreads();
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int c = tcn * 32 + ty + 8 * k, r = tr * 32 + tx;  // output row c, output column r
+        if (r < rows && c < cols) d[(long long)c * ld_dst + r] = tile[ty + 8 * k][tx];
+      }
+      __syncthreads();
+    }
+  }
+}
+
 int grid_for(long long work_items, int per_sm) {
   int sms = 0;
   if (device_sm_count(&sms) != OK) return -1;
@@ -623,20 +694,32 @@ int launch_prologue(const PrologueArgs& a, int dtype, int transpose, cudaStream_
   return OK;
 }
 
-int launch_epilogue(const EpilogueArgs& a, int dtype, int transpose, cudaStream_t stream) {
+template <typename T, bool TRANSPOSE>
+void launch_epilogue_variant(int grid, const EpilogueArgs& a, const EpiloguePeers* peers, cudaStream_t stream) {
+  if (peers && peers->n_peers > 0) {
+    epilogue_kernel<T, TRANSPOSE, true><<<grid, kThreads, 0, stream>>>(a, *peers);
+  } else {
+    EpiloguePeers none;
+    none.n_peers = 0;
+    epilogue_kernel<T, TRANSPOSE, false><<<grid, kThreads, 0, stream>>>(a, none);
+  }
+}
+
+int launch_epilogue(const EpilogueArgs& a, int dtype, int transpose, cudaStream_t stream,
+                    const EpiloguePeers* peers) {
   const int tile_cols = 16 * (dtype == DT_F32 ? 4 : 8);
   long long tiles = (long long)((a.cols + tile_cols - 1) / tile_cols) *
                     ((a.rows + kTileRows - 1) / kTileRows) * a.count;
   int grid = grid_for(tiles, 8);
   if (grid < 0) return ERR_UNSUPPORTED;
-  const double b = dtype == DT_F32 ? 4 : 2;  // read bf16 U; read and write p
+  const double b = dtype == DT_F32 ? 4 : 2;  // read bf16 U; read and write p (peer copies not counted)
   LaunchScope scope(K_EPILOGUE, (double)a.rows * a.cols * a.count * (2 * b + 2), stream);
   if (dtype == DT_F32) {
-    if (transpose) epilogue_kernel<float, true><<<grid, kThreads, 0, stream>>>(a);
-    else epilogue_kernel<float, false><<<grid, kThreads, 0, stream>>>(a);
+    if (transpose) launch_epilogue_variant<float, true>(grid, a, peers, stream);
+    else launch_epilogue_variant<float, false>(grid, a, peers, stream);
   } else {
-    if (transpose) epilogue_kernel<__nv_bfloat16, true><<<grid, kThreads, 0, stream>>>(a);
-    else epilogue_kernel<__nv_bfloat16, false><<<grid, kThreads, 0, stream>>>(a);
+    if (transpose) launch_epilogue_variant<__nv_bfloat16, true>(grid, a, peers, stream);
+    else launch_epilogue_variant<__nv_bfloat16, false>(grid, a, peers, stream);
   }
   MB_CUDA_CHECK(cudaGetLastError());
   return OK;
@@ -672,6 +755,33 @@ int launch_fro_normalize(__nv_bfloat16* X, long long ldx, long long x_bs, int m,
   sumsq_partial_kernel<<<grid, kThreads, 0, stream>>>(X, ldx, x_bs, m, n, chunks, partials);
   MB_CUDA_CHECK(cudaGetLastError());
   fro_scale_kernel<<<grid, kThreads, 0, stream>>>(X, ldx, x_bs, m, n, chunks, partials, eps);
+  MB_CUDA_CHECK(cudaGetLastError());
+  return OK;
+}
+
+int launch_cast_bf16(const void* src, int dtype, long long ld_src, long long src_bs, __nv_bfloat16* dst,
+                     long long ld_dst, long long dst_bs, int rows, int cols, int batch, int transpose,
+                     float scale, cudaStream_t stream) {
+  const long long tiles = (long long)((cols + 31) / 32) * ((rows + 31) / 32) * batch;
+  int grid = grid_for(tiles, 8);
+  if (grid < 0) return ERR_UNSUPPORTED;
+#define MB_CAST(T)                                                                                      \
+  do {                                                                                                  \
+    if (transpose)                                                                                      \
+      cast_bf16_kernel<T, true><<<grid, kThreads, 0, stream>>>(static_cast<const T*>(src), ld_src, src_bs, \
+                                                               dst, ld_dst, dst_bs, rows, cols, batch, scale); \
+    else                                                                                                \
+      cast_bf16_kernel<T, false><<<grid, kThreads, 0, stream>>>(static_cast<const T*>(src), ld_src, src_bs, \
+                                                                dst, ld_dst, dst_bs, rows, cols, batch, scale); \
+  } while (0)
+  switch (dtype) {
+    case DT_F32: MB_CAST(float); break;
+    case DT_BF16: MB_CAST(__nv_bfloat16); break;
+    case DT_F16: MB_CAST(__half); break;
+    case DT_F64: MB_CAST(double); break;
+    default: return set_error(ERR_INVALID_ARG, "cast: unknown element type %d", dtype);
+  }
+#undef MB_CAST
   MB_CUDA_CHECK(cudaGetLastError());
   return OK;
 }

@@ -7,7 +7,8 @@
 
 namespace mb {
 
-enum DType : int { DT_F32 = 0, DT_BF16 = 1 };
+// DT_F16 and DT_F64 are accepted by the cast kernel only (inputs of the functional Newton-Schulz).
+enum DType : int { DT_F32 = 0, DT_BF16 = 1, DT_F16 = 2, DT_F64 = 3 };
 
 constexpr int kMaxTensors = 32;  // tensors per multi-tensor launch
 
@@ -38,6 +39,14 @@ struct EpilogueArgs {
   float neg_lr;  // float(-lr)
 };
 
+// Copies of the same parameters in other GPUs' memory (mapped on this device): the epilogue
+// kernel stores every updated element there as well, with plain stores over NVLink.
+constexpr int kMaxPeers = 7;
+struct EpiloguePeers {
+  void* param[kMaxPeers][kMaxTensors];
+  int n_peers;
+};
+
 struct AdamArgs {
   void* param[kMaxTensors];
   void* grad[kMaxTensors];
@@ -57,12 +66,19 @@ struct AdamArgs {
 
 int adam_elems_per_block(int dtype);
 int launch_prologue(const PrologueArgs& a, int dtype, int transpose, cudaStream_t stream);
-int launch_epilogue(const EpilogueArgs& a, int dtype, int transpose, cudaStream_t stream);
+int launch_epilogue(const EpilogueArgs& a, int dtype, int transpose, cudaStream_t stream,
+                    const EpiloguePeers* peers = nullptr);
 int launch_aol_rescale(__nv_bfloat16* X, long long ldx, long long x_bs, const __nv_bfloat16* A,
                        __nv_bfloat16* A_out, long long lda, long long a_bs, float* svec,
                        long long s_bs, int m, int n, int batch, float eps, cudaStream_t stream);
 int launch_fro_normalize(__nv_bfloat16* X, long long ldx, long long x_bs, int m, int n, int batch,
                          float eps, float* partials, int chunks, cudaStream_t stream);
 int launch_adam(const AdamArgs& a, int dtype, cudaStream_t stream);
+// dst[b][r][c] (or dst[b][c][r] when transpose) = bf16(float(src[b][r][c]) * scale); src has
+// element type `dtype`, pitches in elements. src and dst may be the same buffer when the types
+// and pitches agree and transpose == 0.
+int launch_cast_bf16(const void* src, int dtype, long long ld_src, long long src_bs, __nv_bfloat16* dst,
+                     long long ld_dst, long long dst_bs, int rows, int cols, int batch, int transpose,
+                     float scale, cudaStream_t stream);
 
 }  // namespace mb

@@ -51,8 +51,6 @@ int scratch_for_current_device(unsigned char** out) {
   return OK;
 }
 
-inline int64_t round_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
-
 // Byte range [lo, hi) that a [batch, m, n] bf16 tensor with the given pitches touches.
 void byte_range(const void* p, int64_t ld, int64_t bs, int batch, int64_t m, int64_t n,
                 uintptr_t* lo, uintptr_t* hi) {
@@ -68,12 +66,7 @@ extern "C" {
 int64_t muon_b200_ns_static_scratch_bytes(void) { return (int64_t)kStaticScratchBytes; }
 
 int64_t muon_b200_ns_static_required_bytes(int batch, int64_t m, int64_t n) {
-  if (batch < 1 || m < 1 || n < m) return -1;
-  const int64_t ldn = round_up(n, 8), ldm = round_up(m, 8);
-  const int64_t xs = round_up(batch * m * ldn * 2, 256);
-  const int64_t as = round_up(batch * m * ldm * 2, 256);
-  const int64_t per_matrix = ldm > kFroChunksMax ? ldm : kFroChunksMax;
-  return xs + 3 * as + round_up((int64_t)batch * per_matrix * 4, 256);
+  return ns_scratch_bytes(batch, m, n);
 }
 
 int muon_b200_ns_run_static(const void* x, int64_t ldx, int64_t x_bs, void* out, int64_t ldo,
@@ -84,6 +77,8 @@ int muon_b200_ns_run_static(const void* x, int64_t ldx, int64_t x_bs, void* out,
     return set_error(ERR_INVALID_ARG, "ns_run_static needs batch >= 1 and 1 <= m <= n");
   int rc = ns_check_mode(mode, &steps, coeffs);
   if (rc != OK) return rc;
+  if (mode == MUON_B200_NS_AOL4_FP8)
+    return set_error(ERR_UNSUPPORTED, "ns_run_static: the e4m3 variant needs a caller workspace (muon_b200_ns_run)");
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) ||
       (ldx % 8) || (ldo % 8) || (x_bs % 8) || (o_bs % 8) || ldx < n || ldo < n)
     return set_error(ERR_ALIGNMENT,
@@ -110,40 +105,11 @@ int muon_b200_ns_run_static(const void* x, int64_t ldx, int64_t x_bs, void* out,
   rc = scratch_for_current_device(&base);
   if (rc != OK) return rc;
 
-  const int64_t ldn = round_up(n, 8), ldm = round_up(m, 8);
-  const int64_t xs = round_up(batch * m * ldn * 2, 256);
-  const int64_t as = round_up(batch * m * ldm * 2, 256);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-
-  // The iteration ping-pongs between two buffers and must end in `out`: with an even number of
-  // iterations it starts there, with an odd number it starts in the built-in buffer.
-  const int o = (steps % 2 == 0) ? 0 : 1;  // index of `out` among the two iterate buffers
-  NsBuffers buf{};
-  buf.x[o] = static_cast<__nv_bfloat16*>(out);
-  buf.ldx[o] = ldo;
-  buf.x_bs[o] = o_bs;
-  buf.x[o ^ 1] = reinterpret_cast<__nv_bfloat16*>(base);
-  buf.ldx[o ^ 1] = ldn;
-  buf.x_bs[o ^ 1] = m * ldn;
-  buf.A = reinterpret_cast<__nv_bfloat16*>(base + xs);
-  buf.A_scaled = reinterpret_cast<__nv_bfloat16*>(base + xs + as);  // row-scaled copy of A
-  buf.B = reinterpret_cast<__nv_bfloat16*>(base + xs + 2 * as);
-  buf.ldm = ldm;
-  buf.a_bs = m * ldm;
-  buf.fscratch = reinterpret_cast<float*>(base + xs + 3 * as);
-  buf.f_bs = ldm;
-  for (int b = 0; b < batch; ++b)
-    MB_CUDA_CHECK(cudaMemcpy2DAsync(buf.x[0] + (int64_t)b * buf.x_bs[0], (size_t)buf.ldx[0] * 2,
-                                    static_cast<const __nv_bfloat16*>(x) + (int64_t)b * x_bs,
-                                    (size_t)ldx * 2, (size_t)n * 2, (size_t)m,
-                                    cudaMemcpyDeviceToDevice, st));
-  // Nothing in the scratch has to start at zero: A, B, the scaled copy, the row scales and the
-  // ping-pong buffer are each written in full before they are read.
-  int where = 0;
-  rc = ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, st, &where);
-  if (rc != OK) return rc;
-  if (where != o) return set_error(ERR_CUDA, "ns_run_static: result landed in the wrong buffer");
-  return OK;
+  // Same launch sequence as muon_b200_ns_run, never replayed from a graph (instantiating one
+  // allocates driver resources).
+  return ns_run_with_scratch(x, DT_BF16, m, n, ldx, x_bs, static_cast<__nv_bfloat16*>(out), ldo, o_bs, base,
+                             batch, mode, steps, coeffs, eps, /*replay=*/false,
+                             static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

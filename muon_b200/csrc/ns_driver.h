@@ -11,6 +11,7 @@
 namespace mb {
 
 constexpr int kFroChunksMax = 296;  // partial sums per matrix of the Frobenius reduction
+constexpr int kFp8MinCols = 1024;   // MUON_B200_NS_AOL4_FP8: narrower matrices stay in bf16
 
 struct NsBuffers {
   // The iterate ping-pongs between x[0] (holds the input on entry) and x[1]; both are
@@ -26,7 +27,16 @@ struct NsBuffers {
   // fp32 scratch, per matrix max(ldm, kFroChunksMax) floats: row scales 1/s or Frobenius partials.
   float* fscratch;
   int64_t f_bs;
+  // MUON_B200_NS_AOL4_FP8 only: e4m3 copies X8 = e4m3(X * sx) [batch, m, ld8n] and
+  // E8 = e4m3((A - I) * se) [batch, m, ld8m] (pitches in bytes, multiples of 16).
+  uint8_t* x8;
+  uint8_t* e8;
+  int64_t ld8n, x8_bs, ld8m, e8_bs;
 };
+
+// Pitches (bytes) of the e4m3 copies and the bytes they add to a workspace or scratch area.
+inline int64_t fp8_pitch(int64_t cols) { return (cols + 15) / 16 * 16; }
+int64_t ns_fp8_extra_bytes(int batch, int64_t m, int64_t n);
 
 // steps > 0; coeffs is NULL (the mode's table) or steps triples (a, b, c). On success
 // *result_index tells which of x[0] / x[1] holds the result (steps % 2).
@@ -46,6 +56,20 @@ int ns_iterate_replayed(const NsBuffers& buf, int batch, int64_t m, int64_t n, i
                         const float* coeffs, float eps, cudaStream_t stream, int* result_index);
 void set_graph_replay(bool on);
 bool graph_replay_enabled();
+
+// Bytes of scratch ns_run_with_scratch needs for `batch` matrices of m x n (m <= n): one
+// [batch, m, ldn] iterate buffer, three [batch, m, ldm] squares and the fp32 area. -1 on bad sizes.
+int64_t ns_scratch_bytes(int batch, int64_t m, int64_t n, int mode = 0);
+
+// Newton-Schulz with caller-owned input and output and a scratch area of ns_scratch_bytes():
+// `src` ([batch, rows, cols], element type `dtype` (a DType), pitches in elements) is cast to bf16,
+// transposed when rows > cols, into whichever iterate buffer makes the result land in `out`
+// ([batch, m, n] bf16, m = min(rows, cols)); the iteration ping-pongs between `out` and the
+// scratch. `replay` allows graph replay (see ns_iterate_replayed).
+int ns_run_with_scratch(const void* src, int dtype, int64_t rows, int64_t cols, int64_t ld_src,
+                        int64_t src_bs, __nv_bfloat16* out, int64_t ldo, int64_t o_bs,
+                        unsigned char* scratch, int batch, int mode, int steps, const float* coeffs,
+                        float eps, bool replay, cudaStream_t stream);
 
 // Argument checks shared by both entry points: fills in the default step count.
 int ns_check_mode(int mode, int* steps, const float* coeffs);

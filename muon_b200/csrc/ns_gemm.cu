@@ -33,6 +33,7 @@
 #include "profiling.h"
 
 #include <cuda.h>
+#include <cuda_fp8.h>
 #include <atomic>
 #include <cstdlib>
 #include <mutex>
@@ -117,11 +118,12 @@ __device__ __forceinline__ TileCoord decode_tile(int t, const GemmParams& p) {
   return tc;
 }
 
-// Instruction descriptor: bf16 x bf16 -> fp32, N = 256, A K-major, B K- or MN-major.
-__host__ __device__ constexpr uint32_t make_idesc(bool b_mn_major, int mma_m) {
+// Instruction descriptor: bf16 x bf16 (kind::f16) or e4m3 x e4m3 (kind::f8f6f4) -> fp32, N = 256,
+// A K-major, B K- or MN-major.
+__host__ __device__ constexpr uint32_t make_idesc(bool b_mn_major, int mma_m, bool e4m3) {
   return (1u << 4)                         // D format: f32
-         | (1u << 7)                       // A format: bf16
-         | (1u << 10)                      // B format: bf16
+         | ((e4m3 ? 0u : 1u) << 7)         // A format: kind::f16 1 = bf16; kind::f8f6f4 0 = e4m3
+         | ((e4m3 ? 0u : 1u) << 10)        // B format
          | ((b_mn_major ? 1u : 0u) << 16)  // B major: 0 = K, 1 = MN
          | (uint32_t(BN >> 3) << 17)       // N
          | (uint32_t(mma_m >> 4) << 24);   // M
@@ -252,8 +254,39 @@ __device__ __forceinline__ void block_store_coal(__nv_bfloat16* base, long long 
     *reinterpret_cast<uint4*>(ptr + 8 * i * ld) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
 }
 
+// ---------------------------------------------------------------------------
+// e4m3 copies of an output block (see Fp8Spec in ns_gemm.h).
+// ---------------------------------------------------------------------------
+// Eight bf16 values (four packed words) times a power-of-two scale -> eight e4m3 bytes.
+__device__ __forceinline__ uint2 bf16x8_to_e4m3x8(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3,
+                                                  float scale) {
+  const uint32_t w[4] = {w0, w1, w2, w3};
+  uint32_t h[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 v = make_float2(bf16_bits_to_float(w[i] & 0xffffu) * scale, bf16_bits_to_float(w[i] >> 16) * scale);
+    h[i] = __nv_cvt_float2_to_fp8x2(v, __NV_SATFINITE, __NV_E4M3);
+  }
+  return make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+}
+__device__ __forceinline__ uint8_t bf16_to_e4m3(uint32_t bits16, float scale, float minus) {
+  return static_cast<uint8_t>(
+      __nv_cvt_float_to_fp8((bf16_bits_to_float(bits16) - minus) * scale, __NV_SATFINITE, __NV_E4M3));
+}
+// A 32 x 32 block held in the "coal" pattern (instruction i, lane l: row 8i + l/4, eight columns
+// from 8 * (l%4)) -> e4m3 at (row0, col0) of a byte matrix with pitch ld: 32 contiguous bytes per row.
+__device__ __forceinline__ void block_store_coal_e4m3(uint8_t* base, long long ld, int row0, int col0,
+                                                      int lane, const uint32_t (&w)[16], float scale) {
+  uint8_t* ptr = base + (row0 + (lane >> 2)) * ld + col0 + (lane & 3) * 8;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    *reinterpret_cast<uint2*>(ptr + 8 * i * ld) =
+        bf16x8_to_e4m3x8(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3], scale);
+}
+
 // ADD: how line 2's addend is formed (AddendMode); the other two lines pass ADD_SYMMETRIC.
-template <int MODE, bool B_MN, int CTAS, int EW, int ADD>
+// F8: an Fp8Kind.
+template <int MODE, bool B_MN, int CTAS, int EW, int ADD, int F8>
 __global__ void __launch_bounds__(num_threads(EW), 1)
 ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const GemmParams p) {
@@ -318,7 +351,9 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   griddep_launch_dependents();
   griddep_wait();
 
-  const int k_blocks = (p.K + BK - 1) / BK;
+  // One shared-memory stage holds 128 bytes of K per row: 64 bf16 or 128 e4m3 elements.
+  constexpr int KSTEP = F8 == F8_OPERANDS ? 2 * BK : BK;
+  const int k_blocks = (p.K + KSTEP - 1) / KSTEP;
   const int total_tiles = p.tiles_per_batch * p.batch;
   const int work0 = blockIdx.x / CTAS;
   const int work_stride = gridDim.x / CTAS;
@@ -348,9 +383,9 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // Both CTAs' copies complete on the leader's barrier, which expects both halves.
             const uint32_t full = map_to_cta(full_bar(stage), 0);
             if (leader) mbar_expect_tx(full_bar(stage), 2 * C::STAGE_BYTES);
-            tma_load_3d_pair(sa, &tmap_a, full, kb * BK, a_row, tc.batch);
+            tma_load_3d_pair(sa, &tmap_a, full, kb * KSTEP, a_row, tc.batch);
             if (!B_MN) {
-              tma_load_3d_pair(sb, &tmap_b, full, kb * BK, b_row, tc.batch);
+              tma_load_3d_pair(sb, &tmap_b, full, kb * KSTEP, b_row, tc.batch);
             } else {
 #pragma unroll
               for (int c = 0; c < C::B_ROWS / 64; ++c)
@@ -358,10 +393,10 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
           } else {
             mbar_expect_tx(full_bar(stage), C::STAGE_BYTES);
-            tma_load_3d(sa, &tmap_a, full_bar(stage), kb * BK, a_row, tc.batch);
+            tma_load_3d(sa, &tmap_a, full_bar(stage), kb * KSTEP, a_row, tc.batch);
             if (!B_MN) {
               // B operand rows are output columns; K contiguous.
-              tma_load_3d(sb, &tmap_b, full_bar(stage), kb * BK, b_row, tc.batch);
+              tma_load_3d(sb, &tmap_b, full_bar(stage), kb * KSTEP, b_row, tc.batch);
             } else {
               // B operand is [K, N] with N contiguous: 64-column slabs of 64 k-rows.
 #pragma unroll
@@ -384,7 +419,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
     if (lane == 0 && leader) {
-      constexpr uint32_t idesc = make_idesc(B_MN, TILE_M);
+      constexpr uint32_t idesc = make_idesc(B_MN, TILE_M, F8 == F8_OPERANDS);
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
@@ -425,8 +460,14 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const uint64_t b_adv = B_MN ? static_cast<uint64_t>((kk * UMMA_K * 128) >> 4)
                                         : static_cast<uint64_t>((kk * UMMA_K * 2) >> 4);
             const uint32_t accumulate = (kb | kk) != 0 ? 1u : 0u;
-            if (CTAS == 2) umma_bf16_ss_pair(d_tmem, a_desc + a_adv, b_desc + b_adv, idesc, accumulate);
-            else umma_bf16_ss(d_tmem, a_desc + a_adv, b_desc + b_adv, idesc, accumulate);
+            // 32 bytes of K per instruction either way: 16 bf16 or 32 e4m3 elements.
+            if constexpr (F8 == F8_OPERANDS) {
+              if (CTAS == 2) umma_f8_ss_pair(d_tmem, a_desc + a_adv, b_desc + b_adv, idesc, accumulate);
+              else umma_f8_ss(d_tmem, a_desc + a_adv, b_desc + b_adv, idesc, accumulate);
+            } else {
+              if (CTAS == 2) umma_bf16_ss_pair(d_tmem, a_desc + a_adv, b_desc + b_adv, idesc, accumulate);
+              else umma_bf16_ss(d_tmem, a_desc + a_adv, b_desc + b_adv, idesc, accumulate);
+            }
           }
           // Frees the stage (in both CTAs of a pair) once these MMAs have read it.
           if (CTAS == 2) umma_commit_pair(empty_bar(stage), 0x3);
@@ -480,6 +521,8 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const __nv_bfloat16* add_b =
           (MODE == MODE_SYRK) ? nullptr : p.add + static_cast<long long>(tc.batch) * p.add_bs;
       __nv_bfloat16* out_row = out_b + static_cast<long long>(r) * p.ldo;
+      // e4m3 copy of the output (null when this launch keeps none)
+      uint8_t* out8_b = (F8 != F8_NONE && p.out8) ? p.out8 + static_cast<long long>(tc.batch) * p.out8_bs : nullptr;
       const __nv_bfloat16* add_row =
           (MODE == MODE_SYRK) ? nullptr : add_b + static_cast<long long>(r) * p.ldadd;
 
@@ -554,6 +597,14 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if constexpr (MODE == MODE_AXPBY) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) f[j] *= p.alpha;
+          if constexpr (F8 == F8_OPERANDS) {
+            // The operand was E = A - I: the identity's share, diag * I, lands on the diagonal
+            // (block on the diagonal: this thread's row is column `lane` of the chunk).
+            if (col0 == row_base) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) f[j] += (j == lane) ? p.diag : 0.f;
+            }
+          }
           if constexpr (ADD == ADD_ROW_SCALED) {
             // The addend is S * w (rows scaled by w = 1/s), S symmetric and given unscaled:
             // bf16(S[r,col] * w[r]) is bit for bit what the materialised scaled matrix holds at
@@ -576,6 +627,10 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           for (int j = 0; j < 16; ++j)
             packed[j] = pack_bf16x2(fmaf(a[2 * j], p.alpha, f[2 * j]), fmaf(a[2 * j + 1], p.alpha, f[2 * j + 1]));
         } else {
+          if constexpr (F8 == F8_OPERANDS) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] *= p.acc_scale;  // the operands carried a power-of-two scale
+          }
 #pragma unroll
           for (int j = 0; j < 16; ++j) packed[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
         }
@@ -588,8 +643,24 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             stage_get_coal(stage, lane, w);
             __syncwarp();
             block_store_coal(out_b, p.ldo, row_base, col0, lane, w);
+            if constexpr (F8 == F8_EXTRA_OUT) {
+              if (out8_b) block_store_coal_e4m3(out8_b, p.ldo8, row_base, col0, lane, w, p.out8_scale);
+            }
           } else if (row_ok) {
             store_row32(out_row, col0, p.N, packed);
+            if constexpr (F8 == F8_EXTRA_OUT) {
+              if (out8_b) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  const int col = col0 + j;
+                  if (col < p.N) {
+                    const uint32_t wv2 = packed[j >> 1];
+                    out8_b[static_cast<long long>(r) * p.ldo8 + col] =
+                        bf16_to_e4m3((j & 1) ? (wv2 >> 16) : (wv2 & 0xffffu), p.out8_scale, 0.f);
+                  }
+                }
+              }
+            }
           }
         } else {
           // Mirror: element (r, col) with col < r also lands at (col, r), with the same finished
@@ -646,6 +717,10 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             stage_get_coal(stage, lane, w);
             __syncwarp();
             block_store_coal(out_b, p.ldo, row_base, col0, lane, w);
+            if constexpr (F8 == F8_OPERANDS && MODE == MODE_SYRK) {
+              // strictly below the diagonal: (A - I) = A here
+              if (out8_b) block_store_coal_e4m3(out8_b, p.ldo8, row_base, col0, lane, w, p.out8_scale);
+            }
             const int odd = lane & 1;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
@@ -657,6 +732,9 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             stage_get_coal(stage, lane, w);
             __syncwarp();
             block_store_coal(out_b, p.ldo, col0, row_base, lane, w);
+            if constexpr (F8 == F8_OPERANDS && MODE == MODE_SYRK) {
+              if (out8_b) block_store_coal_e4m3(out8_b, p.ldo8, col0, row_base, lane, w, p.out8_scale);
+            }
           } else if (row_ok) {
             // Blocks on the diagonal and ragged edges: one row per thread, the lower triangle
             // (col <= r) from its own position, the elements with col < r also to (col, r).
@@ -670,6 +748,23 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 const uint32_t w = mp[j >> 1];
                 out_s[static_cast<long long>(col) * p.ldo + r] =
                     static_cast<unsigned short>((j & 1) ? (w >> 16) : (w & 0xffffu));
+              }
+            }
+            if constexpr (F8 == F8_OPERANDS && MODE == MODE_SYRK) {
+              if (out8_b) {
+                // E8 = e4m3((A - I) * se), from the bf16 values just stored: own position for
+                // col <= r (the diagonal loses its 1), mirrored position for col < r.
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  const int col = col0 + j;
+                  if (col <= r && col < p.N) {
+                    const uint32_t w = packed[j >> 1];
+                    const uint8_t e = bf16_to_e4m3((j & 1) ? (w >> 16) : (w & 0xffffu), p.out8_scale,
+                                                   col == r ? 1.f : 0.f);
+                    out8_b[static_cast<long long>(r) * p.ldo8 + col] = e;
+                    if (col < r) out8_b[static_cast<long long>(col) * p.ldo8 + r] = e;
+                  }
+                }
               }
             }
           }
@@ -719,23 +814,25 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// bf16 tensor [batch, rows, cols] with row pitch `ld` and batch pitch `bs` (elements).
-// Box = box_rows x 64 columns, 128-byte swizzle, zero fill outside the tensor.
+// bf16 (elem_bytes 2) or e4m3 (elem_bytes 1) tensor [batch, rows, cols] with row pitch `ld` and
+// batch pitch `bs` (elements). Box = box_rows x 128 bytes of columns, 128-byte swizzle, zero fill
+// outside the tensor.
 int encode_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld,
-               int64_t bs, int batch, int box_rows) {
+               int64_t bs, int batch, int box_rows, int elem_bytes = 2) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return set_error(ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0)
     return set_error(ERR_ALIGNMENT, "GEMM operand base %p is not 16-byte aligned", base);
-  if ((ld * 2) % 16 != 0 || (batch > 1 && (bs * 2) % 16 != 0))
+  if ((ld * elem_bytes) % 16 != 0 || (batch > 1 && (bs * elem_bytes) % 16 != 0))
     return set_error(ERR_ALIGNMENT,
-                     "GEMM operand pitch must be a multiple of 8 bf16 elements (ld=%lld bs=%lld)",
-                     (long long)ld, (long long)bs);
+                     "GEMM operand pitch must be a multiple of 16 bytes (ld=%lld bs=%lld elements of %d bytes)",
+                     (long long)ld, (long long)bs, elem_bytes);
   cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
-  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)(batch > 1 ? bs : rows * ld) * 2};
-  cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * elem_bytes, (cuuint64_t)(batch > 1 ? bs : rows * ld) * elem_bytes};
+  cuuint32_t box[3] = {(cuuint32_t)(128 / elem_bytes), (cuuint32_t)box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+  CUresult r = fn(map, elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                  const_cast<void*>(base), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
@@ -743,7 +840,7 @@ int encode_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, i
   return OK;
 }
 
-constexpr int kKernelSlots = 3 * 2 * 2 * 3;  // mode x CTAs per tile x epilogue warps x addend mode
+constexpr int kKernelSlots = 3 * 2 * 2 * 3 * 3;  // mode x CTAs per tile x epilogue warps x addend mode x e4m3 kind
 struct DeviceInfo {
   int sm_count = 0;
   int cc_major = 0;
@@ -791,12 +888,12 @@ int forced_epi_warps() {
   return v;
 }
 
-template <int MODE, bool B_MN, int CTAS, int EW, int ADD>
+template <int MODE, bool B_MN, int CTAS, int EW, int ADD, int F8 = F8_NONE>
 int launch_instance(int dev, int sms, const CUtensorMap& ta, const CUtensorMap& tb,
                     const GemmParams& p, cudaStream_t stream) {
   using C = Cfg<CTAS>;
-  auto kern = ns_gemm_kernel<MODE, B_MN, CTAS, EW, ADD>;
-  const int slot = ((MODE * 2 + (CTAS - 1)) * 2 + (EW == 4 ? 0 : 1)) * 3 + ADD;
+  auto kern = ns_gemm_kernel<MODE, B_MN, CTAS, EW, ADD, F8>;
+  const int slot = (((MODE * 2 + (CTAS - 1)) * 2 + (EW == 4 ? 0 : 1)) * 3 + ADD) * 3 + F8;
   const long long total = (long long)p.tiles_per_batch * p.batch;
 
   cudaLaunchConfig_t cfg = {};
@@ -857,8 +954,14 @@ int launch_instance(int dev, int sms, const CUtensorMap& ta, const CUtensorMap& 
 constexpr int kLongK = 2048;  // from this K on, four epilogue warps (see launch_ns_gemm)
 
 template <int MODE, bool B_MN, int CTAS>
-int launch_epi(int ew, int dev, int sms, const CUtensorMap& ta, const CUtensorMap& tb,
+int launch_epi(int ew, int f8, int dev, int sms, const CUtensorMap& ta, const CUtensorMap& tb,
                const GemmParams& p, cudaStream_t stream) {
+  if (f8 != F8_NONE) {
+    // e4m3 variants exist for the symmetric-addend forms only (iterations after the first).
+    constexpr int KIND = MODE == MODE_BX ? F8_EXTRA_OUT : F8_OPERANDS;
+    if (ew == 4) return launch_instance<MODE, B_MN, CTAS, 4, ADD_SYMMETRIC, KIND>(dev, sms, ta, tb, p, stream);
+    return launch_instance<MODE, B_MN, CTAS, 8, ADD_SYMMETRIC, KIND>(dev, sms, ta, tb, p, stream);
+  }
   if constexpr (MODE == MODE_AXPBY) {
     if (p.sym_add == ADD_ROW_SCALED)
       return ew == 4 ? launch_instance<MODE, B_MN, CTAS, 4, ADD_ROW_SCALED>(dev, sms, ta, tb, p, stream)
@@ -905,7 +1008,7 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
                    const __nv_bfloat16* opb, int64_t ldb, int64_t b_bs, __nv_bfloat16* out,
                    int64_t ldo, int64_t out_bs, int batch, int64_t M, int64_t N, int64_t K,
                    float alpha, float beta, int sym_add, cudaStream_t stream, const __nv_bfloat16* addend,
-                   const float* row_scale, int64_t scale_bs) {
+                   const float* row_scale, int64_t scale_bs, const Fp8Spec* f8) {
   if (!opa || !opb || !out) return set_error(ERR_INVALID_ARG, "null pointer passed to NS GEMM");
   if (batch < 1 || M < 1 || N < 1 || K < 1)
     return set_error(ERR_INVALID_ARG, "NS GEMM needs batch, M, N, K >= 1 (got %d, %lld, %lld, %lld)",
@@ -938,6 +1041,23 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
   p.out = out;
   p.ldo = ldo;
   p.out_bs = out_bs;
+  const int f8_kind = f8 ? f8->kind : F8_NONE;
+  p.acc_scale = 1.f;
+  if (f8_kind != F8_NONE) {
+    if ((f8_kind == F8_OPERANDS) != (mode != MODE_BX))
+      return set_error(ERR_INVALID_ARG, "e4m3 operands go with lines 1 and 2, the extra e4m3 output with line 3");
+    if (f8_kind == F8_OPERANDS && (!f8->op8 || sym_add != ADD_SYMMETRIC))
+      return set_error(ERR_INVALID_ARG, "e4m3 products need the e4m3 operand and a symmetric addend");
+    if (f8->out8 && ((reinterpret_cast<uintptr_t>(f8->out8) & 15) || (f8->ldo8 % 16) || (f8->out8_bs % 16) ||
+                     f8->ldo8 < N))
+      return set_error(ERR_ALIGNMENT, "e4m3 output must be 16-byte aligned with pitches %% 16 == 0 and >= N");
+    p.out8 = f8->out8;
+    p.ldo8 = f8->ldo8;
+    p.out8_bs = f8->out8_bs;
+    p.out8_scale = f8->out8_scale;
+    p.acc_scale = f8->acc_scale;
+    p.diag = f8->diag;
+  }
 
   CUtensorMap ta, tb;
   if (mode == MODE_SYRK || mode == MODE_AXPBY) {
@@ -959,8 +1079,14 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
     if (mode == MODE_AXPBY && K != M)
       return set_error(ERR_INVALID_ARG, "line 2 needs a square operand (got %lld x %lld)",
                        (long long)M, (long long)K);
-    if ((rc = encode_map(&ta, opa, M, K, lda, a_bs, batch, BM)) != OK) return rc;
-    if ((rc = encode_map(&tb, opb, M, K, ldb, b_bs, batch, b_rows)) != OK) return rc;
+    if (f8_kind == F8_OPERANDS) {
+      // Both operands are the e4m3 matrix; the bf16 one (opa) is only line 2's addend.
+      if ((rc = encode_map(&ta, f8->op8, M, K, f8->ld8, f8->bs8, batch, BM, 1)) != OK) return rc;
+      if ((rc = encode_map(&tb, f8->op8, M, K, f8->ld8, f8->bs8, batch, b_rows, 1)) != OK) return rc;
+    } else {
+      if ((rc = encode_map(&ta, opa, M, K, lda, a_bs, batch, BM)) != OK) return rc;
+      if ((rc = encode_map(&tb, opb, M, K, ldb, b_bs, batch, b_rows)) != OK) return rc;
+    }
   } else if (mode == MODE_BX) {
     if (K != M) return set_error(ERR_INVALID_ARG, "line 3 needs a square left operand");
     p.triangular = 0;
@@ -983,18 +1109,19 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
   // smaller CTA leaves room on the SM (registers, 8 KiB of shared memory) for the HBM-bound
   // kernels that the engine runs beside the GEMMs. With a short K the epilogue is what a tile
   // waits for: eight warps.
-  if (ew == 0) ew = K >= kLongK ? 4 : 8;
+  // (with e4m3 operands a tile's main loop takes half as long: the threshold doubles)
+  if (ew == 0) ew = K >= (f8_kind == F8_OPERANDS ? 2 * kLongK : kLongK) ? 4 : 8;
   if (ctas == 2) {
     switch (mode) {
-      case MODE_SYRK: return launch_epi<MODE_SYRK, false, 2>(ew, dev, sms, ta, tb, p, stream);
-      case MODE_AXPBY: return launch_epi<MODE_AXPBY, false, 2>(ew, dev, sms, ta, tb, p, stream);
-      default: return launch_epi<MODE_BX, true, 2>(ew, dev, sms, ta, tb, p, stream);
+      case MODE_SYRK: return launch_epi<MODE_SYRK, false, 2>(ew, f8_kind, dev, sms, ta, tb, p, stream);
+      case MODE_AXPBY: return launch_epi<MODE_AXPBY, false, 2>(ew, f8_kind, dev, sms, ta, tb, p, stream);
+      default: return launch_epi<MODE_BX, true, 2>(ew, f8_kind, dev, sms, ta, tb, p, stream);
     }
   }
   switch (mode) {
-    case MODE_SYRK: return launch_epi<MODE_SYRK, false, 1>(ew, dev, sms, ta, tb, p, stream);
-    case MODE_AXPBY: return launch_epi<MODE_AXPBY, false, 1>(ew, dev, sms, ta, tb, p, stream);
-    default: return launch_epi<MODE_BX, true, 1>(ew, dev, sms, ta, tb, p, stream);
+    case MODE_SYRK: return launch_epi<MODE_SYRK, false, 1>(ew, f8_kind, dev, sms, ta, tb, p, stream);
+    case MODE_AXPBY: return launch_epi<MODE_AXPBY, false, 1>(ew, f8_kind, dev, sms, ta, tb, p, stream);
+    default: return launch_epi<MODE_BX, true, 1>(ew, f8_kind, dev, sms, ta, tb, p, stream);
   }
 }
 

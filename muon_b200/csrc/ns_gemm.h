@@ -20,6 +20,32 @@ enum AddendMode : int {
   ADD_ROW_SCALED = 2,  // A = S / s with S symmetric: both addends are rebuilt from S and s
 };
 
+// 8-bit floating point (e4m3) in the two symmetric products, see Fp8Spec.
+enum Fp8Kind : int {
+  F8_NONE = 0,
+  F8_OPERANDS = 1,  // the product's operands are e4m3 (lines 1 and 2)
+  F8_EXTRA_OUT = 2, // bf16 product that also writes an e4m3 copy of its output (line 3)
+};
+
+// The e4m3 variant of the iteration keeps, beside the bf16 matrices, X8 = e4m3(X * sx) and
+// E8 = e4m3((A - I) * se), both with power-of-two scales:
+//   line 1 (F8_OPERANDS): A = (X8 · X8ᵀ) * acc_scale, acc_scale = 1 / sx²; writes A in bf16 and E8.
+//   line 2 (F8_OPERANDS): with E = A - I, alpha·A·A + beta·A = alpha·E·E + (beta + 2·alpha)·A - alpha·I,
+//                         so only the small matrix E goes through e4m3: out = (E8 · E8ᵀ) * alpha'
+//                         + beta' * A + diag * I with alpha' = alpha / se², beta' = beta + 2·alpha,
+//                         diag = -alpha (the caller passes alpha', beta', diag).
+//   line 3 (F8_EXTRA_OUT): bf16 as always, and writes X8 for the next line 1.
+struct Fp8Spec {
+  int kind = F8_NONE;
+  const uint8_t* op8 = nullptr;  // F8_OPERANDS: the e4m3 operand [batch, M, K], pitch ld8 bytes
+  int64_t ld8 = 0, bs8 = 0;
+  uint8_t* out8 = nullptr;       // e4m3 copy of the output (line 1: E8, line 3: X8), or null
+  int64_t ldo8 = 0, out8_bs = 0;
+  float out8_scale = 1.f;        // se or sx
+  float acc_scale = 1.f;         // line 1: 1 / sx²
+  float diag = 0.f;              // line 2: added to the diagonal of the output
+};
+
 struct GemmParams {
   int M, N, K;  // output rows, output cols, contraction length
   int batch;
@@ -34,6 +60,10 @@ struct GemmParams {
   long long ldo, out_bs;
   const __nv_bfloat16* add;
   long long ldadd, add_bs;
+  // e4m3 variants (see Fp8Spec)
+  uint8_t* out8;
+  long long ldo8, out8_bs;
+  float out8_scale, acc_scale, diag;
 };
 
 int device_sm_count(int* sm_count_out);
@@ -47,6 +77,6 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
                    int64_t ldo, int64_t out_bs, int batch, int64_t M, int64_t N, int64_t K,
                    float alpha, float beta, int sym_add, cudaStream_t stream,
                    const __nv_bfloat16* addend = nullptr, const float* row_scale = nullptr,
-                   int64_t scale_bs = 0);
+                   int64_t scale_bs = 0, const Fp8Spec* f8 = nullptr);
 
 }  // namespace mb

@@ -7,6 +7,12 @@ The reference ends every window with ``dist.all_gather`` of the freshly updated 
           copy kernels that need SMs; the Newton-Schulz GEMMs are persistent grids that fill
           the device, so the two compete and only part of the transfer is hidden.
 
+``st``    same mappings as ``ce`` below, but nothing is copied afterwards: the update epilogue
+          kernel itself stores every new parameter value into the W-1 peer copies as it computes
+          it (``muon_b200_epilogue_push``, plain global stores over NVLink). The exchange of a
+          launch group is finished when its epilogue kernel is, that kernel runs beside the next
+          group's GEMMs, and the copy engines stay free for host-to-device traffic. Up to 8 ranks.
+
 ``ce``    every rank maps the other ranks' parameter allocations on its own device (CUDA IPC
           handles opened with peer access, ``muon_b200_ipc_export`` / ``muon_b200_ipc_open``)
           and, as soon as some of its own parameters are updated, pushes them to the peers
@@ -18,27 +24,39 @@ The reference ends every window with ``dist.all_gather`` of the freshly updated 
           only after every rank's pushes have completed, which gives ``step()`` the reference's
           post-condition that all ranks hold all updated parameters.
 
-``MUON_B200_EXCHANGE`` selects ``nccl``, ``ce``, or ``auto`` (``ce`` when every rank can map
-its peers, else ``nccl``). CPU tensors (the gloo test ranks) always use ``all_gather``.
-The ``ce`` transport needs parameters that live in plain ``cudaMalloc`` blocks (PyTorch's
-default allocator without expandable segments) and stay allocated while the optimizer lives.
+``MUON_B200_EXCHANGE`` selects ``nccl``, ``ce``, or ``auto`` (default). ``auto`` means ``ce``; when
+the peers cannot be mapped it raises and names the reason instead of switching transports behind
+the caller's back: the ``nccl`` transport is slower (its copy kernels compete with the GEMMs for
+SMs) and an early version of it stopped twice in a 2-GPU run for a reason that was never found, so
+it is only used when asked for by name. CPU tensors (the gloo test ranks) always use
+``all_gather``. The ``ce`` transport needs parameters that live in plain ``cudaMalloc`` blocks
+(PyTorch's default allocator without expandable segments) and stay allocated while the optimizer
+lives.
 """
 from __future__ import annotations
 
 import ctypes
 import os
+import weakref
 
 import torch
 import torch.distributed as dist
 
 DEFAULT_MODE = "auto"
 
+# CUDA refuses to open an IPC handle twice in one process, so mappings are shared process-wide:
+# handle bytes -> [base address on this device, number of PeerPush objects using it].
+_OPEN_HANDLES: dict = {}
+
 
 def _mode() -> str:
     m = os.environ.get("MUON_B200_EXCHANGE", DEFAULT_MODE).lower()
-    if m not in ("auto", "ce", "nccl"):
-        raise ValueError(f"MUON_B200_EXCHANGE must be auto, ce or nccl, got {m!r}")
+    if m not in ("auto", "ce", "st", "nccl"):
+        raise ValueError(f"MUON_B200_EXCHANGE must be auto, ce, st or nccl, got {m!r}")
     return m
+
+
+MAX_STORE_PEERS = 7  # peer copies one launch of the epilogue kernel can address
 
 
 class PeerPush:
@@ -107,18 +125,21 @@ class PeerPush:
         for handle, offset, _ in items:
             base = self._opened.get(handle)
             if base is None:
-                ptr = ctypes.c_void_p(0)
-                rc = lib.muon_b200_ipc_open(handle, ctypes.byref(ptr))
-                if rc != 0:
-                    raise RuntimeError(lib.muon_b200_last_error().decode())
-                base = self._opened[handle] = ptr.value
+                shared = _OPEN_HANDLES.get(handle)
+                if shared is None:
+                    ptr = ctypes.c_void_p(0)
+                    rc = lib.muon_b200_ipc_open(handle, ctypes.byref(ptr))
+                    if rc != 0:
+                        raise RuntimeError(lib.muon_b200_last_error().decode())
+                    shared = _OPEN_HANDLES[handle] = [ptr.value, 0]
+                shared[1] += 1
+                base = self._opened[handle] = shared[0]
             out.append(base + offset)
         return out
 
     def close(self) -> None:
-        from ._lib import lib
-        for base in self._opened.values():
-            lib.muon_b200_ipc_close(base)
+        """Drop this object's use of its mappings; a mapping is removed with its last user."""
+        _release_handles(self._opened)
         self._opened = {}
         self.ptrs = None
 
@@ -147,6 +168,11 @@ class PeerPush:
                     check(lib.muon_b200_push_copies(ptr_array([self.ptrs[r][i]]), 1, p.data_ptr(),
                                                     self.nbytes[i], stream.cuda_stream))
 
+    def peer_ptrs(self, p) -> list:
+        """Addresses, on this device, of parameter `p` in every other rank's memory."""
+        i = self.index[id(p)]
+        return [self.ptrs[r][i] for r in self.peers]
+
     def end_step(self) -> None:
         """Returns (in stream order) once every rank's pushes have landed."""
         current = torch.cuda.current_stream(self.device)
@@ -155,14 +181,38 @@ class PeerPush:
         dist.all_reduce(self._token)
 
 
+def _release_handles(opened: dict) -> None:
+    from ._lib import lib
+    for handle, base in opened.items():
+        shared = _OPEN_HANDLES.get(handle)
+        if shared is None:
+            continue
+        shared[1] -= 1
+        if shared[1] <= 0:
+            lib.muon_b200_ipc_close(base)
+            del _OPEN_HANDLES[handle]
+
+
+def _close_all(cache: dict) -> None:
+    for push in cache.values():
+        if push is not None:
+            push.close()
+    cache.clear()
+
+
 def get_peer_push(optimizer, group):
     """PeerPush of `group`, built collectively on first use; None when the NCCL/gloo gather is to
-    be used. Every rank takes the same decision."""
-    cache = optimizer.__dict__.setdefault("_muon_b200_exchange", {})
-    key = id(group)
+    be used. Every rank takes the same decision. The cache is keyed on the parameters' storage
+    addresses (``load_state_dict`` replaces the group dicts, not the parameters) and closed when
+    the optimizer is collected."""
+    cache = optimizer.__dict__.get("_muon_b200_exchange")
+    if cache is None:
+        cache = optimizer.__dict__["_muon_b200_exchange"] = {}
+        weakref.finalize(optimizer, _close_all, cache)
+    params = group["params"]
+    key = tuple(p.data_ptr() for p in params)
     if key in cache:
         return cache[key]
-    params = group["params"]
     mode = _mode()
     usable = mode != "nccl" and dist.get_world_size() > 1 and all(p.is_cuda for p in params) \
         and "nccl" in str(dist.get_backend())
@@ -170,8 +220,11 @@ def get_peer_push(optimizer, group):
     if usable:
         push = PeerPush(params)
         if not push.ok:
-            if mode == "ce":
-                raise RuntimeError(f"MUON_B200_EXCHANGE=ce but peers cannot be mapped: {push.error}")
-            push = None
+            raise RuntimeError(
+                f"muon_b200: the copy-engine exchange cannot map the other ranks' parameters ({push.error}). "
+                "Keep parameters in plain cudaMalloc blocks (no expandable segments), or ask for the "
+                "all_gather transport by name with MUON_B200_EXCHANGE=nccl")
+    if push is not None:
+        push.mode = "st" if mode == "st" and len(push.peers) <= MAX_STORE_PEERS else "ce"
     cache[key] = push
     return push

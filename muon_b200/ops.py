@@ -73,6 +73,9 @@ def ns_line_2(A: Tensor, alpha: float, beta: float, *, out: Tensor = None) -> Te
     if buf.data_ptr() == A3.data_ptr():
         buf, user = _out_3d(None, A, (batch, M, M))[0], out
     with torch.cuda.device(A.device):
+        # The reference's kernel takes any square A (muon.py:483-486); nothing here knows whether this
+        # one is symmetric bit for bit, so the general addend path is used (for such an A it gives
+        # the same result as the symmetric one).
         check(lib.muon_b200_ns_line2(A3.data_ptr(), A3.stride(-2), A3.stride(0), buf.data_ptr(),
                                      buf.stride(-2), buf.stride(0), batch, M, float(alpha), float(beta), 0,
                                      _stream_ptr(A.device)))
@@ -116,7 +119,8 @@ def zeropower_via_newtonschulz5(G: Tensor, epsilon: float = 1e-7) -> Tensor:
 
 def muon_update(grad: Tensor, momentum: Tensor, beta: float = 0.95, nesterov: bool = True) -> Tensor:
     """muon.py:8-15: momentum update in place, Nesterov blend written back into ``grad``,
-    then the orthogonalised, aspect-scaled bf16 update of the (collapsed) 2-D shape."""
+    then the orthogonalised, aspect-scaled bf16 update of the (collapsed) 2-D shape. Three library
+    calls (prologue, Newton-Schulz, scale); the result is a fresh tensor, scratch is cached."""
     _require_cuda(grad, "grad")
     if grad.shape != momentum.shape or grad.dtype != momentum.dtype:
         raise ValueError("grad and momentum must have the same shape and dtype")
@@ -125,29 +129,28 @@ def muon_update(grad: Tensor, momentum: Tensor, beta: float = 0.95, nesterov: bo
     rows, cols = view_2d(grad.shape)
     tall = rows > cols
     m_, n_ = (cols, rows) if tall else (rows, cols)
-    layout = _lib.ns_layout(1, m_, n_)
+    ldn = (n_ + 7) // 8 * 8
     dev = grad.device
     backend = get_backend()
     with torch.cuda.device(dev):
-        ws = torch.empty(layout.total_bytes + 256, dtype=torch.uint8, device=dev)
-        wptr = backend._aligned_ptr(ws)
+        stage_bytes = (m_ * ldn * 2 + 255) // 256 * 256  # bf16 X as the prologue leaves it
+        mode, steps = get_ns_mode()
+        need = lib.muon_b200_zeropower_scratch_bytes(1, m_, n_, _NS_MODES[mode])
+        ws = backend.workspace(dev, stage_bytes + need, slot=3)
+        stage = backend._aligned_ptr(ws)
         stream = _stream_ptr(dev)
         check(lib.muon_b200_prologue(_lib.ptr_array([grad.data_ptr()]), _lib.ptr_array([momentum.data_ptr()]),
                                      1, rows, cols, dtype_code(grad), beta, 1 if nesterov else 0,
-                                     wptr + layout.x_offset_bytes, layout.ldn, layout.x_bs,
-                                     1 if tall else 0, stream))
-        res = ctypes.c_int(0)
-        mode, steps = get_ns_mode()
-        check(lib.muon_b200_ns_run(wptr, 1, m_, n_, _NS_MODES[mode], steps, None, 1e-7,
-                                   ctypes.byref(res), stream))
-        off = (wptr - ws.data_ptr()) + (layout.x_offset_bytes if res.value == 0 else layout.c_offset_bytes)
-        out = ws[off: off + layout.x_bs * 2].view(torch.bfloat16).view(m_, layout.ldn)[:, :n_]
-    if tall:
-        out = out.mT
-    scale = aspect_scale(grad.shape)
-    if scale != 1:
-        out *= scale
-    return out
+                                     stage, ldn, m_ * ldn, 1 if tall else 0, stream))
+        out = torch.empty(m_, ldn, dtype=torch.bfloat16, device=dev)
+        check(lib.muon_b200_zeropower(stage, _lib.BF16, m_, n_, ldn, m_ * ldn, 1, out.data_ptr(), ldn, m_ * ldn,
+                                      stage + stage_bytes, need, _NS_MODES[mode], steps, None, 1e-7, stream))
+        scale = aspect_scale(grad.shape)
+        if scale != 1:  # update *= max(1, rows/cols)**0.5, rounded to bf16 like the reference's multiply
+            check(lib.muon_b200_cast_bf16(out.data_ptr(), _lib.BF16, m_, n_, ldn, m_ * ldn, out.data_ptr(), ldn,
+                                          m_ * ldn, 1, 0, scale, stream))
+    out = out[:, :n_]
+    return out.mT if tall else out
 
 
 def adam_update(grad: Tensor, buf1: Tensor, buf2: Tensor, step: int, betas, eps: float) -> Tensor:

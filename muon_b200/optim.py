@@ -94,6 +94,24 @@ def _next_chunk(params, owned, done_upto, backend):
     return [params[idx] for idx in owned[done_upto:done_upto + limit]]
 
 
+# Gathers issued but not yet known to be complete, per step. An earlier version kept every
+# window's gather of a step in flight (over a hundred at a time); the number is now bounded.
+_MAX_GATHERS_IN_FLIGHT = 16
+
+
+def _throttle_gathers(pending, settled: int, device) -> int:
+    """Wait (on the host) for the oldest gathers until at most _MAX_GATHERS_IN_FLIGHT are
+    outstanding. Returns the new count of settled entries of `pending`."""
+    while len(pending) - settled > _MAX_GATHERS_IN_FLIGHT:
+        work = pending[settled]
+        if work is not None:
+            work.wait()
+            if device.type == "cuda":  # Work.wait() only orders the stream: wait for the stream too
+                torch.cuda.current_stream(device).synchronize()
+        settled += 1
+    return settled
+
+
 def _distributed_muon_group_step(optimizer, group) -> None:
     """Windowed round-robin of muon.py:54-68. Window k holds params[kW:(k+1)W]; rank r
     updates params[kW + r] and every rank then receives the whole window."""
@@ -104,7 +122,7 @@ def _distributed_muon_group_step(optimizer, group) -> None:
     params_pad = params + [torch.empty_like(params[-1])] * (world - len(params) % world)
     owned = list(range(rank, len(params), world))
     done_upto = 0  # owned[:done_upto] have been updated
-    pending = []
+    pending, settled = [], 0
     if world == 1:
         # Nothing to exchange: the whole group goes to the engine, which plans its own launches.
         _muon_update_params(optimizer, params, group)
@@ -120,8 +138,12 @@ def _distributed_muon_group_step(optimizer, group) -> None:
         mine = [params[i] for i in owned]
         push.begin_step()
         for plist in _bucket_by_shape(mine).values():
-            cap = max(1, -(-len(plist) // 2)) if world >= 4 else None
-            _muon_update_params(optimizer, plist, group, after_group=push.push, max_group=cap)
+            if push.mode == "st":
+                # The epilogue kernel stores into the peer copies itself: nothing to enqueue afterwards.
+                _muon_update_params(optimizer, plist, group, peer_ptrs=push.peer_ptrs)
+            else:
+                cap = max(1, -(-len(plist) // 2)) if world >= 4 else None
+                _muon_update_params(optimizer, plist, group, after_group=push.push, max_group=cap)
         push.end_step()
         return
     for base_i in range(0, len(params), world):
@@ -143,7 +165,8 @@ def _distributed_muon_group_step(optimizer, group) -> None:
             for r, w in enumerate(window):
                 if base_i + r < len(params):
                     pending.append(dist.broadcast(w, src=r, async_op=True))
-    for work in pending:
+        settled = _throttle_gathers(pending, settled, params[0].device)
+    for work in pending[settled:]:
         if work is not None:
             work.wait()
 

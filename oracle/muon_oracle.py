@@ -123,16 +123,25 @@ def zeropower_via_newtonschulz5(G: Tensor, epsilon: float = 1e-7, *, mirror: str
     """The live algorithm, muon.py:748-799: AOL rescale + 4 iterations.
 
     Rounding points (each ``.to(dtype)``): the cast (:760), every GEMM line's output,
-    the row sums s (:779-781, a materialised bf16 tensor), X·rsqrt(s) (:782) and A/s
-    (:785).  ``glue="fused"`` (default, what the CUDA kernels implement) evaluates the
-    elementwise glue in fp32 and rounds once per tensor, which is how the reference's compiled
-    graph evaluates it.  ``glue="eager"`` rounds after every torch op (abs, sum, clamp, rsqrt,
-    multiply, divide), which is what the reference does when it runs uncompiled; with
-    ``mirror="ref_square_tiles"`` that variant reproduces the real reference driver executed
-    on CPU (its Triton kernels under the interpreter), which is what pins this function.
+    X·rsqrt(s) (:782), A/s (:785) and, depending on ``glue``, the row sums s (:779-781):
+
+    * ``glue="compiled"``: the graph torch.compile generates for the reference on a B200 (read from
+      its generated code): one reduction kernel sums |A| per row in fp32, divides A by the
+      unrounded clamped sum and stores the sum as bf16; one pointwise kernel multiplies the
+      *uncast* input G (fp32 when the caller passes fp32) by rsqrt(max(stored sum, eps)).  With the
+      default mirror rule this is within accumulation-order noise (about 3e-3) of the reference's
+      output on a B200 (``tests/golden/reference_b200.pt``).
+    * ``glue="fused"`` (default, what the CUDA kernels implement): the same, except that X·rsqrt(s)
+      starts from the bf16 cast of G, like every uncompiled run of the reference does; the only
+      copy of G the kernels keep is the bf16 one.  A/s is formed as A·(1/s) with a correctly
+      rounded reciprocal (the CUDA kernels rebuild it bit for bit in two places).
+    * ``glue="eager"`` rounds after every torch op (abs, sum, clamp, rsqrt, multiply, divide),
+      which is what the reference does when it runs uncompiled; with
+      ``mirror="ref_square_tiles"`` that variant reproduces the real reference driver executed on
+      CPU (its Triton kernels under the interpreter) bit for bit.
     """
     assert G.ndim in (2, 3)
-    assert glue in ("fused", "eager")
+    assert glue in ("fused", "eager", "compiled")
     X = G.to(dtype)
     tall = G.size(-2) > G.size(-1)
     if tall:
@@ -145,12 +154,15 @@ def zeropower_via_newtonschulz5(G: Tensor, epsilon: float = 1e-7, *, mirror: str
         X = X * torch.rsqrt(s)  # :782
         A = A / s  # :785
     else:
-        s = torch.clamp_min(A.float().abs().sum(dim=-1, keepdim=True), epsilon).to(dtype)  # :779-781
-        X = (X.float() * torch.rsqrt(s.float())).to(dtype)  # :782
-        # :785 (rows only). The quotient is formed as A * (1/s) with a correctly rounded
-        # reciprocal: the reference's compiled division is itself approximate, and this form is
-        # the one the CUDA kernels can reproduce bit for bit in two places.
-        A = (A.float() * (1.0 / s.float())).to(dtype)
+        s32 = A.float().abs().sum(dim=-1, keepdim=True)  # :779-780, kept in fp32 by the reduction kernel
+        s_stored = torch.clamp_min(s32.to(dtype).float(), epsilon)  # what the pointwise kernel reads back
+        if glue == "compiled":
+            src = (G.mT if tall else G).float()  # the cast of :760 is fused away: G itself is read
+            X = (src * torch.rsqrt(s_stored)).to(dtype)  # :782
+            A = (A.float() / torch.clamp_min(s32, epsilon)).to(dtype)  # :785 (rows only)
+        else:
+            X = (X.float() * torch.rsqrt(s_stored)).to(dtype)  # :782
+            A = (A.float() * (1.0 / torch.clamp_min(s32, epsilon))).to(dtype)  # :785 (rows only)
     for k, (a, b, c) in enumerate(AOL4_COEFFS):
         if k > 0:
             A = ns_line_1(X, mirror=m1)  # :792
@@ -158,6 +170,51 @@ def zeropower_via_newtonschulz5(G: Tensor, epsilon: float = 1e-7, *, mirror: str
         X = ns_line_3(B, X, a)  # :787 / :794
     if tall:
         X = X.mT  # :797-798
+    return X
+
+
+def _e4m3(T: Tensor, scale: float) -> Tensor:
+    """fp32 values of e4m3(T * scale) / scale: round to nearest even, saturating at +-448."""
+    return (T.float() * scale).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).float() / scale
+
+
+def zeropower_aol4_fp8(G: Tensor, epsilon: float = 1e-7) -> Tensor:
+    """Restatement of the library's ``aol4_fp8`` variant (no counterpart in the reference): the
+    live algorithm (muon.py:748-799) with the two symmetric products of iterations 2..4 taken on
+    e4m3 operands with power-of-two scales and fp32 accumulation.  Line 1 multiplies
+    e4m3(X * sx); line 2, rewritten as c·E·E + (b + 2c)·A − c·I with E = A − I, multiplies
+    e4m3(E * 64).  The first iteration and every line 3 are those of ``zeropower_via_newtonschulz5``."""
+    assert G.ndim in (2, 3)
+    if max(G.size(-2), G.size(-1)) < 1024:  # the library iterates narrow matrices in bf16 in this mode too
+        return zeropower_via_newtonschulz5(G, epsilon)
+    dtype = torch.bfloat16
+    X = G.to(dtype)
+    tall = G.size(-2) > G.size(-1)
+    if tall:
+        X = X.mT
+    X = X.contiguous()
+    m, n = X.shape[-2], X.shape[-1]
+    sx = 1.0
+    while sx < 256.0 and sx * sx * 2.0 <= n:
+        sx *= 2.0
+    se = 64.0
+    eye = torch.eye(m)
+    A = ns_line_1(X, mirror="ref_square_tiles")
+    s32 = A.float().abs().sum(dim=-1, keepdim=True)
+    s_stored = torch.clamp_min(s32.to(dtype).float(), epsilon)
+    X = (X.float() * torch.rsqrt(s_stored)).to(dtype)
+    A = (A.float() * (1.0 / torch.clamp_min(s32, epsilon))).to(dtype)
+    for k, (a, b, c) in enumerate(AOL4_COEFFS):
+        if k == 0:
+            B = ns_line_2(A, alpha=c, beta=b)
+        else:
+            X8 = _e4m3(X, sx)
+            A = _mirror(X8 @ X8.mT, "lower", 64).to(dtype)
+            E8 = _e4m3(A.float() - eye, se)
+            B = (_mirror(E8 @ E8.mT, "lower", 64) * c + A.float() * (b + 2.0 * c) - c * eye).to(dtype)
+        X = ns_line_3(B, X, a)
+    if tall:
+        X = X.mT
     return X
 
 

@@ -1,6 +1,7 @@
 """Multi-GPU test of the distributed step (needs >= 2 GPUs; skipped otherwise): after `Muon.step`
 every rank holds every updated parameter, bit-identical to what `SingleDeviceMuon` produces on one
-GPU with the same kernels, for both exchange transports (copy-engine pushes, NCCL all_gather)."""
+GPU with the same kernels, for the three exchange transports (stores from the update kernel,
+copy-engine pushes, NCCL all_gather)."""
 import os
 
 import pytest
@@ -46,7 +47,7 @@ def _worker(rank, world, tmpdir, exchange, dtype):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange", ["ce", "nccl"])
+@pytest.mark.parametrize("exchange", ["st", "ce", "nccl"])
 @pytest.mark.parametrize("dtype", [torch.bfloat16])
 def test_distributed_step_matches_single_device(tmp_path, exchange, dtype):
     world = min(torch.cuda.device_count(), 4)
@@ -65,7 +66,7 @@ def test_distributed_step_matches_single_device(tmp_path, exchange, dtype):
 
     for r, o in enumerate(outs):
         assert o["status"] == 0
-        assert o["used_ce"] == (exchange == "ce")
+        assert o["used_ce"] == (exchange in ("ce", "st"))
         assert o["owned"] == list(range(r, len(SHAPES), world))
         for i, (p, q) in enumerate(zip(o["params"], ref)):
             assert torch.equal(p, q), f"rank {r}, parameter {i} {tuple(q.shape)} ({exchange})"

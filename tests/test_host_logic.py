@@ -61,6 +61,17 @@ def test_argument_errors_are_reported_without_a_gpu():
     assert rc == -1 and b"dtype" in L.lib.muon_b200_last_error()
 
 
+def test_ramped_launch_groups():
+    """Groups of 1, 2, 4, ... at the start of a set whose gradients are still arriving; every
+    parameter stays in exactly one group and the planned groups are never exceeded."""
+    from muon_b200.engine import ramped_sizes
+    assert ramped_sizes([13, 13, 13]) == [1, 2, 4, 6, 13, 13]
+    assert ramped_sizes([1]) == [1] and ramped_sizes([32]) == [1, 2, 4, 8, 17]
+    for planned in ([5], [2, 2], [7, 6], [40, 40, 3]):
+        got = ramped_sizes(planned)
+        assert sum(got) == sum(planned) and max(got) <= max(planned) and got[0] == 1
+
+
 def test_no_cpu_fallback():
     import muon_b200
     p = torch.nn.Parameter(torch.randn(8, 16))

@@ -181,6 +181,11 @@ def test_oracle_against_the_reference_run_on_a_b200(golden):
         if c["shape"][0] != c["shape"][1]:
             lo, hi = orc.singular_value_band(U)
             assert abs(lo - c["sv_band"][0]) <= 0.01 and abs(hi - c["sv_band"][1]) <= 0.01
+        # With the rounding points of the graph torch.compile generates for the reference
+        # (glue="compiled"), only accumulation-order noise is left (measured 3.0e-3 .. 3.5e-3; the
+        # square case keeps 6e-3: its smallest singular values are near zero and amplify noise).
+        exact = orc.rel_fro(orc.zeropower_via_newtonschulz5(G, glue="compiled")[c["rows"]], c["U_rows"])
+        assert exact <= (5e-3 if c["shape"][0] != c["shape"][1] else 1e-2), (c["shape"], exact)
         if c["shape"] == (128, 1152):
             far = orc.rel_fro(orc.zeropower_via_newtonschulz5(G, mirror="product")[c["rows"]], c["U_rows"])
             assert err < far
