@@ -79,10 +79,10 @@ SMALL_CONFIGS = {
     "gpt2-small-hidden": ("gpt2-small-hidden", "MuonWithAuxAdam", 25, 0.91),
     "conv-filters": ("conv-filters", "SingleDeviceMuon", 0, 0.28),
 }
-# DRAM bytes (read + write) per matrix element that one launch of the line-3 kernel moved in the
-# ncu capture summarised in profiles/ns_gemm_line3_llama3-8b-4layers.md: 2.120 GB read + 0.925 GB
-# written for 8 matrices of 4096 x 14336. Traffic of that kernel grows with the elements a launch
-# covers.
+# DRAM bytes (read + write) per matrix element that one launch of the line-3 kernel moved in an ncu
+# capture of that kernel on 8 matrices of 4096 x 14336: 2.120 GB read + 0.925 GB written (a later
+# capture on 4 matrices gives the same bytes per element). Traffic of that kernel grows with the
+# elements a launch covers.
 LINE3_DRAM_BYTES_PER_ELEMENT = 3.045e9 / (8 * 4096 * 14336)
 
 

@@ -186,6 +186,20 @@ int muon_b200_ns_workspace_layout_mode(int batch, int64_t m, int64_t n, int mode
 int muon_b200_ns_run(void* workspace, int batch, int64_t m, int64_t n, int mode, int steps,
                      const float* coeffs, float eps, int* result_slot, muon_b200_stream_t stream);
 
+/* muon_b200_ns_run followed by the update epilogue (muon_b200_epilogue) of the `count` parameters
+ * whose bf16 matrices the workspace holds, with the update done by the last GEMM of the iteration
+ * itself where that is possible: its epilogue reads the parameter, applies
+ * p = p*(1 - lr*wd) - lr * bf16(U*scale) with the roundings of muon_b200_epilogue and writes the
+ * parameter back, so the orthogonalised matrix never goes to memory. Fused for bfloat16 parameters
+ * of either orientation and for float32 parameters with rows <= cols, up to 32 per call, rows a
+ * multiple of 16 bytes; otherwise the iteration is followed by the epilogue kernel on the same
+ * stream. rows, cols, dtype, lr, weight_decay, scale as for muon_b200_epilogue; the workspace is
+ * laid out for (count, min(rows, cols), max(rows, cols), mode). Replaces muon.py:13-14 and :66-67
+ * (:98-99) for a group of parameters. */
+int muon_b200_ns_run_update(void* workspace, int mode, int steps, const float* coeffs, float eps,
+                            void* const* params, int count, int64_t rows, int64_t cols, int dtype,
+                            double lr, double weight_decay, double scale, muon_b200_stream_t stream);
+
 /* The whole of zeropower_via_newtonschulz5 (muon.py:748-799) in one call, with caller-owned input
  * and output: g is [batch, rows, cols] of element type dtype (MUON_B200_F32/BF16/F16/F64), pitch ldg
  * and batch pitch g_bs in elements, and is not modified. It is cast to bf16 (muon.py:760),

@@ -79,6 +79,9 @@ PROTOTYPES = {
     "muon_b200_ns_workspace_layout_mode": (c_int, [c_int, c_int64, c_int64, c_int, POINTER(NsLayout)]),
     "muon_b200_ns_run": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int, POINTER(c_float),
                                  c_float, POINTER(c_int), c_void_p]),
+    "muon_b200_ns_run_update": (c_int, [c_void_p, c_int, c_int, POINTER(c_float), c_float, POINTER(c_void_p),
+                                        c_int, c_int64, c_int64, c_int, c_double, c_double, c_double,
+                                        c_void_p]),
     "muon_b200_prologue": (c_int, [POINTER(c_void_p), POINTER(c_void_p), c_int, c_int64, c_int64,
                                    c_int, c_double, c_int, c_void_p, c_int64, c_int64, c_int,
                                    c_void_p]),

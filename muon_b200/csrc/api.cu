@@ -172,15 +172,15 @@ int muon_b200_ns_workspace_layout_mode(int batch, int64_t m, int64_t n, int mode
   return OK;
 }
 
-int muon_b200_ns_run(void* workspace, int batch, int64_t m, int64_t n, int mode, int steps,
-                     const float* coeffs, float eps, int* result_slot, muon_b200_stream_t stream) {
+namespace {
+// Buffers of a Newton-Schulz run inside a workspace laid out by muon_b200_ns_workspace_layout_mode.
+int workspace_buffers(void* workspace, int batch, int64_t m, int64_t n, int mode, NsBuffers* out,
+                      muon_b200_ns_layout* layout) {
   if (!workspace) return set_error(ERR_INVALID_ARG, "workspace is NULL");
   if (reinterpret_cast<uintptr_t>(workspace) & 255)
     return set_error(ERR_ALIGNMENT, "NS workspace must be 256-byte aligned");
-  int rc = ns_check_mode(mode, &steps, coeffs);
-  if (rc != OK) return rc;
   muon_b200_ns_layout l;
-  rc = muon_b200_ns_workspace_layout_mode(batch, m, n, mode, &l);
+  int rc = muon_b200_ns_workspace_layout_mode(batch, m, n, mode, &l);
   if (rc != OK) return rc;
   char* ws = static_cast<char*>(workspace);
   NsBuffers buf{};
@@ -204,7 +204,55 @@ int muon_b200_ns_run(void* workspace, int batch, int64_t m, int64_t n, int mode,
   buf.a_bs = l.a_bs;
   buf.fscratch = reinterpret_cast<float*>(ws + l.partials_offset_bytes);
   buf.f_bs = l.ldm;
+  *out = buf;
+  if (layout) *layout = l;
+  return OK;
+}
+}  // namespace
+
+int muon_b200_ns_run(void* workspace, int batch, int64_t m, int64_t n, int mode, int steps,
+                     const float* coeffs, float eps, int* result_slot, muon_b200_stream_t stream) {
+  int rc = ns_check_mode(mode, &steps, coeffs);
+  if (rc != OK) return rc;
+  NsBuffers buf;
+  rc = workspace_buffers(workspace, batch, m, n, mode, &buf, nullptr);
+  if (rc != OK) return rc;
   return ns_iterate_replayed(buf, batch, m, n, mode, steps, coeffs, eps, as_stream(stream), result_slot);
+}
+
+int muon_b200_ns_run_update(void* workspace, int mode, int steps, const float* coeffs, float eps,
+                            void* const* params, int count, int64_t rows, int64_t cols, int dtype,
+                            double lr, double weight_decay, double scale, muon_b200_stream_t stream) {
+  int rc = check_dtype(dtype);
+  if (rc != OK) return rc;
+  if (!params) return set_error(ERR_INVALID_ARG, "ns_run_update: params is NULL");
+  if (count < 1 || rows < 1 || cols < 1)
+    return set_error(ERR_INVALID_ARG, "ns_run_update needs count, rows, cols >= 1");
+  rc = ns_check_mode(mode, &steps, coeffs);
+  if (rc != OK) return rc;
+  const bool tall = rows > cols;
+  const int64_t m = tall ? cols : rows, n = tall ? rows : cols;
+  NsBuffers buf;
+  muon_b200_ns_layout l;
+  rc = workspace_buffers(workspace, count, m, n, mode, &buf, &l);
+  if (rc != OK) return rc;
+  UpdateSpec upd;
+  upd.param = params;
+  upd.dtype = dtype;
+  upd.rows = rows;
+  upd.cols = cols;
+  upd.scale = (float)scale;
+  upd.decay = (float)(1.0 - lr * weight_decay);
+  upd.neg_lr = (float)(-lr);
+  if (update_fusable(upd, count))
+    return ns_iterate_replayed(buf, count, m, n, mode, steps, coeffs, eps, as_stream(stream), nullptr, &upd);
+  // Not fusable (tall fp32 parameters, more than 32 of them, rows that are not 16-byte multiples):
+  // the iteration, then the update kernel on the same stream.
+  int slot = 0;
+  rc = ns_iterate_replayed(buf, count, m, n, mode, steps, coeffs, eps, as_stream(stream), &slot);
+  if (rc != OK) return rc;
+  return muon_b200_epilogue(params, count, rows, cols, dtype, buf.x[slot], l.ldn, l.x_bs, tall ? 1 : 0, lr,
+                            weight_decay, scale, stream);
 }
 
 int64_t muon_b200_zeropower_scratch_bytes(int batch, int64_t rows, int64_t cols, int mode) {
@@ -366,12 +414,8 @@ int muon_b200_muon_step(void* const* params, void* const* grads, void* const* mo
   rc = muon_b200_prologue(grads, moms, count, rows, cols, dtype, beta, nesterov,
                           ws + l.x_offset_bytes, l.ldn, l.x_bs, tall ? 1 : 0, stream);
   if (rc != OK) return rc;
-  int slot = 0;
-  rc = muon_b200_ns_run(workspace, count, m, n, ns_mode, ns_steps, ns_coeffs, ns_eps, &slot, stream);
-  if (rc != OK) return rc;
-  const void* u = ws + (slot == 0 ? l.x_offset_bytes : l.c_offset_bytes);
-  return muon_b200_epilogue(params, count, rows, cols, dtype, u, l.ldn, l.x_bs, tall ? 1 : 0, lr,
-                            weight_decay, scale, stream);
+  return muon_b200_ns_run_update(workspace, ns_mode, ns_steps, ns_coeffs, ns_eps, params, count, rows, cols,
+                                 dtype, lr, weight_decay, scale, stream);
 }
 
 int muon_b200_adam(void* const* params, void* const* grads, void* const* exp_avg,

@@ -37,7 +37,7 @@ int ns_check_mode(int mode, int* steps, const float* coeffs) {
 }
 
 int ns_iterate(const NsBuffers& buf, int batch, int64_t m, int64_t n, int mode, int steps,
-               const float* coeffs, float eps, cudaStream_t st, int* result_index) {
+               const float* coeffs, float eps, cudaStream_t st, int* result_index, const UpdateSpec* upd) {
   int cur = 0;
   int rc;
   bool have_gram = false;
@@ -119,7 +119,7 @@ int ns_iterate(const NsBuffers& buf, int batch, int64_t m, int64_t n, int mode, 
       if (rc != OK) return rc;
       rc = launch_ns_gemm(MODE_BX, buf.B, buf.ldm, buf.a_bs, X, ldx, xbs, buf.x[cur ^ 1], buf.ldx[cur ^ 1],
                           buf.x_bs[cur ^ 1], batch, m, n, m, a, 0.f, ADD_GENERIC, st, nullptr, nullptr, 0,
-                          l3_out.kind != F8_NONE ? &l3_out : nullptr);
+                          l3_out.kind != F8_NONE ? &l3_out : nullptr, k + 1 == steps ? upd : nullptr);
       if (rc != OK) return rc;
       cur ^= 1;
       continue;
@@ -142,7 +142,7 @@ int ns_iterate(const NsBuffers& buf, int batch, int64_t m, int64_t n, int mode, 
     if (rc != OK) return rc;
     rc = launch_ns_gemm(MODE_BX, buf.B, buf.ldm, buf.a_bs, X, ldx, xbs, buf.x[cur ^ 1], buf.ldx[cur ^ 1],
                         buf.x_bs[cur ^ 1], batch, m, n, m, a, 0.f, ADD_GENERIC, st, nullptr, nullptr, 0,
-                        l3_out.kind != F8_NONE ? &l3_out : nullptr);
+                        l3_out.kind != F8_NONE ? &l3_out : nullptr, k + 1 == steps ? upd : nullptr);
     if (rc != OK) return rc;
     cur ^= 1;
   }
@@ -233,6 +233,12 @@ struct GraphKey {  // plain data, compared with memcmp: keep it free of padding 
   int batch, mode, steps, has_coeffs, device, reserved_sms;
   float eps;
   float coeffs[3 * kGraphMaxSteps];
+  // fused update (all zero without one): the graph holds the parameter addresses and the
+  // step's learning rate, so a run with a changing learning rate never comes back to a graph
+  void* upd_param[kMaxUpdateTensors];
+  int64_t upd_rows, upd_cols;
+  int upd_dtype;
+  float upd_scale, upd_decay, upd_neg_lr;
 };
 
 struct GraphEntry {
@@ -265,17 +271,18 @@ bool graph_replay_enabled() {
 }
 
 int ns_iterate_replayed(const NsBuffers& buf, int batch, int64_t m, int64_t n, int mode, int steps,
-                        const float* coeffs, float eps, cudaStream_t stream, int* result_index) {
+                        const float* coeffs, float eps, cudaStream_t stream, int* result_index,
+                        const UpdateSpec* upd) {
   const double flops = (double)batch * steps * ((double)m * (m + 1) * n + (double)m * m * (m + 1) + 2.0 * m * m * n);
   cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
   if (!graph_replay_enabled() || timing_enabled() || steps > kGraphMaxSteps || flops > kGraphMaxFlops ||
       cudaStreamIsCapturing(stream, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) {
     (void)cudaGetLastError();
-    return ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, stream, result_index);
+    return ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, stream, result_index, upd);
   }
   int dev = 0;
   MB_CUDA_CHECK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, stream, result_index);
+  if (dev < 0 || dev >= 64) return ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, stream, result_index, upd);
 
   GraphKey key;
   std::memset(&key, 0, sizeof(key));
@@ -286,6 +293,11 @@ int ns_iterate_replayed(const NsBuffers& buf, int batch, int64_t m, int64_t n, i
   key.reserved_sms = get_reserved_sms();
   key.eps = eps;
   if (coeffs) std::memcpy(key.coeffs, coeffs, sizeof(float) * 3 * steps);
+  if (upd) {
+    for (int b = 0; b < batch && b < kMaxUpdateTensors; ++b) key.upd_param[b] = upd->param[b];
+    key.upd_rows = upd->rows; key.upd_cols = upd->cols; key.upd_dtype = upd->dtype + 1;
+    key.upd_scale = upd->scale; key.upd_decay = upd->decay; key.upd_neg_lr = upd->neg_lr;
+  }
 
   std::lock_guard<std::mutex> lk(g_graph_mu);
   GraphEntry* hit = nullptr;
@@ -293,7 +305,7 @@ int ns_iterate_replayed(const NsBuffers& buf, int batch, int64_t m, int64_t n, i
     if (std::memcmp(&e.key, &key, sizeof(key)) == 0) { hit = &e; break; }
   if (hit) {
     hit->last_use = ++g_graph_clock;
-    if (hit->failed) return ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, stream, result_index);
+    if (hit->failed) return ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, stream, result_index, upd);
     if (hit->exec) {
       MB_CUDA_CHECK(cudaGraphLaunch(hit->exec, stream));
       add_launch_counts(hit->counts);
@@ -315,7 +327,7 @@ int ns_iterate_replayed(const NsBuffers& buf, int batch, int64_t m, int64_t n, i
     seen.key = key;
     seen.last_use = ++g_graph_clock;
     g_graphs.push_back(seen);
-    return ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, stream, result_index);
+    return ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, stream, result_index, upd);
   }
 
   // Second sighting: capture the launch sequence on the library's own stream (the caller's may be
@@ -328,7 +340,7 @@ int ns_iterate_replayed(const NsBuffers& buf, int batch, int64_t m, int64_t n, i
   int rc = OK;
   if (cudaStreamBeginCapture(g_capture_stream[dev], cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
     set_launch_recorder(fresh.counts);
-    rc = ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, g_capture_stream[dev], &fresh.result_index);
+    rc = ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, g_capture_stream[dev], &fresh.result_index, upd);
     set_launch_recorder(nullptr);
     const cudaError_t ended = cudaStreamEndCapture(g_capture_stream[dev], &graph);
     // The launches above were only recorded: take them out of the process totals again; the
@@ -343,7 +355,7 @@ int ns_iterate_replayed(const NsBuffers& buf, int batch, int64_t m, int64_t n, i
       (void)cudaGetLastError();
       fresh.failed = true;
       for (int k = 0; k < K_KIND_COUNT; ++k) fresh.counts[k] = 0;
-      return ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, stream, result_index);
+      return ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, stream, result_index, upd);
     }
     if (ended != cudaSuccess || !graph ||
         cudaGraphInstantiate(&fresh.exec, graph, 0) != cudaSuccess) {
@@ -354,7 +366,7 @@ int ns_iterate_replayed(const NsBuffers& buf, int batch, int64_t m, int64_t n, i
   (void)cudaGetLastError();
   if (!fresh.exec) {
     fresh.failed = true;
-    return ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, stream, result_index);
+    return ns_iterate(buf, batch, m, n, mode, steps, coeffs, eps, stream, result_index, upd);
   }
   MB_CUDA_CHECK(cudaGraphLaunch(fresh.exec, stream));
   add_launch_counts(fresh.counts);

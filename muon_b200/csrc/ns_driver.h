@@ -8,6 +8,8 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 
+#include "ns_gemm.h"
+
 namespace mb {
 
 constexpr int kFroChunksMax = 296;  // partial sums per matrix of the Frobenius reduction
@@ -39,9 +41,12 @@ inline int64_t fp8_pitch(int64_t cols) { return (cols + 15) / 16 * 16; }
 int64_t ns_fp8_extra_bytes(int batch, int64_t m, int64_t n);
 
 // steps > 0; coeffs is NULL (the mode's table) or steps triples (a, b, c). On success
-// *result_index tells which of x[0] / x[1] holds the result (steps % 2).
+// *result_index tells which of x[0] / x[1] holds the result (steps % 2). With `upd` (which must be
+// update_fusable) the last line 3 applies its output to the parameters instead of storing it: no
+// buffer holds the result then.
 int ns_iterate(const NsBuffers& buf, int batch, int64_t m, int64_t n, int mode, int steps,
-               const float* coeffs, float eps, cudaStream_t stream, int* result_index);
+               const float* coeffs, float eps, cudaStream_t stream, int* result_index,
+               const UpdateSpec* upd = nullptr);
 
 // Same launch sequence, replayed from a CUDA graph when that pays: a short iteration (a few
 // matrices of a few hundred rows) is thirteen kernels of microseconds each, and issuing them one
@@ -53,7 +58,8 @@ int ns_iterate(const NsBuffers& buf, int batch, int64_t m, int64_t n, int mode, 
 // switched off (set_graph_replay(false) or MUON_B200_GRAPH=0). Graph instantiation allocates
 // driver-side resources, so callers that must not allocate use ns_iterate.
 int ns_iterate_replayed(const NsBuffers& buf, int batch, int64_t m, int64_t n, int mode, int steps,
-                        const float* coeffs, float eps, cudaStream_t stream, int* result_index);
+                        const float* coeffs, float eps, cudaStream_t stream, int* result_index,
+                        const UpdateSpec* upd = nullptr);
 void set_graph_replay(bool on);
 bool graph_replay_enabled();
 

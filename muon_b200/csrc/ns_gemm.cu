@@ -29,6 +29,7 @@
 //   warps 2..   epilogue: tcgen05.ld -> fp32 epilogue -> bf16 stores (+ mirrored stores)
 // The grid is persistent: each CTA (or CTA pair) walks tiles w, w + stride, ...
 #include "common.cuh"
+#include "elementwise.h"
 #include "ns_gemm.h"
 #include "profiling.h"
 
@@ -284,12 +285,54 @@ __device__ __forceinline__ void block_store_coal_e4m3(uint8_t* base, long long l
         bf16x8_to_e4m3x8(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3], scale);
 }
 
+// ---------------------------------------------------------------------------
+// Fused parameter update (reference muon.py:14 and :66-67, see UpdateSpec in ns_gemm.h): the
+// last line 3 of an orthogonalisation applies its output to the parameter instead of storing it.
+//   u' = bf16(U * scale);  p1 = T(p * decay);  p = T(p1 - lr * u')        (T = parameter dtype)
+// The same operations, in the same order and with the same roundings, as epilogue_kernel.
+// ---------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float upd_round(float v);
+template <>
+__device__ __forceinline__ float upd_round<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float upd_round<__nv_bfloat16>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+template <typename T>
+__device__ __forceinline__ float upd_apply(float pv, float u_bf16, float scale, float decay, float neg_lr) {
+  const float us = __bfloat162float(__float2bfloat16_rn(u_bf16 * scale));
+  const float p1 = upd_round<T>(pv * decay);
+  return upd_round<T>(fmaf(neg_lr, us, p1));
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr) : "memory");
+  return v;
+}
+// A 32-row x 16-float block (64 bytes per row, like a 32 x 32 bf16 block) in the "coal" pattern.
+__device__ __forceinline__ void block_load_coal_f32(const float* base, long long ld, int row0, int col0,
+                                                    int lane, uint32_t (&w)[16]) {
+  const float* ptr = base + (row0 + (lane >> 2)) * ld + col0 + (lane & 3) * 4;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint4 q = *reinterpret_cast<const uint4*>(ptr + 8 * i * ld);
+    w[4 * i] = q.x; w[4 * i + 1] = q.y; w[4 * i + 2] = q.z; w[4 * i + 3] = q.w;
+  }
+}
+__device__ __forceinline__ void block_store_coal_f32(float* base, long long ld, int row0, int col0, int lane,
+                                                     const uint32_t (&w)[16]) {
+  float* ptr = base + (row0 + (lane >> 2)) * ld + col0 + (lane & 3) * 4;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    *reinterpret_cast<uint4*>(ptr + 8 * i * ld) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+}
+
 // ADD: how line 2's addend is formed (AddendMode); the other two lines pass ADD_SYMMETRIC.
-// F8: an Fp8Kind.
-template <int MODE, bool B_MN, int CTAS, int EW, int ADD, int F8>
+// VAR: a Variant (e4m3 operands / extra e4m3 output / fused parameter update).
+template <int MODE, bool B_MN, int CTAS, int EW, int ADD, int VAR>
 __global__ void __launch_bounds__(num_threads(EW), 1)
 ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const GemmParams p) {
+               const __grid_constant__ GemmParams p) {
   using C = Cfg<CTAS>;
   constexpr int STAGES = C::STAGES;
   constexpr int TILE_M = C::TILE_M;
@@ -352,7 +395,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   griddep_wait();
 
   // One shared-memory stage holds 128 bytes of K per row: 64 bf16 or 128 e4m3 elements.
-  constexpr int KSTEP = F8 == F8_OPERANDS ? 2 * BK : BK;
+  constexpr int KSTEP = VAR == F8_OPERANDS ? 2 * BK : BK;
   const int k_blocks = (p.K + KSTEP - 1) / KSTEP;
   const int total_tiles = p.tiles_per_batch * p.batch;
   const int work0 = blockIdx.x / CTAS;
@@ -419,7 +462,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
     if (lane == 0 && leader) {
-      constexpr uint32_t idesc = make_idesc(B_MN, TILE_M, F8 == F8_OPERANDS);
+      constexpr uint32_t idesc = make_idesc(B_MN, TILE_M, VAR == F8_OPERANDS);
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
@@ -461,7 +504,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                                         : static_cast<uint64_t>((kk * UMMA_K * 2) >> 4);
             const uint32_t accumulate = (kb | kk) != 0 ? 1u : 0u;
             // 32 bytes of K per instruction either way: 16 bf16 or 32 e4m3 elements.
-            if constexpr (F8 == F8_OPERANDS) {
+            if constexpr (VAR == F8_OPERANDS) {
               if (CTAS == 2) umma_f8_ss_pair(d_tmem, a_desc + a_adv, b_desc + b_adv, idesc, accumulate);
               else umma_f8_ss(d_tmem, a_desc + a_adv, b_desc + b_adv, idesc, accumulate);
             } else {
@@ -522,7 +565,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           (MODE == MODE_SYRK) ? nullptr : p.add + static_cast<long long>(tc.batch) * p.add_bs;
       __nv_bfloat16* out_row = out_b + static_cast<long long>(r) * p.ldo;
       // e4m3 copy of the output (null when this launch keeps none)
-      uint8_t* out8_b = (F8 != F8_NONE && p.out8) ? p.out8 + static_cast<long long>(tc.batch) * p.out8_bs : nullptr;
+      uint8_t* out8_b = (VAR != F8_NONE && p.out8) ? p.out8 + static_cast<long long>(tc.batch) * p.out8_bs : nullptr;
       const __nv_bfloat16* add_row =
           (MODE == MODE_SYRK) ? nullptr : add_b + static_cast<long long>(r) * p.ldadd;
 
@@ -597,7 +640,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if constexpr (MODE == MODE_AXPBY) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) f[j] *= p.alpha;
-          if constexpr (F8 == F8_OPERANDS) {
+          if constexpr (VAR == F8_OPERANDS) {
             // The operand was E = A - I: the identity's share, diag * I, lands on the diagonal
             // (block on the diagonal: this thread's row is column `lane` of the chunk).
             if (col0 == row_base) {
@@ -627,7 +670,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           for (int j = 0; j < 16; ++j)
             packed[j] = pack_bf16x2(fmaf(a[2 * j], p.alpha, f[2 * j]), fmaf(a[2 * j + 1], p.alpha, f[2 * j + 1]));
         } else {
-          if constexpr (F8 == F8_OPERANDS) {
+          if constexpr (VAR == F8_OPERANDS) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) f[j] *= p.acc_scale;  // the operands carried a power-of-two scale
           }
@@ -635,7 +678,129 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           for (int j = 0; j < 16; ++j) packed[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
         }
 
-        if constexpr (MODE == MODE_BX) {
+        if constexpr (MODE == MODE_BX && VAR >= V_UPD_BF16) {
+          // Last line 3 of the run: `packed` holds the bf16 Newton-Schulz output of row r, columns
+          // col0 .. col0+31; it goes into the parameter instead of into the workspace.
+          if constexpr (VAR == V_UPD_BF16) {
+            // bf16 parameter [M, N] in the tile's orientation
+            __nv_bfloat16* pb = static_cast<__nv_bfloat16*>(p.upd_param[tc.batch]);
+            if (full) {
+              uint32_t pw[16], own[16];
+              block_load_coal(pb, p.N, row_base, col0, lane, pw);
+              stage_put_coal(stage, lane, pw);
+              __syncwarp();
+              stage_get_row(stage, lane, own);
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const float n0 = upd_apply<__nv_bfloat16>(bf16_bits_to_float(own[j] & 0xffffu),
+                                                          bf16_bits_to_float(packed[j] & 0xffffu), p.upd_scale,
+                                                          p.upd_decay, p.upd_neg_lr);
+                const float n1 = upd_apply<__nv_bfloat16>(bf16_bits_to_float(own[j] >> 16),
+                                                          bf16_bits_to_float(packed[j] >> 16), p.upd_scale,
+                                                          p.upd_decay, p.upd_neg_lr);
+                own[j] = pack_bf16x2(n0, n1);
+              }
+              stage_put_row(stage, lane, own);
+              __syncwarp();
+              stage_get_coal(stage, lane, pw);
+              __syncwarp();
+              block_store_coal(pb, p.N, row_base, col0, lane, pw);
+            } else if (row_ok) {
+              __nv_bfloat16* prow = pb + static_cast<long long>(r) * p.N;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int col = col0 + j;
+                if (col < p.N) {
+                  const uint32_t u = (j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xffffu);
+                  prow[col] = __float2bfloat16_rn(upd_apply<__nv_bfloat16>(
+                      __bfloat162float(prow[col]), bf16_bits_to_float(u), p.upd_scale, p.upd_decay, p.upd_neg_lr));
+                }
+              }
+            }
+          } else if constexpr (VAR == V_UPD_BF16_T) {
+            // bf16 parameter [N, M]: the tile is its transpose; block (col0.., row_base..) of it
+            __nv_bfloat16* pb = static_cast<__nv_bfloat16*>(p.upd_param[tc.batch]);
+            if (full) {
+              uint32_t pw[16], np[16];
+              block_load_coal(pb, p.M, col0, row_base, lane, pw);
+              stage_put_coal(stage, lane, pw);
+              __syncwarp();
+              // this thread's tile row r is column `lane` of the staged block: read it down the rows
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const float o0 = bf16_bits_to_float(lds_u16(stage_addr(stage, 2 * j, lane >> 3) + (lane & 7) * 2));
+                const float o1 = bf16_bits_to_float(lds_u16(stage_addr(stage, 2 * j + 1, lane >> 3) + (lane & 7) * 2));
+                const float n0 = upd_apply<__nv_bfloat16>(o0, bf16_bits_to_float(packed[j] & 0xffffu), p.upd_scale,
+                                                          p.upd_decay, p.upd_neg_lr);
+                const float n1 = upd_apply<__nv_bfloat16>(o1, bf16_bits_to_float(packed[j] >> 16), p.upd_scale,
+                                                          p.upd_decay, p.upd_neg_lr);
+                np[j] = pack_bf16x2(n0, n1);
+              }
+              __syncwarp();
+              // transposed store, as for the mirrored blocks of lines 1 and 2
+              const int odd = lane & 1;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const uint32_t other = __shfl_xor_sync(0xffffffffu, np[j], 1);
+                const uint32_t word = odd ? __byte_perm(other, np[j], 0x7632) : __byte_perm(np[j], other, 0x5410);
+                sts32(stage_addr(stage, 2 * j + odd, lane >> 3) + ((lane & 6) << 1), word);
+              }
+              __syncwarp();
+              stage_get_coal(stage, lane, pw);
+              __syncwarp();
+              block_store_coal(pb, p.M, col0, row_base, lane, pw);
+            } else if (row_ok) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int col = col0 + j;
+                if (col < p.N) {
+                  __nv_bfloat16* pe = pb + static_cast<long long>(col) * p.M + r;
+                  const uint32_t u = (j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xffffu);
+                  *pe = __float2bfloat16_rn(upd_apply<__nv_bfloat16>(__bfloat162float(*pe), bf16_bits_to_float(u),
+                                                                     p.upd_scale, p.upd_decay, p.upd_neg_lr));
+                }
+              }
+            }
+          } else {
+            // fp32 parameter [M, N] in the tile's orientation: two halves of 16 columns, each a
+            // 32-row x 64-byte block like a bf16 one
+            float* pf = static_cast<float*>(p.upd_param[tc.batch]);
+            if (full) {
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                uint32_t pw[16], own[16];
+                block_load_coal_f32(pf, p.N, row_base, col0 + 16 * h, lane, pw);
+                stage_put_coal(stage, lane, pw);
+                __syncwarp();
+                stage_get_row(stage, lane, own);
+                __syncwarp();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  const int jj = 16 * h + j;
+                  const uint32_t u = (jj & 1) ? (packed[jj >> 1] >> 16) : (packed[jj >> 1] & 0xffffu);
+                  own[j] = __float_as_uint(upd_apply<float>(__uint_as_float(own[j]), bf16_bits_to_float(u), p.upd_scale,
+                                                            p.upd_decay, p.upd_neg_lr));
+                }
+                stage_put_row(stage, lane, own);
+                __syncwarp();
+                stage_get_coal(stage, lane, pw);
+                __syncwarp();
+                block_store_coal_f32(pf, p.N, row_base, col0 + 16 * h, lane, pw);
+              }
+            } else if (row_ok) {
+              float* prow = pf + static_cast<long long>(r) * p.N;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int col = col0 + j;
+                if (col < p.N) {
+                  const uint32_t u = (j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xffffu);
+                  prow[col] = upd_apply<float>(prow[col], bf16_bits_to_float(u), p.upd_scale, p.upd_decay, p.upd_neg_lr);
+                }
+              }
+            }
+          }
+        } else if constexpr (MODE == MODE_BX) {
           if (full) {
             uint32_t w[16];
             stage_put_row(stage, lane, packed);
@@ -643,12 +808,12 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             stage_get_coal(stage, lane, w);
             __syncwarp();
             block_store_coal(out_b, p.ldo, row_base, col0, lane, w);
-            if constexpr (F8 == F8_EXTRA_OUT) {
+            if constexpr (VAR == F8_EXTRA_OUT) {
               if (out8_b) block_store_coal_e4m3(out8_b, p.ldo8, row_base, col0, lane, w, p.out8_scale);
             }
           } else if (row_ok) {
             store_row32(out_row, col0, p.N, packed);
-            if constexpr (F8 == F8_EXTRA_OUT) {
+            if constexpr (VAR == F8_EXTRA_OUT) {
               if (out8_b) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
@@ -717,7 +882,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             stage_get_coal(stage, lane, w);
             __syncwarp();
             block_store_coal(out_b, p.ldo, row_base, col0, lane, w);
-            if constexpr (F8 == F8_OPERANDS && MODE == MODE_SYRK) {
+            if constexpr (VAR == F8_OPERANDS && MODE == MODE_SYRK) {
               // strictly below the diagonal: (A - I) = A here
               if (out8_b) block_store_coal_e4m3(out8_b, p.ldo8, row_base, col0, lane, w, p.out8_scale);
             }
@@ -732,7 +897,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             stage_get_coal(stage, lane, w);
             __syncwarp();
             block_store_coal(out_b, p.ldo, col0, row_base, lane, w);
-            if constexpr (F8 == F8_OPERANDS && MODE == MODE_SYRK) {
+            if constexpr (VAR == F8_OPERANDS && MODE == MODE_SYRK) {
               if (out8_b) block_store_coal_e4m3(out8_b, p.ldo8, col0, row_base, lane, w, p.out8_scale);
             }
           } else if (row_ok) {
@@ -750,7 +915,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     static_cast<unsigned short>((j & 1) ? (w >> 16) : (w & 0xffffu));
               }
             }
-            if constexpr (F8 == F8_OPERANDS && MODE == MODE_SYRK) {
+            if constexpr (VAR == F8_OPERANDS && MODE == MODE_SYRK) {
               if (out8_b) {
                 // E8 = e4m3((A - I) * se), from the bf16 values just stored: own position for
                 // col <= r (the diagonal loses its 1), mirrored position for col < r.
@@ -840,7 +1005,7 @@ int encode_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, i
   return OK;
 }
 
-constexpr int kKernelSlots = 3 * 2 * 2 * 3 * 3;  // mode x CTAs per tile x epilogue warps x addend mode x e4m3 kind
+constexpr int kKernelSlots = 3 * 2 * 2 * 3 * 6;  // mode x CTAs per tile x epilogue warps x addend mode x variant
 struct DeviceInfo {
   int sm_count = 0;
   int cc_major = 0;
@@ -893,7 +1058,7 @@ int launch_instance(int dev, int sms, const CUtensorMap& ta, const CUtensorMap& 
                     const GemmParams& p, cudaStream_t stream) {
   using C = Cfg<CTAS>;
   auto kern = ns_gemm_kernel<MODE, B_MN, CTAS, EW, ADD, F8>;
-  const int slot = (((MODE * 2 + (CTAS - 1)) * 2 + (EW == 4 ? 0 : 1)) * 3 + ADD) * 3 + F8;
+  const int slot = (((MODE * 2 + (CTAS - 1)) * 2 + (EW == 4 ? 0 : 1)) * 3 + ADD) * 6 + F8;
   const long long total = (long long)p.tiles_per_batch * p.batch;
 
   cudaLaunchConfig_t cfg = {};
@@ -956,6 +1121,21 @@ constexpr int kLongK = 2048;  // from this K on, four epilogue warps (see launch
 template <int MODE, bool B_MN, int CTAS>
 int launch_epi(int ew, int f8, int dev, int sms, const CUtensorMap& ta, const CUtensorMap& tb,
                const GemmParams& p, cudaStream_t stream) {
+  if constexpr (MODE == MODE_BX) {
+    // line 3 with the parameter update fused into its epilogue
+    switch (f8) {
+      case V_UPD_BF16:
+        return ew == 4 ? launch_instance<MODE, B_MN, CTAS, 4, ADD_SYMMETRIC, V_UPD_BF16>(dev, sms, ta, tb, p, stream)
+                       : launch_instance<MODE, B_MN, CTAS, 8, ADD_SYMMETRIC, V_UPD_BF16>(dev, sms, ta, tb, p, stream);
+      case V_UPD_BF16_T:
+        return ew == 4 ? launch_instance<MODE, B_MN, CTAS, 4, ADD_SYMMETRIC, V_UPD_BF16_T>(dev, sms, ta, tb, p, stream)
+                       : launch_instance<MODE, B_MN, CTAS, 8, ADD_SYMMETRIC, V_UPD_BF16_T>(dev, sms, ta, tb, p, stream);
+      case V_UPD_F32:
+        return ew == 4 ? launch_instance<MODE, B_MN, CTAS, 4, ADD_SYMMETRIC, V_UPD_F32>(dev, sms, ta, tb, p, stream)
+                       : launch_instance<MODE, B_MN, CTAS, 8, ADD_SYMMETRIC, V_UPD_F32>(dev, sms, ta, tb, p, stream);
+      default: break;
+    }
+  }
   if (f8 != F8_NONE) {
     // e4m3 variants exist for the symmetric-addend forms only (iterations after the first).
     constexpr int KIND = MODE == MODE_BX ? F8_EXTRA_OUT : F8_OPERANDS;
@@ -978,6 +1158,21 @@ int launch_epi(int ew, int f8, int dev, int sms, const CUtensorMap& ta, const CU
 }
 
 }  // namespace
+
+bool update_fusable(const UpdateSpec& u, int batch) {
+  if (!u.param || batch < 1 || batch > kMaxUpdateTensors || u.rows < 1 || u.cols < 1) return false;
+  const bool tall = u.rows > u.cols;
+  if (u.dtype == DT_F32) {
+    if (tall || u.cols % 4 != 0) return false;  // tall fp32 parameters: left to the epilogue kernel
+  } else if (u.dtype == DT_BF16) {
+    if (u.cols % 8 != 0) return false;          // rows of the parameter must be 16-byte multiples
+  } else {
+    return false;
+  }
+  for (int b = 0; b < batch; ++b)
+    if (!u.param[b] || (reinterpret_cast<uintptr_t>(u.param[b]) & 15)) return false;
+  return true;
+}
 
 void set_reserved_sms(int n) { g_reserved_sms.store(n < 0 ? 0 : n); }
 int get_reserved_sms() { return g_reserved_sms.load(); }
@@ -1008,7 +1203,7 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
                    const __nv_bfloat16* opb, int64_t ldb, int64_t b_bs, __nv_bfloat16* out,
                    int64_t ldo, int64_t out_bs, int batch, int64_t M, int64_t N, int64_t K,
                    float alpha, float beta, int sym_add, cudaStream_t stream, const __nv_bfloat16* addend,
-                   const float* row_scale, int64_t scale_bs, const Fp8Spec* f8) {
+                   const float* row_scale, int64_t scale_bs, const Fp8Spec* f8, const UpdateSpec* upd) {
   if (!opa || !opb || !out) return set_error(ERR_INVALID_ARG, "null pointer passed to NS GEMM");
   if (batch < 1 || M < 1 || N < 1 || K < 1)
     return set_error(ERR_INVALID_ARG, "NS GEMM needs batch, M, N, K >= 1 (got %d, %lld, %lld, %lld)",
@@ -1041,9 +1236,21 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
   p.out = out;
   p.ldo = ldo;
   p.out_bs = out_bs;
-  const int f8_kind = f8 ? f8->kind : F8_NONE;
+  int f8_kind = f8 ? f8->kind : F8_NONE;
   p.acc_scale = 1.f;
-  if (f8_kind != F8_NONE) {
+  if (upd) {
+    if (mode != MODE_BX || f8_kind != F8_NONE || !update_fusable(*upd, batch))
+      return set_error(ERR_INVALID_ARG, "this parameter update cannot be fused into the launch");
+    const bool tall = upd->rows > upd->cols;
+    if ((tall ? upd->cols : upd->rows) != M || (tall ? upd->rows : upd->cols) != N)
+      return set_error(ERR_INVALID_ARG, "fused update: parameter shape does not match the product");
+    for (int b = 0; b < batch; ++b) p.upd_param[b] = upd->param[b];
+    p.upd_scale = upd->scale;
+    p.upd_decay = upd->decay;
+    p.upd_neg_lr = upd->neg_lr;
+    f8_kind = upd->dtype == DT_F32 ? V_UPD_F32 : (tall ? V_UPD_BF16_T : V_UPD_BF16);
+  }
+  if (f8 && f8->kind != F8_NONE) {
     if ((f8_kind == F8_OPERANDS) != (mode != MODE_BX))
       return set_error(ERR_INVALID_ARG, "e4m3 operands go with lines 1 and 2, the extra e4m3 output with line 3");
     if (f8_kind == F8_OPERANDS && (!f8->op8 || sym_add != ADD_SYMMETRIC))

@@ -20,12 +20,32 @@ enum AddendMode : int {
   ADD_ROW_SCALED = 2,  // A = S / s with S symmetric: both addends are rebuilt from S and s
 };
 
-// 8-bit floating point (e4m3) in the two symmetric products, see Fp8Spec.
-enum Fp8Kind : int {
+// Kernel variants beyond mode and addend: 8-bit floating point (e4m3) in the two symmetric
+// products (see Fp8Spec), and the parameter update fused into the last line 3 (see UpdateSpec).
+enum Variant : int {
   F8_NONE = 0,
-  F8_OPERANDS = 1,  // the product's operands are e4m3 (lines 1 and 2)
-  F8_EXTRA_OUT = 2, // bf16 product that also writes an e4m3 copy of its output (line 3)
+  F8_OPERANDS = 1,   // the product's operands are e4m3 (lines 1 and 2)
+  F8_EXTRA_OUT = 2,  // bf16 product that also writes an e4m3 copy of its output (line 3)
+  V_UPD_BF16 = 3,    // line 3 applies its output to bf16 parameters of the tile's orientation
+  V_UPD_BF16_T = 4,  // ... to bf16 parameters stored as the transpose of the tile (tall parameters)
+  V_UPD_F32 = 5,     // ... to fp32 parameters of the tile's orientation
 };
+
+constexpr int kMaxUpdateTensors = 32;  // parameters one fused-update launch can address
+
+// The update epilogue (reference muon.py:14 and :66-67) done by the last line 3 itself:
+//   p = T(T(p * decay) + neg_lr * bf16(U * scale))
+// param[b] is the parameter of matrix b of the batch, contiguous [rows, cols]; the iteration ran
+// on its transpose when rows > cols.
+struct UpdateSpec {
+  void* const* param = nullptr;
+  int dtype = 0;  // a DType
+  int64_t rows = 0, cols = 0;
+  float scale = 1.f, decay = 1.f, neg_lr = 0.f;
+};
+// Whether launch_ns_gemm can fuse this update (fp32 tall parameters, batches beyond
+// kMaxUpdateTensors and rows that are not 16-byte multiples are left to the epilogue kernel).
+bool update_fusable(const UpdateSpec& u, int batch);
 
 // The e4m3 variant of the iteration keeps, beside the bf16 matrices, X8 = e4m3(X * sx) and
 // E8 = e4m3((A - I) * se), both with power-of-two scales:
@@ -64,6 +84,9 @@ struct GemmParams {
   uint8_t* out8;
   long long ldo8, out8_bs;
   float out8_scale, acc_scale, diag;
+  // fused parameter update (see UpdateSpec)
+  void* upd_param[kMaxUpdateTensors];
+  float upd_scale, upd_decay, upd_neg_lr;
 };
 
 int device_sm_count(int* sm_count_out);
@@ -77,6 +100,6 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
                    int64_t ldo, int64_t out_bs, int batch, int64_t M, int64_t N, int64_t K,
                    float alpha, float beta, int sym_add, cudaStream_t stream,
                    const __nv_bfloat16* addend = nullptr, const float* row_scale = nullptr,
-                   int64_t scale_bs = 0, const Fp8Spec* f8 = nullptr);
+                   int64_t scale_bs = 0, const Fp8Spec* f8 = nullptr, const UpdateSpec* upd = nullptr);
 
 }  // namespace mb

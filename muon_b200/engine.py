@@ -307,7 +307,7 @@ class CudaBackend:
                                                ctypes.byref(slot), stream))
                     u = wptr + (layout.x_offset_bytes if slot.value == 0 else layout.c_offset_bytes)
                     self._epilogue(params[s:e], peer_ptrs, rows, cols, code, u, layout, tall, lr, weight_decay,
-                                   scale, stream)
+                                   scale, stream)  # the update kernel also writes the peers' copies
                 self.launch_groups += 1
                 if after_group is not None:
                     done = torch.cuda.Event()
@@ -369,19 +369,30 @@ class CudaBackend:
                 l = layouts[i]
                 next_p = prologue(i + 1) if i + 1 < len(groups) else None
                 main.wait_event(p_done)
-                slot = ctypes.c_int(0)
-                check(lib.muon_b200_ns_run(ws_ptr[i % 2], e - s, m_, n_, ns_mode, steps, None, eps,
-                                           ctypes.byref(slot), main.cuda_stream))
-                ns_done = torch.cuda.Event()
-                ns_done.record(main)
-                side.wait_event(ns_done)
-                u = ws_ptr[i % 2] + (l.x_offset_bytes if slot.value == 0 else l.c_offset_bytes)
-                self._epilogue(params[s:e], peer_ptrs, rows, cols, code, u, l, tall, lr, weight_decay, scale,
-                               side.cuda_stream)
-                if after_group is not None:
-                    done = torch.cuda.Event()
-                    done.record(side)
-                    after_group(params[s:e], done)
+                if peer_ptrs is None:
+                    # the last GEMM of the iteration applies the update itself (where it can)
+                    check(lib.muon_b200_ns_run_update(
+                        ws_ptr[i % 2], ns_mode, steps, None, eps, ptr_array([p.data_ptr() for p in params[s:e]]),
+                        e - s, rows, cols, code, lr, weight_decay, scale, main.cuda_stream))
+                    ns_done = torch.cuda.Event()
+                    ns_done.record(main)
+                    side.wait_event(ns_done)  # the next prologue but one reuses this workspace
+                    if after_group is not None:
+                        after_group(params[s:e], ns_done)
+                else:
+                    slot = ctypes.c_int(0)
+                    check(lib.muon_b200_ns_run(ws_ptr[i % 2], e - s, m_, n_, ns_mode, steps, None, eps,
+                                               ctypes.byref(slot), main.cuda_stream))
+                    ns_done = torch.cuda.Event()
+                    ns_done.record(main)
+                    side.wait_event(ns_done)
+                    u = ws_ptr[i % 2] + (l.x_offset_bytes if slot.value == 0 else l.c_offset_bytes)
+                    self._epilogue(params[s:e], peer_ptrs, rows, cols, code, u, l, tall, lr, weight_decay, scale,
+                                   side.cuda_stream)  # the update kernel also writes the peers' copies
+                    if after_group is not None:
+                        done = torch.cuda.Event()
+                        done.record(side)
+                        after_group(params[s:e], done)
                 p_done = next_p
                 self.launch_groups += 1
             main.wait_stream(side)

@@ -47,6 +47,69 @@ def _worker(rank, world, tmpdir, exchange, dtype):
         dist.destroy_process_group()
 
 
+def _worker_overlap(rank, world, tmpdir, exchange):
+    """Three steps of `MuonWithAuxAdam` driven by StepInBackward: updates and pushes start inside
+    the backward pass, one parameter gets no gradient in the second step."""
+    import datetime
+    os.environ["MUON_B200_EXCHANGE"] = exchange
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", init_method=f"file://{tmpdir}/pg_ov_{exchange}", rank=rank,
+                            world_size=world, timeout=datetime.timedelta(seconds=60))
+    try:
+        import muon_b200 as mb
+        dev = torch.device("cuda", rank)
+        p0, _ = _problem()
+        g = torch.Generator().manual_seed(6)
+        weights = [[torch.randn(s, generator=g) for s in SHAPES] for _ in range(3)]
+        params = [torch.nn.Parameter(p.to(dev)) for p in p0]
+        gain = torch.nn.Parameter(torch.ones(64, device=dev))
+        opt = mb.MuonWithAuxAdam([dict(params=list(params), use_muon=True, lr=0.02, weight_decay=0.01),
+                                  dict(params=[gain], use_muon=False, lr=1e-3)])
+        overlap = mb.StepInBackward(opt)
+        for step, w in enumerate(weights):
+            skip = 2 if step == 1 else -1
+            for q in params + [gain]:
+                q.grad = None
+            loss = sum((p * wi.to(dev)).sum() for i, (p, wi) in enumerate(zip(params, w)) if i != skip) * gain.sum()
+            loss.backward()
+            overlap.step()
+        torch.cuda.synchronize()
+        overlap.remove()
+        torch.save(dict(params=[p.detach().cpu() for p in params], gain=gain.detach().cpu(),
+                        status=mb.device_status()), f"{tmpdir}/ov_{exchange}_{rank}.pt")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("exchange", ["st", "ce"])
+def test_step_in_backward_on_a_distributed_optimizer(tmp_path, exchange):
+    """Every rank ends with the parameters a single GPU gets from the plain optimizer step."""
+    world = min(torch.cuda.device_count(), 4)
+    mp.spawn(_worker_overlap, args=(world, str(tmp_path), exchange), nprocs=world, join=True)
+    outs = [torch.load(f"{tmp_path}/ov_{exchange}_{r}.pt", weights_only=False) for r in range(world)]
+
+    import muon_b200 as mb
+    p0, _ = _problem()
+    g = torch.Generator().manual_seed(6)
+    weights = [[torch.randn(s, generator=g) for s in SHAPES] for _ in range(3)]
+    params = [torch.nn.Parameter(p.cuda()) for p in p0]
+    gain = torch.nn.Parameter(torch.ones(64, device="cuda"))
+    opt = mb.SingleDeviceMuonWithAuxAdam([dict(params=list(params), use_muon=True, lr=0.02, weight_decay=0.01),
+                                          dict(params=[gain], use_muon=False, lr=1e-3)])
+    for step, w in enumerate(weights):
+        skip = 2 if step == 1 else -1
+        for q in params + [gain]:
+            q.grad = None
+        loss = sum((p * wi.cuda()).sum() for i, (p, wi) in enumerate(zip(params, w)) if i != skip) * gain.sum()
+        loss.backward()
+        opt.step()
+    for r, o in enumerate(outs):
+        assert o["status"] == 0
+        assert torch.equal(o["gain"], gain.detach().cpu())
+        for i, (p, q) in enumerate(zip(o["params"], params)):
+            assert torch.equal(p, q.detach().cpu()), f"rank {r}, parameter {i} ({exchange})"
+
+
 @pytest.mark.parametrize("exchange", ["st", "ce", "nccl"])
 @pytest.mark.parametrize("dtype", [torch.bfloat16])
 def test_distributed_step_matches_single_device(tmp_path, exchange, dtype):

@@ -327,6 +327,26 @@ def test_single_device_muon_mixed_shapes(mb, dtype):
         assert orc.rel_fro(p.detach().cpu(), r) <= tol, p.shape
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_update_fused_into_the_last_gemm_on_ragged_shapes(mb, dtype):
+    """The last GEMM of the iteration applies the update itself for bf16 parameters of either
+    orientation and for wide fp32 ones (muon_b200_ns_run_update). Shapes whose tiles have partial
+    32 x 32 blocks on both edges, next to shapes the fusion must leave to the update kernel (tall
+    fp32, rows that are not 16-byte multiples): all against the oracle, and the epilogue kernel is
+    launched only for the ones that cannot be fused."""
+    shapes = [(200, 328), (328, 200), (72, 136), (136, 72), (100, 250), (40, 24, 3, 3)]
+    fusable = {torch.float32: [True, False, True, False, False, True],
+               torch.bfloat16: [True, True, True, True, False, True]}[dtype]
+    hyper = dict(lr=0.02, weight_decay=0.01, momentum=0.95)
+    before = dict(mb._lib.launch_counts())
+    params, ref_p, _, _ = _run_single_device(mb, shapes, dtype, 1, hyper, seed=23)
+    after = mb._lib.launch_counts()
+    assert after["epilogue"] - before["epilogue"] == fusable.count(False)
+    tol = 1e-3 if dtype == torch.float32 else 4e-3
+    for p, r in zip(params, ref_p):
+        assert orc.rel_fro(p.detach().cpu(), r) <= tol, p.shape
+
+
 def test_grad_none_becomes_zero_and_state_keys(mb):
     p = torch.nn.Parameter(torch.randn(64, 96, device=DEV))
     before = p.detach().clone()
