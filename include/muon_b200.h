@@ -191,7 +191,7 @@ int muon_b200_ns_run(void* workspace, int batch, int64_t m, int64_t n, int mode,
  * itself where that is possible: its epilogue reads the parameter, applies
  * p = p*(1 - lr*wd) - lr * bf16(U*scale) with the roundings of muon_b200_epilogue and writes the
  * parameter back, so the orthogonalised matrix never goes to memory. Fused for bfloat16 parameters
- * of either orientation and for float32 parameters with rows <= cols, up to 32 per call, rows a
+ * of either orientation and for float32 parameters with rows <= cols, up to 64 per call, rows a
  * multiple of 16 bytes; otherwise the iteration is followed by the epilogue kernel on the same
  * stream. rows, cols, dtype, lr, weight_decay, scale as for muon_b200_epilogue; the workspace is
  * laid out for (count, min(rows, cols), max(rows, cols), mode). Replaces muon.py:13-14 and :66-67

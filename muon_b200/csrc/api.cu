@@ -246,7 +246,7 @@ int muon_b200_ns_run_update(void* workspace, int mode, int steps, const float* c
   upd.neg_lr = (float)(-lr);
   if (update_fusable(upd, count))
     return ns_iterate_replayed(buf, count, m, n, mode, steps, coeffs, eps, as_stream(stream), nullptr, &upd);
-  // Not fusable (tall fp32 parameters, more than 32 of them, rows that are not 16-byte multiples):
+  // Not fusable (tall fp32 parameters, more than 64 of them, rows that are not 16-byte multiples):
   // the iteration, then the update kernel on the same stream.
   int slot = 0;
   rc = ns_iterate_replayed(buf, count, m, n, mode, steps, coeffs, eps, as_stream(stream), &slot);

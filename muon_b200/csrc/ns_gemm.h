@@ -31,7 +31,7 @@ enum Variant : int {
   V_UPD_F32 = 5,     // ... to fp32 parameters of the tile's orientation
 };
 
-constexpr int kMaxUpdateTensors = 32;  // parameters one fused-update launch can address
+constexpr int kMaxUpdateTensors = 64;  // parameters one fused-update launch can address
 
 // The update epilogue (reference muon.py:14 and :66-67) done by the last line 3 itself:
 //   p = T(T(p * decay) + neg_lr * bf16(U * scale))

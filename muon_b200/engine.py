@@ -245,74 +245,112 @@ class CudaBackend:
     def muon_step(self, params: Sequence[Tensor], grads: Sequence[Tensor], moms: Sequence[Tensor],
                   lr: float, weight_decay: float, beta: float, nesterov: bool = True,
                   after_group=None, max_group: int | None = None, peer_ptrs=None) -> None:
-        """prologue -> Newton-Schulz -> epilogue for same-shape, same-dtype parameters.
+        """prologue -> Newton-Schulz -> update for same-shape, same-dtype parameters (one set of
+        `muon_step_sets`)."""
+        self.muon_step_sets([(params, grads, moms)], lr, weight_decay, beta, nesterov, after_group,
+                            max_group=max_group, peer_ptrs=peer_ptrs)
 
-        The parameters are processed in launch groups (see plan_launches), at most `max_group`
-        per group when given. `after_group(params_of_group, event)` is called once the update of
-        a group has been enqueued; `event` completes when those parameters hold their new values.
-        `peer_ptrs(param)` (optional) returns the addresses of that parameter's copies in other
-        GPUs' memory; the epilogue kernel then stores every new value there as well."""
-        p0 = params[0]
-        rows, cols = view_2d(p0.shape)
-        code = dtype_code(p0)
-        for p, g, m in zip(params, grads, moms):
-            _require_cuda(p, "parameter")
-            if p.shape != p0.shape or p.dtype != p0.dtype or g.dtype != p0.dtype or m.dtype != p0.dtype:
-                raise ValueError("muon_step needs tensors of one shape and one dtype")
-            if not (p.is_contiguous() and g.is_contiguous() and m.is_contiguous()):
-                raise ValueError("muon_step needs contiguous parameter, gradient and momentum")
-        m_, n_ = min(rows, cols), max(rows, cols)
-        scale = aspect_scale(p0.shape)
+    def muon_step_sets(self, sets, lr: float, weight_decay: float, beta: float, nesterov: bool = True,
+                       after_group=None, max_group: int | None = None, halve_groups: bool = False,
+                       peer_ptrs=None) -> None:
+        """prologue -> Newton-Schulz -> update for several sets of parameters, each set of one
+        shape and dtype: `sets` is a list of (params, grads, moms).
+
+        Every set is cut into launch groups (see plan_launches; at most `max_group` members per
+        group when given, at most half of the set with `halve_groups`), and all groups of all sets
+        go through ONE pipeline: the prologue of group i+1 (and, where the update is a kernel of
+        its own, the update of group i-1) run on a side stream beside the GEMMs of group i, also
+        across the boundary between two sets. `after_group(params_of_group, event)` is called
+        once the update of a group has been enqueued; `event` completes when those parameters hold
+        their new values. `peer_ptrs(param)` (optional) returns the addresses of that parameter's
+        copies in other GPUs' memory; the update kernel then stores every new value there as well."""
         mode, steps = _ns_mode, _ns_steps
-        eps = 1e-7
-        sizes = plan_launches(m_, n_, len(params), self.workspace_cap_bytes, self._sm_pairs(p0.device))
-        if _grad_ready and len(params) > 1 and grads[0].data_ptr() in _grad_ready:
-            # The gradients are still arriving (copied in or reduced on another stream): start with
-            # small groups, so that the first kernels only wait for the first arrivals.
-            sizes = ramped_sizes(sizes)
-        if max_group is not None and max(sizes) > max_group:
-            launches = -(-len(params) // max(1, max_group))
-            cuts = [round(i * len(params) / launches) for i in range(launches + 1)]
-            sizes = [e - s for s, e in zip(cuts[:-1], cuts[1:])]
-        bounds = [0]
-        for b in sizes:
-            bounds.append(bounds[-1] + b)
-        dev = p0.device
-        if self.overlap_elementwise and len(sizes) >= 2:
-            self._muon_step_pipelined(params, grads, moms, bounds, rows, cols, code, lr, weight_decay,
-                                      beta, nesterov, scale, mode, steps, eps, after_group, peer_ptrs)
+        jobs = []
+        for params, grads, moms in sets:
+            if not params:
+                continue
+            p0 = params[0]
+            rows, cols = view_2d(p0.shape)
+            code = dtype_code(p0)
+            for p, g, m in zip(params, grads, moms):
+                _require_cuda(p, "parameter")
+                if p.shape != p0.shape or p.dtype != p0.dtype or g.dtype != p0.dtype or m.dtype != p0.dtype:
+                    raise ValueError("muon_step needs tensors of one shape and one dtype")
+                if not (p.is_contiguous() and g.is_contiguous() and m.is_contiguous()):
+                    raise ValueError("muon_step needs contiguous parameter, gradient and momentum")
+                if p.device != sets[0][0][0].device:
+                    raise ValueError("muon_step_sets needs all parameters on one device")
+            m_, n_ = min(rows, cols), max(rows, cols)
+            sizes = plan_launches(m_, n_, len(params), self.workspace_cap_bytes, self._sm_pairs(p0.device))
+            if _grad_ready and len(params) > 1 and grads[0].data_ptr() in _grad_ready:
+                # The gradients are still arriving (copied in or reduced on another stream): start
+                # with small groups, so that the first kernels only wait for the first arrivals.
+                sizes = ramped_sizes(sizes)
+            cap = max_group
+            if halve_groups:
+                half = max(1, -(-len(params) // 2))
+                cap = half if cap is None else min(cap, half)
+            if cap is not None and max(sizes) > cap:
+                launches = -(-len(params) // max(1, cap))
+                cuts = [round(i * len(params) / launches) for i in range(launches + 1)]
+                sizes = [e - s for s, e in zip(cuts[:-1], cuts[1:])]
+            start = 0
+            for b in sizes:
+                sl = slice(start, start + b)
+                jobs.append(dict(params=params[sl], grads=grads[sl], moms=moms[sl], rows=rows, cols=cols,
+                                 code=code, m=m_, n=n_, tall=rows > cols, scale=aspect_scale(p0.shape),
+                                 layout=_lib.ns_layout(b, m_, n_, _NS_MODES[mode])))
+                start += b
+        if not jobs:
             return
-        tall = rows > cols
+        dev = jobs[0]["params"][0].device
+        hyper = dict(lr=lr, weight_decay=weight_decay, beta=beta, nesterov=nesterov, mode=_NS_MODES[mode],
+                     steps=steps, eps=1e-7)
+        if self.overlap_elementwise and len(jobs) >= 2:
+            self._run_jobs_pipelined(dev, jobs, hyper, after_group, peer_ptrs)
+        else:
+            self._run_jobs_serial(dev, jobs, hyper, after_group, peer_ptrs)
+
+    def _run_jobs_serial(self, dev, jobs, hyper, after_group, peer_ptrs) -> None:
         with torch.cuda.device(dev):
-            stream = _stream_ptr(dev)
-            for s, e in zip(bounds[:-1], bounds[1:]):
-                layout = _lib.ns_layout(e - s, m_, n_, _NS_MODES[mode])
+            current = torch.cuda.current_stream(dev)
+            stream = current.cuda_stream
+            for job in jobs:
+                layout = job["layout"]
                 ws = self.workspace(dev, layout.total_bytes)
                 wptr = self._aligned_ptr(ws)
-                _wait_grads(torch.cuda.current_stream(dev), grads[s:e])
+                _wait_grads(current, job["grads"])
+                n = len(job["params"])
                 if peer_ptrs is None:
                     check(lib.muon_b200_muon_step(
-                        ptr_array([p.data_ptr() for p in params[s:e]]),
-                        ptr_array([g.data_ptr() for g in grads[s:e]]),
-                        ptr_array([m.data_ptr() for m in moms[s:e]]),
-                        e - s, rows, cols, code, lr, weight_decay, beta, 1 if nesterov else 0, scale,
-                        _NS_MODES[mode], steps, None, eps, wptr, layout.total_bytes, stream))
+                        ptr_array([p.data_ptr() for p in job["params"]]),
+                        ptr_array([g.data_ptr() for g in job["grads"]]),
+                        ptr_array([m.data_ptr() for m in job["moms"]]),
+                        n, job["rows"], job["cols"], job["code"], hyper["lr"], hyper["weight_decay"], hyper["beta"],
+                        1 if hyper["nesterov"] else 0, job["scale"], hyper["mode"], hyper["steps"], None, hyper["eps"],
+                        wptr, layout.total_bytes, stream))
                 else:
-                    check(lib.muon_b200_prologue(
-                        ptr_array([g.data_ptr() for g in grads[s:e]]), ptr_array([m.data_ptr() for m in moms[s:e]]),
-                        e - s, rows, cols, code, beta, 1 if nesterov else 0, wptr + layout.x_offset_bytes,
-                        layout.ldn, layout.x_bs, 1 if tall else 0, stream))
+                    self._prologue(job, hyper, wptr, stream)
                     slot = ctypes.c_int(0)
-                    check(lib.muon_b200_ns_run(wptr, e - s, m_, n_, _NS_MODES[mode], steps, None, eps,
-                                               ctypes.byref(slot), stream))
+                    check(lib.muon_b200_ns_run(wptr, n, job["m"], job["n"], hyper["mode"], hyper["steps"], None,
+                                               hyper["eps"], ctypes.byref(slot), stream))
                     u = wptr + (layout.x_offset_bytes if slot.value == 0 else layout.c_offset_bytes)
-                    self._epilogue(params[s:e], peer_ptrs, rows, cols, code, u, layout, tall, lr, weight_decay,
-                                   scale, stream)  # the update kernel also writes the peers' copies
+                    # the update kernel also writes the peers' copies
+                    self._epilogue(job["params"], peer_ptrs, job["rows"], job["cols"], job["code"], u, layout,
+                                   job["tall"], hyper["lr"], hyper["weight_decay"], job["scale"], stream)
                 self.launch_groups += 1
                 if after_group is not None:
                     done = torch.cuda.Event()
-                    done.record(torch.cuda.current_stream(dev))
-                    after_group(params[s:e], done)
+                    done.record(current)
+                    after_group(job["params"], done)
+
+    @staticmethod
+    def _prologue(job, hyper, wptr, stream) -> None:
+        layout = job["layout"]
+        check(lib.muon_b200_prologue(
+            ptr_array([g.data_ptr() for g in job["grads"]]), ptr_array([m.data_ptr() for m in job["moms"]]),
+            len(job["params"]), job["rows"], job["cols"], job["code"], hyper["beta"], 1 if hyper["nesterov"] else 0,
+            wptr + layout.x_offset_bytes, layout.ldn, layout.x_bs, 1 if job["tall"] else 0, stream))
 
     @staticmethod
     def _epilogue(plist, peer_ptrs, rows, cols, code, u, layout, tall, lr, weight_decay, scale, stream) -> None:
@@ -329,70 +367,62 @@ class CudaBackend:
                                           layout.ldn, layout.x_bs, 1 if tall else 0, lr, weight_decay, scale,
                                           stream))
 
-    def _muon_step_pipelined(self, params, grads, moms, bounds, rows, cols, code, lr, weight_decay,
-                             beta, nesterov, scale, mode, steps, eps, after_group=None, peer_ptrs=None) -> None:
-        """Same work as the loop over muon_b200_muon_step, with the HBM-bound stages of one launch
-        group running on a side stream while the tensor-bound Newton-Schulz kernels of another
-        group run on the caller's stream. The persistent GEMM CTAs leave registers, threads and
-        ~30 KiB of shared memory free on every SM, so the elementwise CTAs are co-resident.
+    def _run_jobs_pipelined(self, dev, jobs, hyper, after_group=None, peer_ptrs=None) -> None:
+        """The HBM-bound stages of one launch group run on a side stream while the tensor-bound
+        Newton-Schulz kernels of another group run on the caller's stream. The persistent GEMM CTAs
+        leave registers, threads and ~30 KiB of shared memory free on every SM, so the elementwise
+        CTAs are co-resident.
 
-        Side stream:  P(0) | for i: P(i+1), wait NS(i), E(i)        (two workspaces, i % 2)
-        Main stream:        for i: wait P(i), NS(i)                  then waits for the side stream
+        Side stream:  P(0) | for i: P(i+1), [wait NS(i), E(i)]       (two workspaces, i % 2)
+        Main stream:        for i: wait P(i), NS(i)                    then waits for the side stream
+        E(i), the update as a kernel of its own, only exists with `peer_ptrs` (it also writes the
+        peers' copies); otherwise the last GEMM of NS(i) applies the update itself.
         """
-        dev = params[0].device
-        tall = rows > cols
-        m_, n_ = min(rows, cols), max(rows, cols)
-        groups = list(zip(bounds[:-1], bounds[1:]))
         with torch.cuda.device(dev):
             main = torch.cuda.current_stream(dev)
             side = self._side_stream(dev)
-            layouts = [_lib.ns_layout(e - s, m_, n_, _NS_MODES[mode]) for s, e in groups]
-            ws_ptr = [self._aligned_ptr(self.workspace(dev, max(l.total_bytes for l in layouts), slot))
-                      for slot in (0, 1)]
+            biggest = max(job["layout"].total_bytes for job in jobs)
+            ws_ptr = [self._aligned_ptr(self.workspace(dev, biggest, slot)) for slot in (0, 1)]
             side.wait_stream(main)  # gradients and parameters are ready in main-stream order
-            ns_mode = _NS_MODES[mode]
 
             def prologue(i):
-                s, e = groups[i]
-                l = layouts[i]
-                _wait_grads(side, grads[s:e])
-                check(lib.muon_b200_prologue(
-                    ptr_array([g.data_ptr() for g in grads[s:e]]), ptr_array([m.data_ptr() for m in moms[s:e]]),
-                    e - s, rows, cols, code, beta, 1 if nesterov else 0, ws_ptr[i % 2] + l.x_offset_bytes,
-                    l.ldn, l.x_bs, 1 if tall else 0, side.cuda_stream))
+                _wait_grads(side, jobs[i]["grads"])
+                self._prologue(jobs[i], hyper, ws_ptr[i % 2], side.cuda_stream)
                 ev = torch.cuda.Event()
                 ev.record(side)
                 return ev
 
             p_done = prologue(0)
-            for i, (s, e) in enumerate(groups):
-                l = layouts[i]
-                next_p = prologue(i + 1) if i + 1 < len(groups) else None
+            for i, job in enumerate(jobs):
+                l, n = job["layout"], len(job["params"])
+                next_p = prologue(i + 1) if i + 1 < len(jobs) else None
                 main.wait_event(p_done)
                 if peer_ptrs is None:
                     # the last GEMM of the iteration applies the update itself (where it can)
                     check(lib.muon_b200_ns_run_update(
-                        ws_ptr[i % 2], ns_mode, steps, None, eps, ptr_array([p.data_ptr() for p in params[s:e]]),
-                        e - s, rows, cols, code, lr, weight_decay, scale, main.cuda_stream))
+                        ws_ptr[i % 2], hyper["mode"], hyper["steps"], None, hyper["eps"],
+                        ptr_array([p.data_ptr() for p in job["params"]]), n, job["rows"], job["cols"], job["code"],
+                        hyper["lr"], hyper["weight_decay"], job["scale"], main.cuda_stream))
                     ns_done = torch.cuda.Event()
                     ns_done.record(main)
                     side.wait_event(ns_done)  # the next prologue but one reuses this workspace
                     if after_group is not None:
-                        after_group(params[s:e], ns_done)
+                        after_group(job["params"], ns_done)
                 else:
                     slot = ctypes.c_int(0)
-                    check(lib.muon_b200_ns_run(ws_ptr[i % 2], e - s, m_, n_, ns_mode, steps, None, eps,
-                                               ctypes.byref(slot), main.cuda_stream))
+                    check(lib.muon_b200_ns_run(ws_ptr[i % 2], n, job["m"], job["n"], hyper["mode"], hyper["steps"],
+                                               None, hyper["eps"], ctypes.byref(slot), main.cuda_stream))
                     ns_done = torch.cuda.Event()
                     ns_done.record(main)
                     side.wait_event(ns_done)
                     u = ws_ptr[i % 2] + (l.x_offset_bytes if slot.value == 0 else l.c_offset_bytes)
-                    self._epilogue(params[s:e], peer_ptrs, rows, cols, code, u, l, tall, lr, weight_decay, scale,
-                                   side.cuda_stream)  # the update kernel also writes the peers' copies
+                    # the update kernel also writes the peers' copies
+                    self._epilogue(job["params"], peer_ptrs, job["rows"], job["cols"], job["code"], u, l, job["tall"],
+                                   hyper["lr"], hyper["weight_decay"], job["scale"], side.cuda_stream)
                     if after_group is not None:
                         done = torch.cuda.Event()
                         done.record(side)
-                        after_group(params[s:e], done)
+                        after_group(job["params"], done)
                 p_done = next_p
                 self.launch_groups += 1
             main.wait_stream(side)

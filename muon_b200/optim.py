@@ -43,14 +43,21 @@ def _bucket_by_shape(params):
 
 
 def _muon_update_params(optimizer, params, group, **step_options) -> None:
-    """Body of the reference's per-parameter loop (muon.py:91-99) for a list of parameters."""
+    """Body of the reference's per-parameter loop (muon.py:91-99) for a list of parameters: same-shape
+    parameters form a set, and all sets go to the engine in one call, which runs one pipeline of
+    grouped launches over them."""
     backend = get_backend()
     for p in params:
         _ensure_grad_and_state(optimizer, p)
-    for plist in _bucket_by_shape(params).values():
-        backend.muon_step(plist, [p.grad for p in plist],
-                          [optimizer.state[p]["momentum_buffer"] for p in plist],
-                          group["lr"], group["weight_decay"], group["momentum"], **step_options)
+    sets = [(plist, [p.grad for p in plist], [optimizer.state[p]["momentum_buffer"] for p in plist])
+            for plist in _bucket_by_shape(params).values()]
+    if hasattr(backend, "muon_step_sets"):
+        backend.muon_step_sets(sets, group["lr"], group["weight_decay"], group["momentum"], **step_options)
+        return
+    step_options.pop("halve_groups", None)
+    for plist, grads, moms in sets:
+        backend.muon_step(plist, grads, moms, group["lr"], group["weight_decay"], group["momentum"],
+                          **step_options)
 
 
 def _adam_update_params(optimizer, group) -> None:
@@ -137,13 +144,11 @@ def _distributed_muon_group_step(optimizer, group) -> None:
         # gained in overlap.)
         mine = [params[i] for i in owned]
         push.begin_step()
-        for plist in _bucket_by_shape(mine).values():
-            if push.mode == "st":
-                # The epilogue kernel stores into the peer copies itself: nothing to enqueue afterwards.
-                _muon_update_params(optimizer, plist, group, peer_ptrs=push.peer_ptrs)
-            else:
-                cap = max(1, -(-len(plist) // 2)) if world >= 4 else None
-                _muon_update_params(optimizer, plist, group, after_group=push.push, max_group=cap)
+        if push.mode == "st":
+            # The update kernel stores into the peer copies itself: nothing to enqueue afterwards.
+            _muon_update_params(optimizer, mine, group, peer_ptrs=push.peer_ptrs)
+        else:
+            _muon_update_params(optimizer, mine, group, after_group=push.push, halve_groups=world >= 4)
         push.end_step()
         return
     for base_i in range(0, len(params), world):

@@ -205,6 +205,27 @@ def test_one_llama3_8b_layer_through_the_optimizer(mb, dtype):
             assert ((mom - m.float()).abs() <= m.float().abs() * 2 ** -7 + 1e-12).all()
 
 
+def test_llama3_70b_shapes_through_the_optimizer(mb):
+    """The Llama-3-70B shapes whose oracle run stays within seconds (q 8192 x 8192; k, v
+    1024 x 8192), bf16, one step of SingleDeviceMuon against the oracle's per-parameter step:
+    parameters <= 4e-3 (bf16 parameters carry 2^-9 rounding themselves), momentum to one bf16
+    ulp. The gate/up/down shapes (28672 x 8192 and its transpose) are covered by the property test
+    above: their oracle run takes minutes."""
+    shapes = [(8192, 8192), (1024, 8192), (1024, 8192)]
+    g = torch.Generator().manual_seed(4300)
+    p0 = [(torch.randn(s, generator=g) * 0.02).bfloat16() for s in shapes]
+    params = [torch.nn.Parameter(p.clone().to(DEV)) for p in p0]
+    opt = mb.SingleDeviceMuon(params, lr=0.02, weight_decay=0.01, momentum=0.95)
+    ref_p = [p.clone() for p in p0]
+    ref_m = [torch.zeros_like(p) for p in p0]
+    grads = [(torch.randn(s, generator=g) * 1e-3).bfloat16() for s in shapes]
+    _step_both(mb, opt, params, ref_p, ref_m, grads, 0.02, 0.01)
+    for p, r, m in zip(params, ref_p, ref_m):
+        assert orc.rel_fro(p.detach().cpu(), r) <= 4e-3, tuple(p.shape)
+        mom = opt.state[p]["momentum_buffer"].cpu().float()
+        assert ((mom - m.float()).abs() <= m.float().abs() * 2 ** -7 + 1e-12).all()
+
+
 def test_gradients_arriving_on_a_copy_stream(mb):
     """Gradients copied in from pinned host memory on a side stream and marked with
     mark_grad_ready: step() called at once from the main stream gives bitwise the result of a step
