@@ -170,11 +170,16 @@ typedef struct muon_b200_ns_layout {
   /* MUON_B200_NS_AOL4_FP8 only (0 otherwise): the e4m3 copies of X ([batch, m, ld8n] bytes) and of
    * A - I ([batch, m, ld8m] bytes) that the iteration keeps beside the bf16 matrices */
   int64_t x8_offset_bytes, e8_offset_bytes, ld8n, ld8m;
+  /* MUON_B200_NS_CLASSIC5 only (0 otherwise): sumsq_bs floats per matrix, starting at
+   * sumsq_offset_bytes, for the sums of squares that muon_b200_prologue_sumsq leaves */
+  int64_t sumsq_offset_bytes, sumsq_bs;
 } muon_b200_ns_layout;
 
-/* Layout for MUON_B200_NS_AOL4 / MUON_B200_NS_CLASSIC5 (they need the same workspace). */
+/* Layout for MUON_B200_NS_AOL4; also enough for MUON_B200_NS_CLASSIC5 without
+ * MUON_B200_NS_HAVE_SUMSQ. */
 int muon_b200_ns_workspace_layout(int batch, int64_t m, int64_t n, muon_b200_ns_layout* out);
-/* Layout for a given mode: MUON_B200_NS_AOL4_FP8 needs about a quarter more. */
+/* Layout for a given mode: MUON_B200_NS_AOL4_FP8 needs about a quarter more, MUON_B200_NS_CLASSIC5
+ * a few floats per 64 x 64 elements more (the sumsq area). */
 int muon_b200_ns_workspace_layout_mode(int batch, int64_t m, int64_t n, int mode, muon_b200_ns_layout* out);
 
 /* Orthogonalises the `batch` matrices already stored (bf16, m x n, m <= n) in slot X of
@@ -185,6 +190,14 @@ int muon_b200_ns_workspace_layout_mode(int batch, int64_t m, int64_t n, int mode
  * Replaces zeropower_via_newtonschulz5 (muon.py:748-799) from line 778 on. */
 int muon_b200_ns_run(void* workspace, int batch, int64_t m, int64_t n, int mode, int steps,
                      const float* coeffs, float eps, int* result_slot, muon_b200_stream_t stream);
+
+/* Flag to OR into `mode` (MUON_B200_NS_CLASSIC5 only) of muon_b200_ns_run and
+ * muon_b200_ns_run_update: the X in the workspace was written by muon_b200_prologue_sumsq together
+ * with its sums of squares (into the sumsq area of a workspace laid out for the classic mode), so
+ * the Frobenius norm of muon.py:282 is taken from those instead of from another pass over X. In
+ * either case X is not divided by its norm in memory: the first Gram product and the first
+ * line 3 multiply their outputs by 1/(||X|| + eps)^2 and 1/(||X|| + eps). */
+#define MUON_B200_NS_HAVE_SUMSQ 0x100
 
 /* muon_b200_ns_run followed by the update epilogue (muon_b200_epilogue) of the `count` parameters
  * whose bf16 matrices the workspace holds, with the update done by the last GEMM of the iteration
@@ -264,6 +277,17 @@ int64_t muon_b200_ns_static_required_bytes(int batch, int64_t m, int64_t n);
 int muon_b200_prologue(void* const* grads, void* const* moms, int count, int64_t rows,
                        int64_t cols, int dtype, double beta, int nesterov, void* x, int64_t ldx,
                        int64_t x_bs, int transpose_out, muon_b200_stream_t stream);
+
+/* muon_b200_prologue that also sums the squares of the bf16 values it writes (the Frobenius norm of
+ * the classic iteration, muon.py:282, fused into the pass that produces X): sumsq receives, for
+ * tensor i, sumsq_bs floats at sumsq + i * sumsq_bs whose sum is ||X_i||_F^2 (one per tile of the
+ * kernel, the rest zero). sumsq = NULL: plain muon_b200_prologue. For a workspace laid out with
+ * muon_b200_ns_workspace_layout_mode(..., MUON_B200_NS_CLASSIC5, &l): sumsq = workspace +
+ * l.sumsq_offset_bytes, sumsq_bs = l.sumsq_bs, then run with MUON_B200_NS_HAVE_SUMSQ. */
+int muon_b200_prologue_sumsq(void* const* grads, void* const* moms, int count, int64_t rows,
+                             int64_t cols, int dtype, double beta, int nesterov, void* x, int64_t ldx,
+                             int64_t x_bs, int transpose_out, float* sumsq, int64_t sumsq_bs,
+                             muon_b200_stream_t stream);
 
 /* Update epilogue, in place on params (muon.py:14 and :66-67):
  * p = p*(1 - lr*wd) - lr * bf16(U*scale). U of tensor i is at u + i*u_bs, pitch ldu, and is

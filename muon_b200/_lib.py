@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_PKG_DIR, "libmuon_b200.so")
 
 F32, BF16, F16, F64 = 0, 1, 2, 3
 NS_AOL4, NS_CLASSIC5, NS_AOL4_FP8 = 0, 1, 2
+NS_HAVE_SUMSQ = 0x100  # MUON_B200_NS_HAVE_SUMSQ
 
 ERR_NAMES = {
     -1: "INVALID_ARG",
@@ -36,7 +37,7 @@ class NsLayout(ctypes.Structure):
     _fields_ = [(name, c_int64) for name in (
         "total_bytes", "x_offset_bytes", "c_offset_bytes", "a_offset_bytes", "b_offset_bytes",
         "partials_offset_bytes", "ldn", "x_bs", "ldm", "a_bs", "x8_offset_bytes", "e8_offset_bytes",
-        "ld8n", "ld8m")]
+        "ld8n", "ld8m", "sumsq_offset_bytes", "sumsq_bs")]
 
 
 # name -> (restype, argtypes); mirrors include/muon_b200.h one to one.
@@ -85,6 +86,9 @@ PROTOTYPES = {
     "muon_b200_prologue": (c_int, [POINTER(c_void_p), POINTER(c_void_p), c_int, c_int64, c_int64,
                                    c_int, c_double, c_int, c_void_p, c_int64, c_int64, c_int,
                                    c_void_p]),
+    "muon_b200_prologue_sumsq": (c_int, [POINTER(c_void_p), POINTER(c_void_p), c_int, c_int64, c_int64,
+                                         c_int, c_double, c_int, c_void_p, c_int64, c_int64, c_int,
+                                         c_void_p, c_int64, c_void_p]),
     "muon_b200_epilogue": (c_int, [POINTER(c_void_p), c_int, c_int64, c_int64, c_int, c_void_p,
                                    c_int64, c_int64, c_int, c_double, c_double, c_double, c_void_p]),
     "muon_b200_epilogue_push": (c_int, [POINTER(c_void_p), POINTER(c_void_p), c_int, c_int, c_int64, c_int64,

@@ -168,6 +168,12 @@ int muon_b200_ns_workspace_layout_mode(int batch, int64_t m, int64_t n, int mode
     l.e8_offset_bytes = l.x8_offset_bytes + round_up(batch * m * l.ld8n, 256);
     l.total_bytes += ns_fp8_extra_bytes(batch, m, n);
   }
+  l.sumsq_offset_bytes = l.sumsq_bs = 0;
+  if (mode == MUON_B200_NS_CLASSIC5) {
+    l.sumsq_offset_bytes = l.total_bytes;
+    l.sumsq_bs = classic_tiles_max(m, n);
+    l.total_bytes += ns_classic_extra_bytes(batch, m, n);
+  }
   *out = l;
   return OK;
 }
@@ -204,19 +210,42 @@ int workspace_buffers(void* workspace, int batch, int64_t m, int64_t n, int mode
   buf.a_bs = l.a_bs;
   buf.fscratch = reinterpret_cast<float*>(ws + l.partials_offset_bytes);
   buf.f_bs = l.ldm;
+  buf.fro_scales = fro_scales_in(buf.fscratch, batch, l.ldm);
   *out = buf;
   if (layout) *layout = l;
   return OK;
 }
 }  // namespace
 
+namespace {
+// MUON_B200_NS_HAVE_SUMSQ: takes the flag off `mode`; with it, points the buffers at the per-tile
+// sums of squares that muon_b200_prologue_sumsq left in the workspace.
+int take_sumsq_flag(int* mode, bool* have) {
+  *have = (*mode & MUON_B200_NS_HAVE_SUMSQ) != 0;
+  *mode &= ~MUON_B200_NS_HAVE_SUMSQ;
+  if (*have && *mode != MUON_B200_NS_CLASSIC5)
+    return set_error(ERR_INVALID_ARG, "MUON_B200_NS_HAVE_SUMSQ goes with MUON_B200_NS_CLASSIC5 only");
+  return OK;
+}
+void use_tile_sumsq(void* workspace, const muon_b200_ns_layout& l, NsBuffers* buf) {
+  buf->tile_sumsq = reinterpret_cast<const float*>(static_cast<char*>(workspace) + l.sumsq_offset_bytes);
+  buf->tile_bs = l.sumsq_bs;
+  buf->tile_count = l.sumsq_bs;  // the prologue entry point zeroed what its kernel does not write
+}
+}  // namespace
+
 int muon_b200_ns_run(void* workspace, int batch, int64_t m, int64_t n, int mode, int steps,
                      const float* coeffs, float eps, int* result_slot, muon_b200_stream_t stream) {
-  int rc = ns_check_mode(mode, &steps, coeffs);
+  bool have_sumsq = false;
+  int rc = take_sumsq_flag(&mode, &have_sumsq);
+  if (rc != OK) return rc;
+  rc = ns_check_mode(mode, &steps, coeffs);
   if (rc != OK) return rc;
   NsBuffers buf;
-  rc = workspace_buffers(workspace, batch, m, n, mode, &buf, nullptr);
+  muon_b200_ns_layout l;
+  rc = workspace_buffers(workspace, batch, m, n, mode, &buf, &l);
   if (rc != OK) return rc;
+  if (have_sumsq) use_tile_sumsq(workspace, l, &buf);
   return ns_iterate_replayed(buf, batch, m, n, mode, steps, coeffs, eps, as_stream(stream), result_slot);
 }
 
@@ -228,6 +257,9 @@ int muon_b200_ns_run_update(void* workspace, int mode, int steps, const float* c
   if (!params) return set_error(ERR_INVALID_ARG, "ns_run_update: params is NULL");
   if (count < 1 || rows < 1 || cols < 1)
     return set_error(ERR_INVALID_ARG, "ns_run_update needs count, rows, cols >= 1");
+  bool have_sumsq = false;
+  rc = take_sumsq_flag(&mode, &have_sumsq);
+  if (rc != OK) return rc;
   rc = ns_check_mode(mode, &steps, coeffs);
   if (rc != OK) return rc;
   const bool tall = rows > cols;
@@ -236,6 +268,7 @@ int muon_b200_ns_run_update(void* workspace, int mode, int steps, const float* c
   muon_b200_ns_layout l;
   rc = workspace_buffers(workspace, count, m, n, mode, &buf, &l);
   if (rc != OK) return rc;
+  if (have_sumsq) use_tile_sumsq(workspace, l, &buf);
   UpdateSpec upd;
   upd.param = params;
   upd.dtype = dtype;
@@ -244,7 +277,8 @@ int muon_b200_ns_run_update(void* workspace, int mode, int steps, const float* c
   upd.scale = (float)scale;
   upd.decay = (float)(1.0 - lr * weight_decay);
   upd.neg_lr = (float)(-lr);
-  if (update_fusable(upd, count))
+  // (a one-step classic iteration: its only line 3 carries the normalisation factor instead)
+  if (update_fusable(upd, count) && !(mode == MUON_B200_NS_CLASSIC5 && steps == 1))
     return ns_iterate_replayed(buf, count, m, n, mode, steps, coeffs, eps, as_stream(stream), nullptr, &upd);
   // Not fusable (tall fp32 parameters, more than 64 of them, rows that are not 16-byte multiples):
   // the iteration, then the update kernel on the same stream.
@@ -301,6 +335,14 @@ int muon_b200_cast_bf16(const void* src, int dtype, int64_t rows, int64_t cols, 
 int muon_b200_prologue(void* const* grads, void* const* moms, int count, int64_t rows,
                        int64_t cols, int dtype, double beta, int nesterov, void* x, int64_t ldx,
                        int64_t x_bs, int transpose_out, muon_b200_stream_t stream) {
+  return muon_b200_prologue_sumsq(grads, moms, count, rows, cols, dtype, beta, nesterov, x, ldx, x_bs,
+                                  transpose_out, nullptr, 0, stream);
+}
+
+int muon_b200_prologue_sumsq(void* const* grads, void* const* moms, int count, int64_t rows,
+                             int64_t cols, int dtype, double beta, int nesterov, void* x, int64_t ldx,
+                             int64_t x_bs, int transpose_out, float* sumsq, int64_t sumsq_bs,
+                             muon_b200_stream_t stream) {
   int rc = check_dtype(dtype);
   if (rc != OK) return rc;
   if (!grads || !moms || !x) return set_error(ERR_INVALID_ARG, "null pointer passed to prologue");
@@ -311,6 +353,15 @@ int muon_b200_prologue(void* const* grads, void* const* moms, int count, int64_t
   if (ldx < (transpose_out ? rows : cols))
     return set_error(ERR_INVALID_ARG, "prologue X pitch %lld is shorter than a row", (long long)ldx);
   const int vec = dtype == DT_F32 ? 4 : 8;
+  if (sumsq) {
+    const int tiles = prologue_tiles((int)rows, (int)cols, dtype);
+    if (sumsq_bs < tiles)
+      return set_error(ERR_INVALID_ARG, "prologue: %lld sums of squares per tensor, the kernel writes %d",
+                       (long long)sumsq_bs, tiles);
+    // entries past the kernel's tiles count as zero when the sums are added up
+    if (sumsq_bs > tiles)
+      MB_CUDA_CHECK(cudaMemsetAsync(sumsq, 0, sizeof(float) * (size_t)sumsq_bs * count, as_stream(stream)));
+  }
   for (int base = 0; base < count; base += kMaxTensors) {
     const int n = count - base < kMaxTensors ? count - base : kMaxTensors;
     PrologueArgs a{};
@@ -330,6 +381,8 @@ int muon_b200_prologue(void* const* grads, void* const* moms, int count, int64_t
     a.vec_ok = (cols % vec == 0) && all_aligned16(grads + base, n) && all_aligned16(moms + base, n);
     a.w_mom = (float)(1.0 - beta);
     a.beta = (float)beta;
+    a.sumsq = sumsq ? sumsq + (int64_t)base * sumsq_bs : nullptr;
+    a.sumsq_bs = sumsq_bs;
     rc = launch_prologue(a, dtype, transpose_out ? 1 : 0, as_stream(stream));
     if (rc != OK) return rc;
   }
@@ -411,11 +464,16 @@ int muon_b200_muon_step(void* const* params, void* const* grads, void* const* mo
   if (reinterpret_cast<uintptr_t>(workspace) & 255)
     return set_error(ERR_ALIGNMENT, "NS workspace must be 256-byte aligned");
   char* ws = static_cast<char*>(workspace);
-  rc = muon_b200_prologue(grads, moms, count, rows, cols, dtype, beta, nesterov,
-                          ws + l.x_offset_bytes, l.ldn, l.x_bs, tall ? 1 : 0, stream);
+  // classic iteration: the prologue kernel sums the squares of X while it writes it (muon.py:282)
+  const bool classic = ns_mode == MUON_B200_NS_CLASSIC5;
+  rc = muon_b200_prologue_sumsq(grads, moms, count, rows, cols, dtype, beta, nesterov,
+                                ws + l.x_offset_bytes, l.ldn, l.x_bs, tall ? 1 : 0,
+                                classic ? reinterpret_cast<float*>(ws + l.sumsq_offset_bytes) : nullptr,
+                                l.sumsq_bs, stream);
   if (rc != OK) return rc;
-  return muon_b200_ns_run_update(workspace, ns_mode, ns_steps, ns_coeffs, ns_eps, params, count, rows, cols,
-                                 dtype, lr, weight_decay, scale, stream);
+  return muon_b200_ns_run_update(workspace, classic ? (ns_mode | MUON_B200_NS_HAVE_SUMSQ) : ns_mode, ns_steps,
+                                 ns_coeffs, ns_eps, params, count, rows, cols, dtype, lr, weight_decay, scale,
+                                 stream);
 }
 
 int muon_b200_adam(void* const* params, void* const* grads, void* const* exp_avg,

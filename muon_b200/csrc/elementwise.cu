@@ -117,6 +117,10 @@ __device__ __forceinline__ float torch_lerp(float self, float end, float w) {
 //   grad <- lerp(grad, mom, beta)            (Nesterov; written back like lerp_ does)
 //   X    <- bf16(nesterov ? grad : mom), stored [rows, cols] or transposed [cols, rows]
 // A tile is kTileRows x (16 * Vec<T>::N) elements.
+// With a.sumsq the kernel also leaves, per tile, the sum of the squares of the bf16 values it
+// stored (the Frobenius norm of the classic iteration, muon.py:282, taken while X is produced):
+// one float per (tensor, tile), added later in index order, so the norm does not depend on which
+// CTA handled which tile.
 // ---------------------------------------------------------------------------
 template <typename T, bool TRANSPOSE>
 __global__ void __launch_bounds__(kThreads)
@@ -125,6 +129,7 @@ prologue_kernel(const PrologueArgs a) {
   constexpr int kTileCols = 16 * V;
   // Transposition staging: [col][row] with one pad column of 2 bf16 to skew banks.
   __shared__ __nv_bfloat16 tile[TRANSPOSE ? kTileCols : 1][TRANSPOSE ? kTileRows + 2 : 1];
+  __shared__ float warp_ss[2][kThreads / 32];  // two sets taking turns: one barrier per tile
 
   const int tiles_c = (a.cols + kTileCols - 1) / kTileCols;
   const int tiles_r = (a.rows + kTileRows - 1) / kTileRows;
@@ -132,6 +137,7 @@ prologue_kernel(const PrologueArgs a) {
   const long long total = tiles_per * a.count;
   const int tx = threadIdx.x & 15;
   const int ty = threadIdx.x >> 4;
+  int turn = 0;
   griddep_launch_dependents();  // line 1 may set itself up while this kernel drains
   const float w1 = a.w_mom;  // float(1 - beta)
   const float w2 = a.beta;   // float(beta)
@@ -145,6 +151,7 @@ prologue_kernel(const PrologueArgs a) {
     T* m = static_cast<T*>(a.mom[ti]);
     __nv_bfloat16* x = a.x + (long long)ti * a.x_bs;
     const int c0 = tcn * kTileCols + tx * V;
+    float ss = 0.f;  // this thread's share of the tile's sum of squares
 
     const bool full = a.vec_ok && (c0 + V <= a.cols);
 #pragma unroll
@@ -200,6 +207,8 @@ prologue_kernel(const PrologueArgs a) {
             xv[j + 1] = mv[j + 1];
           }
           if (sizeof(T) == 4) round_pair_to<__nv_bfloat16>(xv[j], xv[j + 1]);  // fp32 state -> bf16 X
+          ss = fmaf(xv[j], xv[j], ss);  // elements outside the matrix are zero
+          ss = fmaf(xv[j + 1], xv[j + 1], ss);
         }
         if (full) {
           Vec<T>::store(m + off, mv);
@@ -257,6 +266,19 @@ prologue_kernel(const PrologueArgs a) {
         }
       }
       __syncthreads();
+    }
+    if (a.sumsq) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if ((threadIdx.x & 31) == 0) warp_ss[turn][threadIdx.x >> 5] = ss;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) s += warp_ss[turn][w];
+        a.sumsq[(long long)ti * a.sumsq_bs + rem] = s;
+      }
+      turn ^= 1;
     }
   }
 }
@@ -466,10 +488,13 @@ aol_rescale_kernel(__nv_bfloat16* X, long long ldx, long long x_bs, const __nv_b
 
 // ---------------------------------------------------------------------------
 // Frobenius normalisation of the classic iteration (commented block, muon.py:282):
-//   X = X / (||X||_F + 1e-7), bf16 eager semantics: the norm and the sum are each
-//   rounded to bf16 before the division.
-// Pass 1 writes one partial sum of squares per (matrix, chunk); pass 2 re-adds the
-// partials in a fixed order, so the result does not depend on scheduling.
+//   X = X / (||X||_F + 1e-7), bf16 eager semantics for the denominator: the norm and the sum are
+//   each rounded to bf16.
+// X itself is not rewritten: the factor 1 / (||X|| + eps) of every matrix goes to device memory
+// and the first Gram product and the first line 3 multiply their outputs by its square and by it
+// (V_BATCH_SCALE in the GEMM kernel). The sum of squares comes as partial sums, one per tile from
+// the prologue kernel or one per chunk of rows from sumsq_partial_kernel, and fro_finish_kernel
+// adds them in a fixed order, so the result does not depend on scheduling.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads)
 sumsq_partial_kernel(const __nv_bfloat16* X, long long ldx, long long x_bs, int m, int n, int chunks,
@@ -503,30 +528,26 @@ sumsq_partial_kernel(const __nv_bfloat16* X, long long ldx, long long x_bs, int 
   }
 }
 
+// One block per matrix: partials[b * stride + i], i < count  ->  scales[b] = 1 / (||X_b|| + eps),
+// scales[batch + b] = its square. Thread t adds the partials t, t + 256, ... in that order, then the
+// 256 sums are added pairwise in a fixed tree.
 __global__ void __launch_bounds__(kThreads)
-fro_scale_kernel(__nv_bfloat16* X, long long ldx, long long x_bs, int m, int n, int chunks,
-                 const float* partials, float eps) {
-  __shared__ float s_den;
-  const int b = blockIdx.y, ch = blockIdx.x;
-  if (threadIdx.x == 0) {
-    float s = 0.f;
-    for (int c = 0; c < chunks; ++c) s += partials[(long long)b * chunks + c];
-    s_den = bf16_round(bf16_round(sqrtf(s)) + eps);
-  }
+fro_finish_kernel(const float* partials, long long stride, int count, float eps, float* scales, int batch) {
+  __shared__ float tree[kThreads];
+  const int b = blockIdx.x;
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < count; i += kThreads) acc += partials[(long long)b * stride + i];
+  tree[threadIdx.x] = acc;
   __syncthreads();
-  const float den = s_den;
-  for (int i = ch; i < m; i += chunks) {
-    __nv_bfloat16* xrow = X + (long long)b * x_bs + (long long)i * ldx;
-    const int nv = n & ~7;
-    for (int j = threadIdx.x * 8; j < nv; j += kThreads * 8) {
-      float v[8];
-      Vec<__nv_bfloat16>::load(xrow + j, v);
-#pragma unroll
-      for (int k = 0; k < 8; ++k) v[k] = __fdiv_rn(v[k], den);
-      Vec<__nv_bfloat16>::store(xrow + j, v);
-    }
-    for (int j = nv + threadIdx.x; j < n; j += kThreads)
-      xrow[j] = __float2bfloat16_rn(__fdiv_rn(__bfloat162float(xrow[j]), den));
+  for (int half = kThreads / 2; half > 0; half >>= 1) {
+    if (threadIdx.x < half) tree[threadIdx.x] += tree[threadIdx.x + half];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    const float den = bf16_round(bf16_round(sqrtf(tree[0])) + eps);
+    const float c = __frcp_rn(den);
+    scales[b] = c;
+    scales[batch + b] = c * c;
   }
 }
 
@@ -674,6 +695,11 @@ int adam_elems_per_block(int dtype) {
   return kThreads * (dtype == DT_F32 ? 4 : 8) * 4;
 }
 
+int prologue_tiles(int rows, int cols, int dtype) {
+  const int tile_cols = 16 * (dtype == DT_F32 ? 4 : 8);
+  return ((cols + tile_cols - 1) / tile_cols) * ((rows + kTileRows - 1) / kTileRows);
+}
+
 int launch_prologue(const PrologueArgs& a, int dtype, int transpose, cudaStream_t stream) {
   const int tile_cols = 16 * (dtype == DT_F32 ? 4 : 8);
   long long tiles = (long long)((a.cols + tile_cols - 1) / tile_cols) *
@@ -747,14 +773,18 @@ int launch_aol_rescale(__nv_bfloat16* X, long long ldx, long long x_bs, const __
   return OK;
 }
 
-int launch_fro_normalize(__nv_bfloat16* X, long long ldx, long long x_bs, int m, int n, int batch,
-                         float eps, float* partials, int chunks, cudaStream_t stream) {
-  dim3 grid(chunks, batch);
-  // pass 1 reads X, pass 2 reads and writes it (bf16); accounted as one unit of two launches
-  LaunchScope scope(K_FRO_NORMALIZE, 6.0 * m * (double)n * batch, stream);
-  sumsq_partial_kernel<<<grid, kThreads, 0, stream>>>(X, ldx, x_bs, m, n, chunks, partials);
-  MB_CUDA_CHECK(cudaGetLastError());
-  fro_scale_kernel<<<grid, kThreads, 0, stream>>>(X, ldx, x_bs, m, n, chunks, partials, eps);
+int launch_fro_scales(const __nv_bfloat16* X, long long ldx, long long x_bs, int m, int n, int batch,
+                      float eps, float* partials, int chunks, const float* tile_sumsq, long long tile_bs,
+                      int tile_count, float* scales, cudaStream_t stream) {
+  if (!tile_sumsq) {
+    // nobody summed while X was produced: one pass over X (bf16)
+    LaunchScope scope(K_FRO_NORMALIZE, 2.0 * m * (double)n * batch, stream);
+    sumsq_partial_kernel<<<dim3(chunks, batch), kThreads, 0, stream>>>(X, ldx, x_bs, m, n, chunks, partials);
+    MB_CUDA_CHECK(cudaGetLastError());
+  }
+  LaunchScope scope(K_FRO_NORMALIZE, 4.0 * (tile_sumsq ? tile_count : chunks) * batch, stream);
+  if (tile_sumsq) fro_finish_kernel<<<batch, kThreads, 0, stream>>>(tile_sumsq, tile_bs, tile_count, eps, scales, batch);
+  else fro_finish_kernel<<<batch, kThreads, 0, stream>>>(partials, chunks, chunks, eps, scales, batch);
   MB_CUDA_CHECK(cudaGetLastError());
   return OK;
 }

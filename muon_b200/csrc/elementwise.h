@@ -24,6 +24,8 @@ struct PrologueArgs {
   int vec_ok;         // all grad/mom pointers 16-byte aligned and cols % vector == 0
   float w_mom;        // float(1 - beta)
   float beta;         // float(beta)
+  float* sumsq;       // or null: per-tile sums of squares of X, tensor i at sumsq + i * sumsq_bs
+  long long sumsq_bs;
 };
 
 struct EpilogueArgs {
@@ -71,8 +73,15 @@ int launch_epilogue(const EpilogueArgs& a, int dtype, int transpose, cudaStream_
 int launch_aol_rescale(__nv_bfloat16* X, long long ldx, long long x_bs, const __nv_bfloat16* A,
                        __nv_bfloat16* A_out, long long lda, long long a_bs, float* svec,
                        long long s_bs, int m, int n, int batch, float eps, cudaStream_t stream);
-int launch_fro_normalize(__nv_bfloat16* X, long long ldx, long long x_bs, int m, int n, int batch,
-                         float eps, float* partials, int chunks, cudaStream_t stream);
+// Tiles (= partial sums) per tensor of the prologue kernel for parameters of this 2-D view.
+int prologue_tiles(int rows, int cols, int dtype);
+// scales[b] = 1 / (||X_b||_F + eps) and scales[batch + b] = its square, for the classic iteration.
+// With tile_sumsq (per-tile sums the prologue kernel left: tile_count per matrix, matrix b at
+// tile_sumsq + b * tile_bs) X is not read; otherwise one pass over X writes `chunks` partial sums
+// per matrix into `partials` first.
+int launch_fro_scales(const __nv_bfloat16* X, long long ldx, long long x_bs, int m, int n, int batch,
+                      float eps, float* partials, int chunks, const float* tile_sumsq, long long tile_bs,
+                      int tile_count, float* scales, cudaStream_t stream);
 int launch_adam(const AdamArgs& a, int dtype, cudaStream_t stream);
 // dst[b][r][c] (or dst[b][c][r] when transpose) = bf16(float(src[b][r][c]) * scale); src has
 // element type `dtype`, pitches in elements. src and dst may be the same buffer when the types

@@ -41,6 +41,10 @@ int ns_iterate(const NsBuffers& buf, int batch, int64_t m, int64_t n, int mode, 
   int cur = 0;
   int rc;
   bool have_gram = false;
+  const bool classic = mode == MUON_B200_NS_CLASSIC5;
+  // (its only line 3 already carries the normalisation factor)
+  if (classic && steps == 1 && upd)
+    return set_error(ERR_INVALID_ARG, "a one-step classic iteration cannot apply the update itself");
   // e4m3 products only where they pay and where their rounding noise averages out: the error of a
   // Gram entry falls with 1/sqrt(n), and below about a thousand columns it is no longer small
   // against the bf16 algorithm's own (measured: 1.2e-2 rel-Fro at n >= 2304, 2e-2 at n = 328).
@@ -65,11 +69,15 @@ int ns_iterate(const NsBuffers& buf, int batch, int64_t m, int64_t n, int mode, 
     if (rc != OK) return rc;
     have_gram = true;
   } else {
-    const int chunks = (int)(m < kFroChunksMax ? m : kFroChunksMax);
-    rc = launch_fro_normalize(buf.x[0], buf.ldx[0], buf.x_bs[0], (int)m, (int)n, batch, eps, buf.fscratch,
-                              chunks, st);
+    // muon.py:282: the factor 1 / (||X|| + eps) per matrix; the first line 1 and the first line 3
+    // apply it (squared, plain) to their outputs, X itself stays as it is.
+    if (!buf.fro_scales) return set_error(ERR_INVALID_ARG, "the classic iteration needs room for its scale factors");
+    const int chunks = (int)(m < kFroChunks ? m : kFroChunks);
+    rc = launch_fro_scales(buf.x[0], buf.ldx[0], buf.x_bs[0], (int)m, (int)n, batch, eps, buf.fscratch, chunks,
+                           buf.tile_sumsq, buf.tile_bs, (int)buf.tile_count, buf.fro_scales, st);
     if (rc != OK) return rc;
   }
+
   for (int k = 0; k < steps; ++k) {
     float a, b, c;
     if (coeffs) {
@@ -132,7 +140,8 @@ int ns_iterate(const NsBuffers& buf, int batch, int64_t m, int64_t n, int mode, 
                           buf.fscratch, buf.f_bs);
     } else {
       rc = launch_ns_gemm(MODE_SYRK, X, ldx, xbs, X, ldx, xbs, buf.A, buf.ldm, buf.a_bs, batch, m, m, n,
-                          1.f, 0.f, ADD_SYMMETRIC, st);
+                          1.f, 0.f, ADD_SYMMETRIC, st, nullptr, nullptr, 0, nullptr, nullptr,
+                          classic && k == 0 ? buf.fro_scales + batch : nullptr);
       if (rc != OK) return rc;
       // A comes straight from line 1 and is exactly symmetric.
       rc = launch_ns_gemm(MODE_AXPBY, buf.A, buf.ldm, buf.a_bs, buf.A, buf.ldm, buf.a_bs, buf.B, buf.ldm,
@@ -142,7 +151,8 @@ int ns_iterate(const NsBuffers& buf, int batch, int64_t m, int64_t n, int mode, 
     if (rc != OK) return rc;
     rc = launch_ns_gemm(MODE_BX, buf.B, buf.ldm, buf.a_bs, X, ldx, xbs, buf.x[cur ^ 1], buf.ldx[cur ^ 1],
                         buf.x_bs[cur ^ 1], batch, m, n, m, a, 0.f, ADD_GENERIC, st, nullptr, nullptr, 0,
-                        l3_out.kind != F8_NONE ? &l3_out : nullptr, k + 1 == steps ? upd : nullptr);
+                        l3_out.kind != F8_NONE ? &l3_out : nullptr, k + 1 == steps ? upd : nullptr,
+                        classic && k == 0 ? buf.fro_scales : nullptr);
     if (rc != OK) return rc;
     cur ^= 1;
   }
@@ -156,6 +166,10 @@ inline int64_t round_up_i64(int64_t v, int64_t a) { return (v + a - 1) / a * a; 
 
 int64_t ns_fp8_extra_bytes(int batch, int64_t m, int64_t n) {
   return round_up_i64(batch * m * fp8_pitch(n), 256) + round_up_i64(batch * m * fp8_pitch(m), 256);
+}
+
+int64_t ns_classic_extra_bytes(int batch, int64_t m, int64_t n) {
+  return round_up_i64((int64_t)batch * classic_tiles_max(m, n) * 4, 256);
 }
 
 int64_t ns_scratch_bytes(int batch, int64_t m, int64_t n, int mode) {
@@ -204,6 +218,9 @@ int ns_run_with_scratch(const void* src, int dtype, int64_t rows, int64_t cols, 
     buf.x8 = extra;
     buf.e8 = extra + round_up_i64(batch * buf.x8_bs, 256);
   }
+  // (classic iteration: the caller's matrices arrive through the cast kernel, so the driver sums
+  // over X itself; tile_sumsq stays null)
+  buf.fro_scales = fro_scales_in(buf.fscratch, batch, ldm);
   // muon.py:760-764: cast, transposition of tall inputs, contiguous copy.
   int rc = launch_cast_bf16(src, dtype, ld_src, src_bs, buf.x[0], buf.ldx[0], buf.x_bs[0], (int)rows,
                             (int)cols, batch, tall ? 1 : 0, 1.0f, st);

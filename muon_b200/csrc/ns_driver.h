@@ -12,7 +12,11 @@
 
 namespace mb {
 
-constexpr int kFroChunksMax = 296;  // partial sums per matrix of the Frobenius reduction
+constexpr int kFroChunksMax = 296;  // floats per matrix the fp32 area holds at least
+// Partial sums per matrix when the driver takes the Frobenius norm over X itself: fewer than
+// kFroChunksMax, so that the last 2 * batch floats of the fp32 area stay free for the factors
+// 1 / (||X|| + eps) and their squares.
+constexpr int kFroChunks = 288;
 constexpr int kFp8MinCols = 1024;   // MUON_B200_NS_AOL4_FP8: narrower matrices stay in bf16
 
 struct NsBuffers {
@@ -34,7 +38,26 @@ struct NsBuffers {
   uint8_t* x8;
   uint8_t* e8;
   int64_t ld8n, x8_bs, ld8m, e8_bs;
+  // MUON_B200_NS_CLASSIC5 only: fro_scales (inside fscratch, see fro_scales_in) receives
+  // 1 / (||X|| + eps) of every matrix and, batch floats further, its square. tile_sumsq, when not null, holds tile_count partial sums of squares
+  // per matrix (matrix b at tile_sumsq + b * tile_bs) that the prologue kernel left while it
+  // produced x[0]; without it the driver sums over x[0] itself.
+  float* fro_scales;
+  const float* tile_sumsq;
+  int64_t tile_bs;
+  int64_t tile_count;
 };
+
+// Floats per matrix of the fp32 area, and where the classic iteration keeps its two factors per
+// matrix inside it (the last 2 * batch floats).
+inline int64_t fscratch_per_matrix(int64_t ldm) { return ldm > kFroChunksMax ? ldm : kFroChunksMax; }
+inline float* fro_scales_in(float* fscratch, int batch, int64_t ldm) {
+  return fscratch + (int64_t)batch * fscratch_per_matrix(ldm) - 2 * (int64_t)batch;
+}
+// Bytes a workspace for the classic iteration adds for the prologue kernel's per-tile sums of
+// squares: at most one tile per 64 x 64 elements, in either orientation of the parameter.
+inline int64_t classic_tiles_max(int64_t m, int64_t n) { return ((m + 63) / 64) * ((n + 63) / 64); }
+int64_t ns_classic_extra_bytes(int batch, int64_t m, int64_t n);
 
 // Pitches (bytes) of the e4m3 copies and the bytes they add to a workspace or scratch area.
 inline int64_t fp8_pitch(int64_t cols) { return (cols + 15) / 16 * 16; }

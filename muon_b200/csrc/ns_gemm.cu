@@ -565,7 +565,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           (MODE == MODE_SYRK) ? nullptr : p.add + static_cast<long long>(tc.batch) * p.add_bs;
       __nv_bfloat16* out_row = out_b + static_cast<long long>(r) * p.ldo;
       // e4m3 copy of the output (null when this launch keeps none)
-      uint8_t* out8_b = (VAR != F8_NONE && p.out8) ? p.out8 + static_cast<long long>(tc.batch) * p.out8_bs : nullptr;
+      uint8_t* out8_b = ((VAR == F8_OPERANDS || VAR == F8_EXTRA_OUT) && p.out8) ? p.out8 + static_cast<long long>(tc.batch) * p.out8_bs : nullptr;
       const __nv_bfloat16* add_row =
           (MODE == MODE_SYRK) ? nullptr : add_b + static_cast<long long>(r) * p.ldadd;
 
@@ -666,10 +666,23 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               packed[j] = pack_bf16x2(fmaf(a[2 * j], p.beta, f[2 * j]), fmaf(a[2 * j + 1], p.beta, f[2 * j + 1]));
           }
         } else if constexpr (MODE == MODE_BX) {
+          if constexpr (VAR == V_BATCH_SCALE) {
+            // X was not normalised: (alpha * X + B X) / (||X|| + eps), one rounding
+            const float s = __ldg(p.batch_scale + tc.batch);
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            packed[j] = pack_bf16x2(fmaf(a[2 * j], p.alpha, f[2 * j]), fmaf(a[2 * j + 1], p.alpha, f[2 * j + 1]));
+            for (int j = 0; j < 16; ++j)
+              packed[j] = pack_bf16x2(fmaf(a[2 * j], p.alpha, f[2 * j]) * s, fmaf(a[2 * j + 1], p.alpha, f[2 * j + 1]) * s);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              packed[j] = pack_bf16x2(fmaf(a[2 * j], p.alpha, f[2 * j]), fmaf(a[2 * j + 1], p.alpha, f[2 * j + 1]));
+          }
         } else {
+          if constexpr (VAR == V_BATCH_SCALE) {
+            const float s = __ldg(p.batch_scale + tc.batch);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] *= s;
+          }
           if constexpr (VAR == F8_OPERANDS) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) f[j] *= p.acc_scale;  // the operands carried a power-of-two scale
@@ -678,7 +691,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           for (int j = 0; j < 16; ++j) packed[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
         }
 
-        if constexpr (MODE == MODE_BX && VAR >= V_UPD_BF16) {
+        if constexpr (MODE == MODE_BX && VAR >= V_UPD_BF16 && VAR <= V_UPD_F32) {
           // Last line 3 of the run: `packed` holds the bf16 Newton-Schulz output of row r, columns
           // col0 .. col0+31; it goes into the parameter instead of into the workspace.
           if constexpr (VAR == V_UPD_BF16) {
@@ -1005,7 +1018,7 @@ int encode_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, i
   return OK;
 }
 
-constexpr int kKernelSlots = 3 * 2 * 2 * 3 * 6;  // mode x CTAs per tile x epilogue warps x addend mode x variant
+constexpr int kKernelSlots = 3 * 2 * 2 * 3 * 7;  // mode x CTAs per tile x epilogue warps x addend mode x variant
 struct DeviceInfo {
   int sm_count = 0;
   int cc_major = 0;
@@ -1058,7 +1071,7 @@ int launch_instance(int dev, int sms, const CUtensorMap& ta, const CUtensorMap& 
                     const GemmParams& p, cudaStream_t stream) {
   using C = Cfg<CTAS>;
   auto kern = ns_gemm_kernel<MODE, B_MN, CTAS, EW, ADD, F8>;
-  const int slot = (((MODE * 2 + (CTAS - 1)) * 2 + (EW == 4 ? 0 : 1)) * 3 + ADD) * 6 + F8;
+  const int slot = (((MODE * 2 + (CTAS - 1)) * 2 + (EW == 4 ? 0 : 1)) * 3 + ADD) * 7 + F8;
   const long long total = (long long)p.tiles_per_batch * p.batch;
 
   cudaLaunchConfig_t cfg = {};
@@ -1136,6 +1149,14 @@ int launch_epi(int ew, int f8, int dev, int sms, const CUtensorMap& ta, const CU
       default: break;
     }
   }
+  if (f8 == V_BATCH_SCALE) {
+    if constexpr (MODE != MODE_AXPBY) {
+      return ew == 4 ? launch_instance<MODE, B_MN, CTAS, 4, ADD_SYMMETRIC, V_BATCH_SCALE>(dev, sms, ta, tb, p, stream)
+                     : launch_instance<MODE, B_MN, CTAS, 8, ADD_SYMMETRIC, V_BATCH_SCALE>(dev, sms, ta, tb, p, stream);
+    } else {
+      return set_error(ERR_INVALID_ARG, "line 2 has no per-matrix scale");
+    }
+  }
   if (f8 != F8_NONE) {
     // e4m3 variants exist for the symmetric-addend forms only (iterations after the first).
     constexpr int KIND = MODE == MODE_BX ? F8_EXTRA_OUT : F8_OPERANDS;
@@ -1203,7 +1224,8 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
                    const __nv_bfloat16* opb, int64_t ldb, int64_t b_bs, __nv_bfloat16* out,
                    int64_t ldo, int64_t out_bs, int batch, int64_t M, int64_t N, int64_t K,
                    float alpha, float beta, int sym_add, cudaStream_t stream, const __nv_bfloat16* addend,
-                   const float* row_scale, int64_t scale_bs, const Fp8Spec* f8, const UpdateSpec* upd) {
+                   const float* row_scale, int64_t scale_bs, const Fp8Spec* f8, const UpdateSpec* upd,
+                   const float* batch_scale) {
   if (!opa || !opb || !out) return set_error(ERR_INVALID_ARG, "null pointer passed to NS GEMM");
   if (batch < 1 || M < 1 || N < 1 || K < 1)
     return set_error(ERR_INVALID_ARG, "NS GEMM needs batch, M, N, K >= 1 (got %d, %lld, %lld, %lld)",
@@ -1249,6 +1271,12 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
     p.upd_decay = upd->decay;
     p.upd_neg_lr = upd->neg_lr;
     f8_kind = upd->dtype == DT_F32 ? V_UPD_F32 : (tall ? V_UPD_BF16_T : V_UPD_BF16);
+  }
+  if (batch_scale) {
+    if (f8_kind != F8_NONE || mode == MODE_AXPBY)
+      return set_error(ERR_INVALID_ARG, "a per-matrix scale goes with plain bf16 lines 1 and 3 only");
+    p.batch_scale = batch_scale;
+    f8_kind = V_BATCH_SCALE;
   }
   if (f8 && f8->kind != F8_NONE) {
     if ((f8_kind == F8_OPERANDS) != (mode != MODE_BX))

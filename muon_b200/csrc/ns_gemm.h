@@ -29,6 +29,9 @@ enum Variant : int {
   V_UPD_BF16 = 3,    // line 3 applies its output to bf16 parameters of the tile's orientation
   V_UPD_BF16_T = 4,  // ... to bf16 parameters stored as the transpose of the tile (tall parameters)
   V_UPD_F32 = 5,     // ... to fp32 parameters of the tile's orientation
+  V_BATCH_SCALE = 6, // lines 1 and 3: the output of matrix b is multiplied by batch_scale[b] (a
+                     // scalar in device memory) before it is rounded: the Frobenius normalisation
+                     // of the classic iteration folded into its first two products
 };
 
 constexpr int kMaxUpdateTensors = 64;  // parameters one fused-update launch can address
@@ -87,6 +90,8 @@ struct GemmParams {
   // fused parameter update (see UpdateSpec)
   void* upd_param[kMaxUpdateTensors];
   float upd_scale, upd_decay, upd_neg_lr;
+  // V_BATCH_SCALE: one factor per matrix of the batch
+  const float* batch_scale;
 };
 
 int device_sm_count(int* sm_count_out);
@@ -100,6 +105,7 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
                    int64_t ldo, int64_t out_bs, int batch, int64_t M, int64_t N, int64_t K,
                    float alpha, float beta, int sym_add, cudaStream_t stream,
                    const __nv_bfloat16* addend = nullptr, const float* row_scale = nullptr,
-                   int64_t scale_bs = 0, const Fp8Spec* f8 = nullptr, const UpdateSpec* upd = nullptr);
+                   int64_t scale_bs = 0, const Fp8Spec* f8 = nullptr, const UpdateSpec* upd = nullptr,
+                   const float* batch_scale = nullptr);
 
 }  // namespace mb

@@ -19,7 +19,7 @@ import torch
 from torch import Tensor
 
 from . import _lib
-from ._lib import BF16, F16, F32, F64, NS_AOL4, NS_AOL4_FP8, NS_CLASSIC5, check, i64_array, lib, ptr_array
+from ._lib import BF16, F16, F32, F64, NS_AOL4, NS_AOL4_FP8, NS_CLASSIC5, NS_HAVE_SUMSQ, check, i64_array, lib, ptr_array
 
 _DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
 # element types the cast at the entry of Newton-Schulz accepts (muon.py:760 takes any float dtype)
@@ -330,9 +330,9 @@ class CudaBackend:
                         1 if hyper["nesterov"] else 0, job["scale"], hyper["mode"], hyper["steps"], None, hyper["eps"],
                         wptr, layout.total_bytes, stream))
                 else:
-                    self._prologue(job, hyper, wptr, stream)
+                    run_mode = self._prologue(job, hyper, wptr, stream)
                     slot = ctypes.c_int(0)
-                    check(lib.muon_b200_ns_run(wptr, n, job["m"], job["n"], hyper["mode"], hyper["steps"], None,
+                    check(lib.muon_b200_ns_run(wptr, n, job["m"], job["n"], run_mode, hyper["steps"], None,
                                                hyper["eps"], ctypes.byref(slot), stream))
                     u = wptr + (layout.x_offset_bytes if slot.value == 0 else layout.c_offset_bytes)
                     # the update kernel also writes the peers' copies
@@ -345,12 +345,18 @@ class CudaBackend:
                     after_group(job["params"], done)
 
     @staticmethod
-    def _prologue(job, hyper, wptr, stream) -> None:
+    def _prologue(job, hyper, wptr, stream) -> int:
+        """Momentum blend + bf16 X into the workspace. Returns the mode to run the iteration with: in
+        the classic mode the kernel also leaves the sums of squares of X (the Frobenius norm of
+        muon.py:282), and the run is told so."""
         layout = job["layout"]
-        check(lib.muon_b200_prologue(
+        classic = hyper["mode"] == NS_CLASSIC5
+        check(lib.muon_b200_prologue_sumsq(
             ptr_array([g.data_ptr() for g in job["grads"]]), ptr_array([m.data_ptr() for m in job["moms"]]),
             len(job["params"]), job["rows"], job["cols"], job["code"], hyper["beta"], 1 if hyper["nesterov"] else 0,
-            wptr + layout.x_offset_bytes, layout.ldn, layout.x_bs, 1 if job["tall"] else 0, stream))
+            wptr + layout.x_offset_bytes, layout.ldn, layout.x_bs, 1 if job["tall"] else 0,
+            wptr + layout.sumsq_offset_bytes if classic else None, layout.sumsq_bs, stream))
+        return hyper["mode"] | NS_HAVE_SUMSQ if classic else hyper["mode"]
 
     @staticmethod
     def _epilogue(plist, peer_ptrs, rows, cols, code, u, layout, tall, lr, weight_decay, scale, stream) -> None:
@@ -387,10 +393,12 @@ class CudaBackend:
 
             def prologue(i):
                 _wait_grads(side, jobs[i]["grads"])
-                self._prologue(jobs[i], hyper, ws_ptr[i % 2], side.cuda_stream)
+                run_modes[i] = self._prologue(jobs[i], hyper, ws_ptr[i % 2], side.cuda_stream)
                 ev = torch.cuda.Event()
                 ev.record(side)
                 return ev
+
+            run_modes = [hyper["mode"]] * len(jobs)
 
             p_done = prologue(0)
             for i, job in enumerate(jobs):
@@ -400,7 +408,7 @@ class CudaBackend:
                 if peer_ptrs is None:
                     # the last GEMM of the iteration applies the update itself (where it can)
                     check(lib.muon_b200_ns_run_update(
-                        ws_ptr[i % 2], hyper["mode"], hyper["steps"], None, hyper["eps"],
+                        ws_ptr[i % 2], run_modes[i], hyper["steps"], None, hyper["eps"],
                         ptr_array([p.data_ptr() for p in job["params"]]), n, job["rows"], job["cols"], job["code"],
                         hyper["lr"], hyper["weight_decay"], job["scale"], main.cuda_stream))
                     ns_done = torch.cuda.Event()
@@ -410,7 +418,7 @@ class CudaBackend:
                         after_group(job["params"], ns_done)
                 else:
                     slot = ctypes.c_int(0)
-                    check(lib.muon_b200_ns_run(ws_ptr[i % 2], n, job["m"], job["n"], hyper["mode"], hyper["steps"],
+                    check(lib.muon_b200_ns_run(ws_ptr[i % 2], n, job["m"], job["n"], run_modes[i], hyper["steps"],
                                                None, hyper["eps"], ctypes.byref(slot), main.cuda_stream))
                     ns_done = torch.cuda.Event()
                     ns_done.record(main)

@@ -218,15 +218,37 @@ def zeropower_aol4_fp8(G: Tensor, epsilon: float = 1e-7) -> Tensor:
     return X
 
 
-def zeropower_classic5(G: Tensor, steps: int = 5, *, fused: bool = False) -> Tensor:
+def zeropower_classic5(G: Tensor, steps: int = 5, *, fused: bool = False, folded: bool = False) -> Tensor:
     """The commented reference block, muon.py:265-291 (Frobenius normalisation, fixed
     coefficients).  ``fused=False`` executes it literally with eager bf16 tensors (every
-    op rounds); ``fused=True`` rounds once per GEMM line like the kernels do."""
+    op rounds); ``fused=True`` rounds once per GEMM line like the kernels do.
+
+    ``folded=True`` (implies the single rounding per line) is the arithmetic of the CUDA path:
+    X is not divided by its norm in memory; with c = 1 / bf16(bf16(||X||) + 1e-7) in fp32 the
+    first Gram product is rounded once from c^2 · (X · Xᵀ) and the first line 3 once from
+    c · (a · X + B · X).  It differs from ``fused=True`` only by the rounding of X / (||X|| + eps)
+    to bf16 that it leaves out."""
     assert G.ndim >= 2
     a, b, c = CLASSIC_COEFFS
     X = G.bfloat16()
     if G.size(-2) > G.size(-1):
         X = X.mT
+    if folded:
+        den = (X.norm(dim=(-2, -1), keepdim=True) + 1e-7).float()  # bf16 norm, bf16 sum (eager)
+        inv = 1.0 / den
+        for k in range(steps):
+            if k == 0:
+                Xf = X.float()
+                A = _mirror((Xf @ Xf.mT) * (inv * inv), "lower", 64).to(X.dtype)
+                B = ns_line_2(A, alpha=c, beta=b)
+                X = ((Xf * a + B.float() @ Xf) * inv).to(X.dtype)
+            else:
+                A = ns_line_1(X)
+                B = ns_line_2(A, alpha=c, beta=b)
+                X = ns_line_3(B, X, a)
+        if G.size(-2) > G.size(-1):
+            X = X.mT
+        return X
     X = X / (X.norm(dim=(-2, -1), keepdim=True) + 1e-7)
     for _ in range(steps):
         if fused:

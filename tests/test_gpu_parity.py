@@ -152,13 +152,63 @@ def test_newton_schulz_classic5(mb, shape):
         U = mb.zeropower_via_newtonschulz5(G.to(DEV)).cpu()
     finally:
         mb.set_ns_mode("aol4")
-    # Against the restatement with the kernels' rounding points (one per GEMM line): 1e-2.
-    assert orc.rel_fro(U, orc.zeropower_classic5(G, fused=True)) <= 1e-2
+    # Against the restatement with the kernels' arithmetic (one rounding per GEMM line, the factor
+    # 1/(||X|| + eps) applied by the first two products): 1e-2. Against the restatement that rounds
+    # X / (||X|| + eps) to bf16 first, as the text does: 2.5e-2 (this iteration amplifies every
+    # change of rounding; the two restatements are 1.3e-2 .. 1.7e-2 apart).
+    assert orc.rel_fro(U, orc.zeropower_classic5(G, folded=True)) <= 1e-2
+    assert orc.rel_fro(U, orc.zeropower_classic5(G, fused=True)) <= 2.5e-2
     # Against the literal eager-bf16 execution of the commented block, which rounds after every
     # op: the oracle's own eager-vs-fused gap is 2.4e-2 .. 3.7e-2, so the bound here is 5e-2.
     assert orc.rel_fro(U, orc.zeropower_classic5(G)) <= 5e-2
     lo, hi = orc.singular_value_band(U)
     assert hi < 1.25
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(384, 1024), (1024, 384), (200, 328), (64, 32, 3, 3)])
+def test_classic5_step_takes_the_norm_in_the_prologue(mb, shape, dtype):
+    """In the classic mode the optimizer's prologue kernel sums the squares of X while it writes it
+    (muon.py:282 fused into the momentum pass). The step must agree with the oracle's step, and
+    with the step whose Newton-Schulz input goes through the functional entry point, which sums
+    over X in a pass of its own: both orders of summation give the same bf16 denominator except on
+    rounding ties, so the parameters agree to the last few bits."""
+    import functools
+    g = torch.Generator().manual_seed(31)
+    p0 = [torch.randn(shape, generator=g).to(dtype) * 0.05 for _ in range(3)]
+    grads = [torch.randn(shape, generator=g).to(dtype) for _ in range(3)]
+    ps = [torch.nn.Parameter(p.clone().to(DEV)) for p in p0]
+    mb.set_ns_mode("classic5")
+    try:
+        opt = mb.SingleDeviceMuon(ps, lr=0.05, weight_decay=0.01, momentum=0.95)
+        for p, gr in zip(ps, grads):
+            p.grad = gr.clone().to(DEV)
+        before = mb._lib.launch_counts()
+        opt.step()
+        torch.cuda.synchronize()
+        after = mb._lib.launch_counts()
+        # functional path on the same blended gradient
+        mom = torch.zeros_like(grads[0])
+        gq = grads[0].clone()
+        mom.lerp_(gq, 1 - 0.95)
+        upd = gq.lerp_(mom, 0.95)
+        U_fn = mb.zeropower_via_newtonschulz5(upd.reshape(upd.shape[0], -1).to(DEV)).float().cpu()
+    finally:
+        mb.set_ns_mode("aol4")
+    assert mb.device_status() == 0
+    # one launch of the tiny kernel that adds the partial sums; no pass over X
+    assert after["fro_normalize"] - before["fro_normalize"] == 1
+    ns = functools.partial(orc.zeropower_classic5, folded=True)
+    for p, ref, gr in zip(ps, p0, grads):
+        ref = ref.clone()
+        orc.muon_param_step(ref, gr.clone(), torch.zeros_like(ref), 0.05, 0.01, 0.95, ns=ns)
+        tol = 1e-3 if dtype == torch.float32 else 6e-3  # lr * |update| / |p| ~ 0.05, update within 1e-2
+        assert orc.rel_fro(p.detach().float().cpu(), ref.float()) <= tol
+    # the update of parameter 0 against the functional path's orthogonalised matrix
+    scale = max(1, U_fn.shape[0] / U_fn.shape[1]) ** 0.5
+    step_update = (p0[0].float() * (1 - 0.05 * 0.01) - ps[0].detach().float().cpu()).reshape(U_fn.shape) / 0.05
+    if dtype == torch.float32:  # (a bf16 parameter keeps too few bits of its update)
+        assert orc.rel_fro(step_update, (U_fn.bfloat16() * scale).float()) <= 6e-3
 
 
 @pytest.mark.parametrize("shape", [(768, 3072), (3072, 768), (256, 2304), (1024, 4096), (2, 384, 1536), (100, 250)])

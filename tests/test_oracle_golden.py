@@ -158,7 +158,15 @@ def test_newton_schulz_restatement_is_stable(golden):
         assert hi < 1.3
         # One rounding per GEMM line (what the kernels do) vs a rounding after every eager op: the
         # non-convergent classic iteration amplifies that to 2.4e-2 .. 3.7e-2 on these shapes.
-        assert orc.rel_fro(orc.zeropower_classic5(c["G"], fused=True), Uc) < 5e-2
+        fused = orc.zeropower_classic5(c["G"], fused=True)
+        assert orc.rel_fro(fused, Uc) < 5e-2
+        # The normalisation factor applied by the first two products instead of to X in memory
+        # (the CUDA path): only the rounding of X / (||X|| + eps) to bf16 is missing, which this
+        # iteration amplifies like any other change of rounding (1.3e-2 .. 1.7e-2 here); the folded
+        # form is as far from the literal text as the fused one (3.1e-2 .. 3.5e-2).
+        folded = orc.zeropower_classic5(c["G"], folded=True)
+        assert orc.rel_fro(folded, fused) < 2.5e-2
+        assert orc.rel_fro(folded, Uc) < 5e-2
 
 
 def test_oracle_against_the_reference_run_on_a_b200(golden):
