@@ -8,6 +8,8 @@ from ._lib import MuonB200Error, device_status  # noqa: F401  (import fails loud
 from .backward_overlap import StepInBackward  # noqa: F401
 from .checkpoint import consolidated_state_dict, load_consolidated_state_dict  # noqa: F401
 from .engine import get_backend, get_ns_mode, mark_grad_ready, set_ns_mode  # noqa: F401
+from .ownership import get_ownership, set_ownership  # noqa: F401
+from .sharded import ShardedMuon  # noqa: F401
 from .ops import (  # noqa: F401
     adam_update,
     muon_update,
@@ -29,4 +31,5 @@ __all__ = [
     "ns_line_1", "ns_line_2", "ns_line_3",
     "set_ns_mode", "get_ns_mode", "get_backend", "device_status", "MuonB200Error",
     "mark_grad_ready", "StepInBackward", "consolidated_state_dict", "load_consolidated_state_dict",
+    "set_ownership", "get_ownership", "ShardedMuon",
 ]

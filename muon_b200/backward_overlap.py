@@ -37,6 +37,7 @@ import torch.distributed as dist
 
 from . import optim as _optim
 from .exchange import get_peer_push
+from .ownership import owned_indices
 
 
 class StepInBackward:
@@ -66,9 +67,10 @@ class StepInBackward:
                 self._pushes.append(push)
             world = dist.get_world_size() if self._distributed else 1
             rank = dist.get_rank() if self._distributed else 0
-            index = {id(p): i for i, p in enumerate(group["params"])}
+            # muon.py:56-58, or the cost-balanced assignment (ownership.py)
+            owned = {id(group["params"][i]) for i in owned_indices(group["params"], world, rank)}
             for plist in _optim._bucket_by_shape(group["params"]).values():
-                mine = [p for p in plist if index[id(p)] % world == rank]  # muon.py:56-58
+                mine = [p for p in plist if id(p) in owned]
                 entry = dict(group=group, params=plist, waiting={id(p) for p in plist}, done=False,
                              push=push, mine=mine)
                 self._sets.append(entry)

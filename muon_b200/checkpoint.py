@@ -12,6 +12,8 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+from .ownership import owned_indices
+
 FORMAT = "muon_b200.consolidated.v1"
 
 
@@ -56,8 +58,8 @@ def consolidated_state_dict(optimizer, dst: int = 0):
 
 def load_consolidated_state_dict(optimizer, state) -> None:
     """Every rank passes the same dictionary (from ``consolidated_state_dict``). Each rank keeps
-    the momentum of the parameters it owns under the current world size (index % world == rank)
-    and drops the rest; Adam state is restored on every rank. Hyper-parameters are restored too."""
+    the momentum of the parameters it owns under the current world size and ownership policy
+    (ownership.py; by default index % world == rank) and drops the rest; Adam state is restored on every rank. Hyper-parameters are restored too."""
     if not isinstance(state, dict) or state.get("format") != FORMAT:
         raise ValueError("not a consolidated muon_b200 optimizer state")
     world, rank = _world()
@@ -72,8 +74,9 @@ def load_consolidated_state_dict(optimizer, state) -> None:
             group[k] = v
         if group.get("use_muon", True):
             momentum = entry.get("momentum", {})
+            mine = set(owned_indices(params, world, rank)) if distributed_cls else set(range(len(params)))
             for i, p in enumerate(params):
-                owned = (i % world == rank) if distributed_cls else True
+                owned = i in mine
                 optimizer.state.pop(p, None)
                 if owned and i in momentum:
                     optimizer.state[p]["momentum_buffer"] = momentum[i].to(device=p.device, dtype=p.dtype).clone()

@@ -435,6 +435,75 @@ class CudaBackend:
                 self.launch_groups += 1
             main.wait_stream(side)
 
+    # -- pieces for row-sharded parameters (sharded.py) -----------------------------------
+    def muon_orthogonalize(self, grads: Sequence[Tensor], moms: Sequence[Tensor], shape: Sequence[int],
+                           beta: float, nesterov: bool, out: Tensor) -> None:
+        """Momentum blend (in place on moms and grads) + Newton-Schulz + aspect scale for full
+        matrices of one shape (muon.py:9-14), the result left in memory instead of applied:
+        out[k, :rows, :cols] = bf16(U_k * scale) in the parameter's own orientation. `out` is
+        bf16 [count, R >= rows, ld >= cols], contiguous, ld a multiple of 8."""
+        mode, steps = _ns_mode, _ns_steps
+        rows, cols = view_2d(shape)
+        if not grads:
+            return
+        if out.dtype != torch.bfloat16 or not out.is_contiguous() or out.ndim != 3 or out.shape[0] != len(grads) \
+                or out.shape[1] < rows or out.shape[2] < cols or out.shape[2] % 8:
+            raise ValueError("muon_orthogonalize: out must be contiguous bf16 [count, >= rows, ld >= cols], ld % 8 == 0")
+        code = dtype_code(grads[0])
+        for g, m in zip(grads, moms):
+            _require_cuda(g, "gradient")
+            if g.dtype != grads[0].dtype or m.dtype != g.dtype or g.numel() != rows * cols or m.numel() != rows * cols:
+                raise ValueError("muon_orthogonalize needs full gradients and momenta of one shape and dtype")
+            if not (g.is_contiguous() and m.is_contiguous()):
+                raise ValueError("muon_orthogonalize needs contiguous gradient and momentum")
+        dev = grads[0].device
+        m_, n_ = min(rows, cols), max(rows, cols)
+        tall = rows > cols
+        hyper = dict(beta=beta, nesterov=nesterov, mode=_NS_MODES[mode], steps=steps, eps=1e-7)
+        sizes = plan_launches(m_, n_, len(grads), self.workspace_cap_bytes, self._sm_pairs(dev))
+        with torch.cuda.device(dev):
+            current = torch.cuda.current_stream(dev)
+            stream = current.cuda_stream
+            start = 0
+            for b in sizes:
+                layout = _lib.ns_layout(b, m_, n_, _NS_MODES[mode])
+                job = dict(params=grads[start:start + b], grads=grads[start:start + b], moms=moms[start:start + b],
+                           rows=rows, cols=cols, code=code, tall=tall, layout=layout)
+                wptr = self._aligned_ptr(self.workspace(dev, layout.total_bytes))
+                _wait_grads(current, job["grads"])
+                run_mode = self._prologue(job, hyper, wptr, stream)
+                slot = ctypes.c_int(0)
+                check(lib.muon_b200_ns_run(wptr, b, m_, n_, run_mode, steps, None, hyper["eps"], ctypes.byref(slot),
+                                           stream))
+                u = wptr + (layout.x_offset_bytes if slot.value == 0 else layout.c_offset_bytes)
+                # bf16(U * scale), transposed back for tall parameters (muon.py:14, :797-798)
+                check(lib.muon_b200_cast_bf16(u, BF16, m_, n_, layout.ldn, layout.x_bs,
+                                              out.data_ptr() + start * out.stride(0) * 2, out.stride(1), out.stride(0),
+                                              b, 1 if tall else 0, aspect_scale(shape), stream))
+                self.launch_groups += 1
+                start += b
+
+    def apply_update(self, shards: Sequence[Tensor], u: Tensor, rows: int, cols: int, lr: float,
+                     weight_decay: float) -> None:
+        """p = p*(1 - lr*wd) - lr*u (muon.py:66-67) on `rows` x `cols` pieces of parameters: shards[k]
+        is contiguous with rows*cols elements, its update is u[k, :rows, :cols], u bf16
+        [count, R >= rows, ld >= cols] contiguous with ld a multiple of 8, already scaled."""
+        if not shards or rows == 0:
+            return
+        if u.dtype != torch.bfloat16 or not u.is_contiguous() or u.ndim != 3 or u.shape[0] != len(shards) \
+                or u.shape[1] < rows or u.shape[2] < cols or u.shape[2] % 8:
+            raise ValueError("apply_update: u must be contiguous bf16 [count, >= rows, ld >= cols], ld % 8 == 0")
+        code = dtype_code(shards[0])
+        for p in shards:
+            _require_cuda(p, "parameter")
+            if p.dtype != shards[0].dtype or p.numel() != rows * cols or not p.is_contiguous():
+                raise ValueError("apply_update needs contiguous pieces of one size and dtype")
+        dev = shards[0].device
+        with torch.cuda.device(dev):
+            check(lib.muon_b200_epilogue(ptr_array([p.data_ptr() for p in shards]), len(shards), rows, cols, code,
+                                         u.data_ptr(), u.stride(1), u.stride(0), 0, lr, weight_decay, 1.0,
+                                         _stream_ptr(dev)))
+
     def _side_stream(self, device: torch.device):
         key = device.index if device.index is not None else torch.cuda.current_device()
         s = self._side_streams.get(key)

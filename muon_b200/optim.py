@@ -20,6 +20,7 @@ import torch.distributed as dist
 
 from .engine import get_backend, plan_launches, view_2d
 from .exchange import get_peer_push
+from .ownership import get_ownership, owners
 
 
 def _ensure_grad_and_state(optimizer, p) -> None:
@@ -121,13 +122,16 @@ def _throttle_gathers(pending, settled: int, device) -> int:
 
 def _distributed_muon_group_step(optimizer, group) -> None:
     """Windowed round-robin of muon.py:54-68. Window k holds params[kW:(k+1)W]; rank r
-    updates params[kW + r] and every rank then receives the whole window."""
+    updates params[kW + r] and every rank then receives the whole window. (With the `balanced`
+    ownership policy the assignment is by cost instead, see ownership.py; the result is the same.)"""
     backend = get_backend()
     world, rank = dist.get_world_size(), dist.get_rank()
     params = group["params"]
     # muon.py:55 — the pad entries alias one scratch tensor and only ever receive.
     params_pad = params + [torch.empty_like(params[-1])] * (world - len(params) % world)
-    owned = list(range(rank, len(params), world))
+    policy = get_ownership()
+    who = owners([tuple(p.shape) for p in params], world, policy)
+    owned = [i for i, r in enumerate(who) if r == rank]
     done_upto = 0  # owned[:done_upto] have been updated
     pending, settled = [], 0
     if world == 1:
@@ -150,6 +154,17 @@ def _distributed_muon_group_step(optimizer, group) -> None:
         else:
             _muon_update_params(optimizer, mine, group, after_group=push.push, halve_groups=world >= 4)
         push.end_step()
+        return
+    if policy != "round_robin":
+        # Not the window pattern all_gather needs: this rank updates what it owns, then every
+        # parameter is broadcast by its owner, in list order on every rank.
+        _muon_update_params(optimizer, [params[i] for i in owned], group)
+        for i, p in enumerate(params):
+            pending.append(dist.broadcast(p, src=who[i], async_op=True))
+            settled = _throttle_gathers(pending, settled, params[0].device)
+        for work in pending[settled:]:
+            if work is not None:
+                work.wait()
         return
     for base_i in range(0, len(params), world):
         mine = base_i + rank

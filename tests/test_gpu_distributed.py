@@ -22,9 +22,10 @@ def _problem(steps=2):
     return p0, grads
 
 
-def _worker(rank, world, tmpdir, exchange, dtype):
+def _worker(rank, world, tmpdir, exchange, dtype, policy="round_robin"):
     import datetime
     os.environ["MUON_B200_EXCHANGE"] = exchange
+    os.environ["MUON_B200_OWNERSHIP"] = policy
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", init_method=f"file://{tmpdir}/pg_{exchange}", rank=rank,
                             world_size=world, timeout=datetime.timedelta(seconds=60))
@@ -81,6 +82,58 @@ def _worker_overlap(rank, world, tmpdir, exchange):
         dist.destroy_process_group()
 
 
+def _worker_sharded(rank, world, tmpdir, dtype):
+    import datetime
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", init_method=f"file://{tmpdir}/pg_sharded", rank=rank,
+                            world_size=world, timeout=datetime.timedelta(seconds=60))
+    try:
+        import muon_b200 as mb
+        from muon_b200.sharded import shard_rows
+        dev = torch.device("cuda", rank)
+        p0, grads = _problem()
+
+        def piece(t):
+            chunk, mine = shard_rows(t.shape[0], world, rank)
+            return t[rank * chunk: rank * chunk + mine].to(dtype).to(dev).contiguous()
+
+        params = [torch.nn.Parameter(piece(p)) for p in p0]
+        opt = mb.ShardedMuon(list(params), lr=0.02, weight_decay=0.01, full_shapes=SHAPES)
+        for step_grads in grads:
+            for p, gr in zip(params, step_grads):
+                p.grad = piece(gr)
+            opt.step()
+        torch.cuda.synchronize()
+        torch.save(dict(local=[p.detach().cpu() for p in params], status=mb.device_status()),
+                   f"{tmpdir}/sharded_{rank}.pt")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_sharded_muon_matches_single_device(tmp_path, dtype):
+    """Row-sharded parameters on 2 to 4 GPUs: every rank's rows equal those of SingleDeviceMuon on
+    the full parameters, bit for bit (SHAPES includes row counts the world size does not divide)."""
+    from muon_b200.sharded import shard_rows
+    world = min(torch.cuda.device_count(), 3)
+    mp.spawn(_worker_sharded, args=(world, str(tmp_path), dtype), nprocs=world, join=True)
+    outs = [torch.load(f"{tmp_path}/sharded_{r}.pt", weights_only=False) for r in range(world)]
+
+    import muon_b200 as mb
+    p0, grads = _problem()
+    ref = [torch.nn.Parameter(p.to(dtype).cuda()) for p in p0]
+    opt = mb.SingleDeviceMuon(ref, lr=0.02, weight_decay=0.01)
+    for step_grads in grads:
+        for p, gr in zip(ref, step_grads):
+            p.grad = gr.to(dtype).cuda()
+        opt.step()
+    for r, o in enumerate(outs):
+        assert o["status"] == 0
+        for i, (piece, full) in enumerate(zip(o["local"], ref)):
+            chunk, mine = shard_rows(full.shape[0], world, r)
+            assert torch.equal(piece, full.detach().cpu()[r * chunk: r * chunk + mine]), f"rank {r}, parameter {i}"
+
+
 @pytest.mark.parametrize("exchange", ["st", "ce"])
 def test_step_in_backward_on_a_distributed_optimizer(tmp_path, exchange):
     """Every rank ends with the parameters a single GPU gets from the plain optimizer step."""
@@ -110,11 +163,12 @@ def test_step_in_backward_on_a_distributed_optimizer(tmp_path, exchange):
             assert torch.equal(p, q.detach().cpu()), f"rank {r}, parameter {i} ({exchange})"
 
 
-@pytest.mark.parametrize("exchange", ["st", "ce", "nccl"])
+@pytest.mark.parametrize("exchange,policy", [("st", "round_robin"), ("ce", "round_robin"), ("nccl", "round_robin"),
+                                             ("ce", "balanced"), ("nccl", "balanced")])
 @pytest.mark.parametrize("dtype", [torch.bfloat16])
-def test_distributed_step_matches_single_device(tmp_path, exchange, dtype):
+def test_distributed_step_matches_single_device(tmp_path, exchange, policy, dtype):
     world = min(torch.cuda.device_count(), 4)
-    mp.spawn(_worker, args=(world, str(tmp_path), exchange, dtype), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, str(tmp_path), exchange, dtype, policy), nprocs=world, join=True)
     outs = [torch.load(f"{tmp_path}/out_{exchange}_{r}.pt", weights_only=False) for r in range(world)]
 
     import muon_b200 as mb
@@ -130,6 +184,11 @@ def test_distributed_step_matches_single_device(tmp_path, exchange, dtype):
     for r, o in enumerate(outs):
         assert o["status"] == 0
         assert o["used_ce"] == (exchange in ("ce", "st"))
-        assert o["owned"] == list(range(r, len(SHAPES), world))
+        if policy == "round_robin":
+            assert o["owned"] == list(range(r, len(SHAPES), world))  # muon.py:56-58
+        else:
+            from muon_b200 import ownership
+            assert o["owned"] == ownership.owned_indices([torch.empty(s) for s in sorted(SHAPES, reverse=True)],
+                                                         world, r, "balanced")
         for i, (p, q) in enumerate(zip(o["params"], ref)):
             assert torch.equal(p, q), f"rank {r}, parameter {i} {tuple(q.shape)} ({exchange})"

@@ -166,6 +166,46 @@ def test_newton_schulz_classic5(mb, shape):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(384, 1024), (1024, 384), (200, 328), (328, 200), (64, 32, 3, 3)])
+def test_update_left_in_memory_then_applied_by_rows(mb, shape, dtype):
+    """The two pieces the row-sharded optimizer is made of: `muon_orthogonalize` leaves
+    bf16(U * scale) in memory, `apply_update` applies rows of it to pieces of the parameters.
+    Applied to row blocks of uneven sizes they must give the parameters of `SingleDeviceMuon.step`
+    bit for bit."""
+    from muon_b200.engine import view_2d
+    g = torch.Generator().manual_seed(41)
+    count = 3
+    p0 = [(torch.randn(shape, generator=g) * 0.05).to(dtype) for _ in range(count)]
+    grads = [torch.randn(shape, generator=g).to(dtype) for _ in range(count)]
+    ref = [torch.nn.Parameter(p.clone().to(DEV)) for p in p0]
+    opt = mb.SingleDeviceMuon(ref, lr=0.03, weight_decay=0.02, momentum=0.9)
+    for p, gr in zip(ref, grads):
+        p.grad = gr.clone().to(DEV)
+    opt.step()
+
+    backend = mb.get_backend()
+    rows, cols = view_2d(shape)
+    ld = (cols + 7) // 8 * 8
+    gq = [gr.clone().to(DEV).reshape(rows, cols) for gr in grads]
+    moms = [torch.zeros(rows, cols, dtype=dtype, device=DEV) for _ in range(count)]
+    out = torch.zeros(count, rows + 5, ld, dtype=torch.bfloat16, device=DEV)
+    backend.muon_orthogonalize(gq, moms, shape, 0.9, True, out)
+    cuts = [0, rows // 3, rows // 3 + 1, rows]  # three row blocks, one of them a single row
+    new = [p.clone().to(DEV).reshape(rows, cols) for p in p0]
+    for lo, hi in zip(cuts[:-1], cuts[1:]):
+        pieces = [q[lo:hi].clone() for q in new]
+        u = out[:, lo:hi].contiguous()
+        backend.apply_update(pieces, u, hi - lo, cols, 0.03, 0.02)
+        for q, piece in zip(new, pieces):
+            q[lo:hi] = piece
+    torch.cuda.synchronize()
+    assert mb.device_status() == 0
+    for q, r, m in zip(new, ref, moms):
+        assert torch.equal(q.reshape(shape), r.detach())
+        assert torch.equal(m.reshape(shape), opt.state[r]["momentum_buffer"])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(384, 1024), (1024, 384), (200, 328), (64, 32, 3, 3)])
 def test_classic5_step_takes_the_norm_in_the_prologue(mb, shape, dtype):
     """In the classic mode the optimizer's prologue kernel sums the squares of X while it writes it

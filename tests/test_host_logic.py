@@ -187,6 +187,17 @@ class OracleBackend:
         for p, g, m, v, s in zip(params, grads, exp_avgs, exp_avg_sqs, steps):
             orc.adam_param_step(p, g, m, v, s, lr, weight_decay, betas, eps)
 
+    def muon_orthogonalize(self, grads, moms, shape, beta, nesterov, out):
+        rows, cols = shape[0], int(torch.tensor(shape[1:]).prod())
+        for k, (g, m) in enumerate(zip(grads, moms)):
+            u = orc.muon_update(g.view(shape), m.view(shape), beta=beta, nesterov=nesterov)
+            out[k, :rows, :cols] = u.reshape(rows, cols)
+
+    def apply_update(self, shards, u, rows, cols, lr, weight_decay):
+        for k, p in enumerate(shards):
+            p.mul_(1 - lr * weight_decay)
+            p.add_(u[k, :rows, :cols].reshape(p.shape).to(p.dtype), alpha=-lr)
+
 
 def _make_problem(shapes, seed=0, steps=2):
     g = torch.Generator().manual_seed(seed)
@@ -195,12 +206,14 @@ def _make_problem(shapes, seed=0, steps=2):
     return p0, grads
 
 
-def _rank_main(rank, world, shapes, tmpdir, with_adam):
+def _rank_main(rank, world, shapes, tmpdir, with_adam, policy="round_robin"):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     dist.init_process_group("gloo", init_method=f"file://{tmpdir}/pg", rank=rank, world_size=world)
     try:
         import muon_b200 as mb
         from muon_b200 import engine as E
+        from muon_b200 import ownership
+        mb.set_ownership(policy)
         backend = OracleBackend()
         E._set_backend_for_testing(backend)
         p0, grads = _make_problem(shapes)
@@ -219,7 +232,9 @@ def _rank_main(rank, world, shapes, tmpdir, with_adam):
                 gp.grad = torch.full((8,), 0.5)
             opt.step()
         sorted_params = opt.param_groups[0]["params"]
-        owned = [i for i in range(len(sorted_params)) if i % world == rank]
+        owned = ownership.owned_indices(sorted_params, world, rank)
+        if policy == "round_robin":
+            assert owned == [i for i in range(len(sorted_params)) if i % world == rank]  # muon.py:56-58
         has_state = [i for i, p in enumerate(sorted_params) if len(opt.state[p]) > 0]
         torch.save(dict(params=[p.detach().clone() for p in params], owned=owned, has_state=has_state,
                         calls=backend.muon_calls, gains=[g.detach().clone() for g in gains]),
@@ -277,6 +292,93 @@ def test_distributed_muon_with_mixed_shape_windows(tmp_path, world, shapes):
         for p, q in zip(o["params"], ref):
             assert torch.equal(p, q), f"rank {r} disagrees with the single-device result"
         assert o["has_state"] == o["owned"]
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_distributed_muon_with_cost_balanced_ownership(tmp_path, world):
+    """`balanced` ownership: parameters go to the rank with the least Newton-Schulz work so far
+    instead of round-robin. The parameters after two steps are those of the single-device run bit
+    for bit (who updates a parameter does not enter its update), the momentum lives on the owner
+    only, and the work is spread more evenly than round-robin spreads this mix."""
+    from muon_b200 import ownership
+    shapes = [(64, 96)] * (world + 1) + [(96, 32)] * 2 + [(16, 16)] * 5 + [(8, 4, 3, 3)] * 3
+    mp.spawn(_rank_main, args=(world, shapes, str(tmp_path), False, "balanced"), nprocs=world, join=True)
+    outs = [torch.load(f"{tmp_path}/out{r}.pt", weights_only=False) for r in range(world)]
+    ref = _single_device_oracle(shapes)
+    for r, o in enumerate(outs):
+        for p, q in zip(o["params"], ref):
+            assert torch.equal(p, q), f"rank {r} disagrees with the single-device result"
+        assert o["has_state"] == o["owned"], "momentum state must exist on the owning rank only"
+    assert sorted(i for o in outs for i in o["owned"]) == list(range(len(shapes)))
+    sorted_shapes = sorted(shapes, reverse=True)
+
+    def spread(policy):
+        who = ownership.owners(sorted_shapes, world, policy)
+        load = [sum(ownership.ns_cost(s) for s, w in zip(sorted_shapes, who) if w == r) for r in range(world)]
+        return max(load) - min(load)
+    assert spread("balanced") < spread("round_robin")
+    assert spread("balanced") <= max(ownership.ns_cost(s) for s in shapes)
+
+
+def _sharded_rank(rank, world, shapes, tmpdir, as_dtensor):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = "29871"
+    dist.init_process_group("gloo", init_method=f"file://{tmpdir}/pg", rank=rank, world_size=world)
+    try:
+        import muon_b200 as mb
+        from muon_b200 import engine as E
+        from muon_b200.sharded import shard_rows
+        E._set_backend_for_testing(OracleBackend())
+        p0, grads = _make_problem(shapes)
+
+        def piece(t):
+            chunk, mine = shard_rows(t.shape[0], world, rank)
+            return t[rank * chunk: rank * chunk + mine].clone()
+
+        if as_dtensor:
+            from torch.distributed.tensor import Shard, distribute_tensor, init_device_mesh
+            mesh = init_device_mesh("cpu", (world,))
+            params = [torch.nn.Parameter(distribute_tensor(p.clone(), mesh, [Shard(0)])) for p in p0]
+            opt = mb.ShardedMuon(list(params), lr=0.02, weight_decay=0.01)
+        else:
+            params = [torch.nn.Parameter(piece(p)) for p in p0]
+            opt = mb.ShardedMuon(list(params), lr=0.02, weight_decay=0.01, full_shapes=shapes)
+        skip_grad_for = 1
+        for step_grads in grads:
+            for i, (p, gr) in enumerate(zip(params, step_grads)):
+                if i == skip_grad_for:
+                    p.grad = None
+                elif as_dtensor:
+                    p.grad = distribute_tensor(gr.clone(), mesh, [Shard(0)])
+                else:
+                    p.grad = piece(gr)
+            opt.step()
+        local = [(p.to_local() if as_dtensor else p).detach().clone() for p in params]
+        has_state = [i for i, p in enumerate(params) if len(opt.state[p]) > 0]
+        torch.save(dict(local=local, has_state=has_state), f"{tmpdir}/out{rank}.pt")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,as_dtensor", [(2, False), (3, False), (2, True)])
+def test_sharded_muon_on_gloo_ranks(tmp_path, world, as_dtensor):
+    """Row-sharded parameters (plain shards with full shapes, or DTensor Shard(0)): gradients go to
+    the owners, updates come back in bf16, every rank updates its rows. The shards must be the
+    rows of the single-device result bit for bit, also where the rows do not divide evenly (one
+    rank short, one rank empty) and for a parameter that never gets a gradient."""
+    from muon_b200.sharded import shard_rows
+    shapes = [(24, 48)] * 3 + [(50, 24)] * 2 + [(4, 16)] * 2 + [(8, 4, 3, 3)]
+    mp.spawn(_sharded_rank, args=(world, shapes, str(tmp_path), as_dtensor), nprocs=world, join=True)
+    outs = [torch.load(f"{tmp_path}/out{r}.pt", weights_only=False) for r in range(world)]
+    ref = _single_device_oracle(shapes)
+    owners_state = set()
+    for r, o in enumerate(outs):
+        for i, (piece, full) in enumerate(zip(o["local"], ref)):
+            chunk, mine = shard_rows(full.shape[0], world, r)
+            assert torch.equal(piece, full[r * chunk: r * chunk + mine]), f"rank {r}, parameter {i}"
+        assert not owners_state & set(o["has_state"]), "a momentum buffer lives on exactly one rank"
+        owners_state |= set(o["has_state"])
+    assert owners_state == set(range(len(shapes)))
 
 
 def _fixture_rank(rank, world, tmpdir, fixture_path):

@@ -62,6 +62,27 @@ def test_ownership_rule(shapes, world):
         assert [i for i, o in enumerate(owners) if o == r] == list(range(r, n, world))
 
 
+@settings(max_examples=100, deadline=None)
+@given(shapes=st.lists(st.tuples(st.integers(1, 40), st.integers(1, 40)), min_size=1, max_size=30),
+       world=st.integers(1, 9))
+def test_balanced_ownership(shapes, world):
+    """Every parameter has exactly one owner; the assignment is a function of the shape list alone;
+    greedy assignment in order of decreasing cost keeps the heaviest rank within one parameter of
+    the lightest: max load - min load <= the largest single cost (and <= the cost of the parameter
+    that was placed last on the heaviest rank)."""
+    from muon_b200 import ownership
+    shapes = sorted(shapes, reverse=True)
+    who = ownership.owners(shapes, world, "balanced")
+    assert len(who) == len(shapes) and all(0 <= r < world for r in who)
+    assert who == ownership.owners(list(shapes), world, "balanced")
+    cost = [ownership.ns_cost(s) for s in shapes]
+    load = [sum(c for c, w in zip(cost, who) if w == r) for r in range(world)]
+    assert max(load) - min(load) <= max(cost)
+    assert ownership.owners(shapes, world, "round_robin") == [i % world for i in range(len(shapes))]
+    m, n = min(shapes[0]), max(shapes[0])
+    assert ownership.ns_cost(shapes[0]) == m * (m + 1) * n + m * m * (m + 1) + 2 * m * m * n
+
+
 @settings(max_examples=40, deadline=None)
 @given(m=st.integers(1, 70), seed=st.integers(0, 2 ** 16), tile=st.sampled_from([8, 16, 64]))
 def test_mirror_rules(m, seed, tile):
