@@ -143,6 +143,18 @@ int muon_b200_timing_collect_records(int max_records, int* kinds, int64_t* tags,
 int muon_b200_ns_line1(const void* x, int64_t ldx, int64_t x_bs, void* a_out, int64_t lda,
                        int64_t a_bs, int batch, int64_t m, int64_t k, muon_b200_stream_t stream);
 
+/* muon_b200_ns_line1 with a scratch area: when the product has so few output tiles that most SMs
+ * would idle (one or a few matrices of a few hundred rows with a long k), the contraction is cut
+ * into slices that run on different SMs, their fp32 partial sums go to `scratch`, and a second
+ * launch adds them in slice order and stores the result (deterministic; differs from the unsplit
+ * product only by the order of the fp32 additions). scratch: 256-byte aligned, at least
+ * muon_b200_ns_line1_scratch_bytes(batch, m, k) bytes (0 = this size is never split); NULL or too
+ * small: same as muon_b200_ns_line1. The workspaces of muon_b200_ns_run include this area. */
+int muon_b200_ns_line1_scratch(const void* x, int64_t ldx, int64_t x_bs, void* a_out, int64_t lda,
+                               int64_t a_bs, int batch, int64_t m, int64_t k, void* scratch,
+                               int64_t scratch_bytes, muon_b200_stream_t stream);
+int64_t muon_b200_ns_line1_scratch_bytes(int batch, int64_t m, int64_t k);
+
 /* B[b] = alpha · A[b] · A[b]ᵀ + beta · A[b], A is m x m. Only the lower triangle of the
  * product is computed and it is mirrored; the addend beta·A is taken per element, so A
  * may be non-symmetric. With a_is_symmetric != 0 the caller asserts A == Aᵀ bit for bit
@@ -173,6 +185,9 @@ typedef struct muon_b200_ns_layout {
   /* MUON_B200_NS_CLASSIC5 only (0 otherwise): sumsq_bs floats per matrix, starting at
    * sumsq_offset_bytes, for the sums of squares that muon_b200_prologue_sumsq leaves */
   int64_t sumsq_offset_bytes, sumsq_bs;
+  /* fp32 partial sums of the Gram products that are split along K (only for launches with few
+   * tiles: one or a few small matrices; 0 bytes otherwise) */
+  int64_t splitk_offset_bytes, splitk_bytes;
 } muon_b200_ns_layout;
 
 /* Layout for MUON_B200_NS_AOL4; also enough for MUON_B200_NS_CLASSIC5 without

@@ -37,7 +37,7 @@ class NsLayout(ctypes.Structure):
     _fields_ = [(name, c_int64) for name in (
         "total_bytes", "x_offset_bytes", "c_offset_bytes", "a_offset_bytes", "b_offset_bytes",
         "partials_offset_bytes", "ldn", "x_bs", "ldm", "a_bs", "x8_offset_bytes", "e8_offset_bytes",
-        "ld8n", "ld8m", "sumsq_offset_bytes", "sumsq_bs")]
+        "ld8n", "ld8m", "sumsq_offset_bytes", "sumsq_bs", "splitk_offset_bytes", "splitk_bytes")]
 
 
 # name -> (restype, argtypes); mirrors include/muon_b200.h one to one.
@@ -72,6 +72,9 @@ PROTOTYPES = {
                                                  POINTER(c_double), POINTER(c_int)]),
     "muon_b200_ns_line1": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int,
                                    c_int64, c_int64, c_void_p]),
+    "muon_b200_ns_line1_scratch": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int,
+                                           c_int64, c_int64, c_void_p, c_int64, c_void_p]),
+    "muon_b200_ns_line1_scratch_bytes": (c_int64, [c_int, c_int64, c_int64]),
     "muon_b200_ns_line2": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int,
                                    c_int64, c_float, c_float, c_int, c_void_p]),
     "muon_b200_ns_line3": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p,

@@ -119,6 +119,21 @@ int muon_b200_ns_line1(const void* x, int64_t ldx, int64_t x_bs, void* a_out, in
                         m, m, k, 1.f, 0.f, 1, as_stream(stream));
 }
 
+int64_t muon_b200_ns_line1_scratch_bytes(int batch, int64_t m, int64_t k) {
+  return splitk_scratch_bytes(batch, m, k);
+}
+
+int muon_b200_ns_line1_scratch(const void* x, int64_t ldx, int64_t x_bs, void* a_out, int64_t lda,
+                               int64_t a_bs, int batch, int64_t m, int64_t k, void* scratch,
+                               int64_t scratch_bytes, muon_b200_stream_t stream) {
+  SplitK sk;
+  sk.partial = static_cast<float*>(scratch);
+  sk.bytes = scratch ? scratch_bytes : 0;
+  return launch_ns_gemm(MODE_SYRK, bf(x), ldx, x_bs, bf(x), ldx, x_bs, bf(a_out), lda, a_bs, batch,
+                        m, m, k, 1.f, 0.f, 1, as_stream(stream), nullptr, nullptr, 0, nullptr, nullptr, nullptr,
+                        &sk);
+}
+
 int muon_b200_ns_line2(const void* a, int64_t lda, int64_t a_bs, void* b_out, int64_t ldb,
                        int64_t b_bs, int batch, int64_t m, float alpha, float beta,
                        int a_is_symmetric, muon_b200_stream_t stream) {
@@ -174,6 +189,10 @@ int muon_b200_ns_workspace_layout_mode(int batch, int64_t m, int64_t n, int mode
     l.sumsq_bs = classic_tiles_max(m, n);
     l.total_bytes += ns_classic_extra_bytes(batch, m, n);
   }
+  // launches of line 1 with few tiles are split along K (any mode): room for their partial sums
+  l.splitk_bytes = splitk_scratch_bytes(batch, m, n);
+  l.splitk_offset_bytes = l.splitk_bytes > 0 ? l.total_bytes : 0;
+  l.total_bytes += round_up(l.splitk_bytes, 256);
   *out = l;
   return OK;
 }
@@ -211,6 +230,10 @@ int workspace_buffers(void* workspace, int batch, int64_t m, int64_t n, int mode
   buf.fscratch = reinterpret_cast<float*>(ws + l.partials_offset_bytes);
   buf.f_bs = l.ldm;
   buf.fro_scales = fro_scales_in(buf.fscratch, batch, l.ldm);
+  if (l.splitk_bytes > 0) {
+    buf.splitk = reinterpret_cast<float*>(ws + l.splitk_offset_bytes);
+    buf.splitk_bytes = l.splitk_bytes;
+  }
   *out = buf;
   if (layout) *layout = l;
   return OK;

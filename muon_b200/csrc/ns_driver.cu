@@ -54,13 +54,17 @@ int ns_iterate(const NsBuffers& buf, int batch, int64_t m, int64_t n, int mode, 
   // Power-of-two scales of the e4m3 copies. Rows of X have norm about 1 after the rescale, so its
   // entries are about 1/sqrt(n): sx brings them to about 1 (and a whole row's norm stays below the
   // e4m3 maximum of 448). E = A - I has entries well below 1: se = 64.
+  SplitK sk;
+  sk.partial = buf.splitk;
+  sk.bytes = buf.splitk_bytes;
   float sx = 1.f;
   while (sx < 256.f && sx * sx * 2.f <= (float)n) sx *= 2.f;  // 2^round(log2(sqrt(n))), capped
   const float se = 64.f;
   if (mode != MUON_B200_NS_CLASSIC5) {
     // Gram matrix once, shared by the rescale and the first iteration (muon.py:778-785).
     rc = launch_ns_gemm(MODE_SYRK, buf.x[0], buf.ldx[0], buf.x_bs[0], buf.x[0], buf.ldx[0], buf.x_bs[0],
-                        buf.A, buf.ldm, buf.a_bs, batch, m, m, n, 1.f, 0.f, ADD_SYMMETRIC, st);
+                        buf.A, buf.ldm, buf.a_bs, batch, m, m, n, 1.f, 0.f, ADD_SYMMETRIC, st, nullptr, nullptr,
+                        0, nullptr, nullptr, nullptr, &sk);
     if (rc != OK) return rc;
     // A / s goes to its own buffer with A's pitches, so the symmetric unscaled A and 1/s remain
     // for line 2's epilogue.
@@ -141,7 +145,7 @@ int ns_iterate(const NsBuffers& buf, int batch, int64_t m, int64_t n, int mode, 
     } else {
       rc = launch_ns_gemm(MODE_SYRK, X, ldx, xbs, X, ldx, xbs, buf.A, buf.ldm, buf.a_bs, batch, m, m, n,
                           1.f, 0.f, ADD_SYMMETRIC, st, nullptr, nullptr, 0, nullptr, nullptr,
-                          classic && k == 0 ? buf.fro_scales + batch : nullptr);
+                          classic && k == 0 ? buf.fro_scales + batch : nullptr, &sk);
       if (rc != OK) return rc;
       // A comes straight from line 1 and is exactly symmetric.
       rc = launch_ns_gemm(MODE_AXPBY, buf.A, buf.ldm, buf.a_bs, buf.A, buf.ldm, buf.a_bs, buf.B, buf.ldm,
@@ -179,7 +183,8 @@ int64_t ns_scratch_bytes(int batch, int64_t m, int64_t n, int mode) {
   const int64_t as = round_up_i64(batch * m * ldm * 2, 256);
   const int64_t per_matrix = ldm > kFroChunksMax ? ldm : kFroChunksMax;
   return xs + 3 * as + round_up_i64((int64_t)batch * per_matrix * 4, 256) +
-         (mode == MUON_B200_NS_AOL4_FP8 ? ns_fp8_extra_bytes(batch, m, n) : 0);
+         (mode == MUON_B200_NS_AOL4_FP8 ? ns_fp8_extra_bytes(batch, m, n) : 0) +
+         round_up_i64(splitk_scratch_bytes(batch, m, n), 256);
 }
 
 int ns_run_with_scratch(const void* src, int dtype, int64_t rows, int64_t cols, int64_t ld_src,
@@ -221,6 +226,12 @@ int ns_run_with_scratch(const void* src, int dtype, int64_t rows, int64_t cols, 
   // (classic iteration: the caller's matrices arrive through the cast kernel, so the driver sums
   // over X itself; tile_sumsq stays null)
   buf.fro_scales = fro_scales_in(buf.fscratch, batch, ldm);
+  buf.splitk_bytes = splitk_scratch_bytes(batch, m, n);
+  if (buf.splitk_bytes > 0) {
+    const int64_t per_matrix = ldm > kFroChunksMax ? ldm : kFroChunksMax;
+    buf.splitk = reinterpret_cast<float*>(scratch + xs + 3 * as + round_up_i64((int64_t)batch * per_matrix * 4, 256) +
+                                          (mode == MUON_B200_NS_AOL4_FP8 ? ns_fp8_extra_bytes(batch, m, n) : 0));
+  }
   // muon.py:760-764: cast, transposition of tall inputs, contiguous copy.
   int rc = launch_cast_bf16(src, dtype, ld_src, src_bs, buf.x[0], buf.ldx[0], buf.x_bs[0], (int)rows,
                             (int)cols, batch, tall ? 1 : 0, 1.0f, st);

@@ -46,6 +46,10 @@ struct NsBuffers {
   const float* tile_sumsq;
   int64_t tile_bs;
   int64_t tile_count;
+  // fp32 partial sums of a line 1 that is split along K (launches with few tiles; see SplitK in
+  // ns_gemm.h), splitk_bytes of them; null: never split.
+  float* splitk;
+  int64_t splitk_bytes;
 };
 
 // Floats per matrix of the fp32 area, and where the classic iteration keeps its two factors per

@@ -397,7 +397,14 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   // One shared-memory stage holds 128 bytes of K per row: 64 bf16 or 128 e4m3 elements.
   constexpr int KSTEP = VAR == F8_OPERANDS ? 2 * BK : BK;
   const int k_blocks = (p.K + KSTEP - 1) / KSTEP;
-  const int total_tiles = p.tiles_per_batch * p.batch;
+  // Split-K (line 1 of launches with far fewer tiles than SMs, see launch_ns_gemm): a work item is
+  // then one K-slice of a tile (phase 1: fp32 partial sums go to p.partial) or one 32-column chunk
+  // of a tile (phase 2: the slices of the chunk are added in order and stored like a finished
+  // accumulator). Otherwise a work item is a tile.
+  constexpr bool kCanSplit = MODE == MODE_SYRK && VAR == F8_NONE;
+  const int split_phase = kCanSplit ? p.split_phase : 0;
+  const int work_per_tile = split_phase == 1 ? p.split_k : (split_phase == 2 ? BN / 32 : 1);
+  const int total_tiles = p.tiles_per_batch * p.batch * work_per_tile;
   const int work0 = blockIdx.x / CTAS;
   const int work_stride = gridDim.x / CTAS;
 
@@ -407,11 +414,13 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = work0; t < total_tiles && ok; t += work_stride) {
-        const TileCoord tc = decode_tile<TILE_M>(t, p);
+      for (int t = work0; t < total_tiles && ok && split_phase != 2; t += work_stride) {
+        const TileCoord tc = decode_tile<TILE_M>(t / work_per_tile, p);
         const int a_row = tc.tm * TILE_M + (int)cta_rank * BM;
         const int b_row = tc.tn * BN + (int)cta_rank * C::B_ROWS;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        const int kb_first = split_phase == 1 ? (t % work_per_tile) * p.split_kb : 0;
+        const int kb_last = split_phase == 1 && kb_first + p.split_kb < k_blocks ? kb_first + p.split_kb : k_blocks;
+        for (int kb = kb_first; kb < kb_last; ++kb) {
           const bool freed = CTAS == 2 ? mbar_wait_bounded_cluster(empty_bar(stage), phase ^ 1u, &s_abort)
                                        : mbar_wait_bounded(empty_bar(stage), phase ^ 1u, &s_abort);
           if (!freed) {
@@ -467,9 +476,11 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
-      for (int t = work0; t < total_tiles && ok; t += work_stride, ++local) {
+      for (int t = work0; t < total_tiles && ok && split_phase != 2; t += work_stride, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1u;
+        const int kb_first = split_phase == 1 ? (t % work_per_tile) * p.split_kb : 0;
+        const int kb_last = split_phase == 1 && kb_first + p.split_kb < k_blocks ? kb_first + p.split_kb : k_blocks;
         const bool drained = CTAS == 2
                                  ? mbar_wait_bounded_cluster(tempty_bar(acc), acc_phase ^ 1u, &s_abort)
                                  : mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, &s_abort);
@@ -480,7 +491,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = kb_first; kb < kb_last; ++kb) {
           const bool filled = CTAS == 2 ? mbar_wait_bounded_cluster(full_bar(stage), phase, &s_abort)
                                         : mbar_wait_bounded(full_bar(stage), phase, &s_abort);
           if (!filled) {
@@ -502,7 +513,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const uint64_t a_adv = static_cast<uint64_t>((kk * UMMA_K * 2) >> 4);
             const uint64_t b_adv = B_MN ? static_cast<uint64_t>((kk * UMMA_K * 128) >> 4)
                                         : static_cast<uint64_t>((kk * UMMA_K * 2) >> 4);
-            const uint32_t accumulate = (kb | kk) != 0 ? 1u : 0u;
+            const uint32_t accumulate = (kb != kb_first || kk != 0) ? 1u : 0u;
             // 32 bytes of K per instruction either way: 16 bf16 or 32 e4m3 elements.
             if constexpr (VAR == F8_OPERANDS) {
               if (CTAS == 2) umma_f8_ss_pair(d_tmem, a_desc + a_adv, b_desc + b_adv, idesc, accumulate);
@@ -539,13 +550,15 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int c_begin = ((warp - 2) >> 2) * CHUNKS;
     int local = 0;
     for (int t = work0; t < total_tiles; t += work_stride, ++local) {
-      const TileCoord tc = decode_tile<TILE_M>(t, p);
+      const TileCoord tc = decode_tile<TILE_M>(t / work_per_tile, p);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1u;
-      int ok = (CTAS == 2 ? mbar_wait_bounded_cluster(tfull_bar(acc), acc_phase, &s_abort)
-                          : mbar_wait_bounded(tfull_bar(acc), acc_phase, &s_abort))
-                   ? 1
-                   : 0;
+      int ok = 1;
+      if (split_phase != 2)  // (phase 2 reads partial sums from memory: no accumulator to wait for)
+        ok = (CTAS == 2 ? mbar_wait_bounded_cluster(tfull_bar(acc), acc_phase, &s_abort)
+                        : mbar_wait_bounded(tfull_bar(acc), acc_phase, &s_abort))
+                 ? 1
+                 : 0;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         if (lane == 0) {
@@ -600,7 +613,29 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const bool full = chunk_full(c);
         uint32_t v[32];
         __syncwarp();  // tcgen05.ld is warp-collective: reconverge after the predicated stores
-        tmem_ld_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, v);
+        if constexpr (kCanSplit) {
+          if (split_phase == 2) {
+            // Work item = chunk (t % 8) of the tile: add its K-slices in slice order. A chunk of a
+            // slice is 32 columns x 32 rows of fp32 with the rows (lanes) contiguous.
+            if (c != t % work_per_tile) continue;
+            const long long tile_index = t / work_per_tile;
+            float sum[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) sum[j] = 0.f;
+            for (int sl = 0; sl < p.split_k; ++sl) {
+              const float* src = p.partial +
+                  ((((tile_index * p.split_k + sl) * CTAS + cta_rank) * 4 + q) * (BN / 32) + c) * 1024 + lane;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) sum[j] += __ldcg(src + j * 32);
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(sum[j]);
+          } else {
+            tmem_ld_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, v);
+          }
+        } else {
+          tmem_ld_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, v);
+        }
         uint32_t add_next[MODE == MODE_SYRK ? 1 : 16] = {};
         const bool more = MODE != MODE_SYRK && c + 1 < c_begin + CHUNKS && chunk_live(c + 1);
         if constexpr (MODE != MODE_SYRK) {
@@ -614,6 +649,16 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         float f[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+        if constexpr (kCanSplit) {
+          if (split_phase == 1) {
+            // this slice's share of the chunk, as it is: phase 2 adds the slices and stores
+            float* dst = p.partial +
+                (((static_cast<long long>(t) * CTAS + cta_rank) * 4 + q) * (BN / 32) + c) * 1024 + lane;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) dst[j * 32] = f[j];
+            continue;
+          }
+        }
         float a[MODE == MODE_SYRK ? 1 : 32];
         if constexpr (MODE != MODE_SYRK) {
           if (full) {
@@ -951,7 +996,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       // Accumulator drained: hand it back to the MMA warp (of the pair's leader).
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
+      if (lane == 0 && split_phase != 2) {
         if (CTAS == 2) mbar_arrive_remote(map_to_cta(tempty_bar(acc), 0));
         else mbar_arrive(tempty_bar(acc));
       }
@@ -1072,7 +1117,8 @@ int launch_instance(int dev, int sms, const CUtensorMap& ta, const CUtensorMap& 
   using C = Cfg<CTAS>;
   auto kern = ns_gemm_kernel<MODE, B_MN, CTAS, EW, ADD, F8>;
   const int slot = (((MODE * 2 + (CTAS - 1)) * 2 + (EW == 4 ? 0 : 1)) * 3 + ADD) * 7 + F8;
-  const long long total = (long long)p.tiles_per_batch * p.batch;
+  const long long total = (long long)p.tiles_per_batch * p.batch *
+                          (p.split_phase == 1 ? p.split_k : p.split_phase == 2 ? BN / 32 : 1);
 
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(num_threads(EW));
@@ -1117,7 +1163,7 @@ int launch_instance(int dev, int sms, const CUtensorMap& ta, const CUtensorMap& 
   cfg.gridDim = dim3(units * CTAS);
   {
     const double m = p.M, n = p.N, k = p.K, b = p.batch;
-    const double flops = MODE == MODE_BX ? 2.0 * m * k * n * b : m * (m + 1.0) * k * b;
+    const double flops = p.split_phase == 2 ? 0.0 : MODE == MODE_BX ? 2.0 * m * k * n * b : m * (m + 1.0) * k * b;
     const int64_t tag = ((int64_t)p.M << 40) | ((int64_t)(MODE == MODE_BX ? p.N : p.K) << 16) | ((int64_t)(p.batch & 0xfff) << 4) |
                         (p.sym_add == ADD_SYMMETRIC ? 1 : 0) | (CTAS == 2 ? 2 : 0) |
                         (p.sym_add == ADD_ROW_SCALED ? 4 : 0) | (EW >= 8 ? 8 : 0);
@@ -1180,6 +1226,50 @@ int launch_epi(int ew, int f8, int dev, int sms, const CUtensorMap& ta, const CU
 
 }  // namespace
 
+namespace {
+// Lower-triangle tile count of an m x m product and the tile geometry launch_ns_gemm picks.
+int tri_tile_count(int64_t m, int* ctas_out) {
+  int ctas = forced_ctas();
+  if (ctas == 0) ctas = m > BM ? 2 : 1;
+  const int tile_m = BM * ctas;
+  const int tiles_m = (int)((m + tile_m - 1) / tile_m), tiles_n = (int)((m + BN - 1) / BN);
+  int cnt = 0;
+  for (int i = 0; i < tiles_m; ++i) cnt += tri_row_count(i, tiles_n, tile_m);
+  if (ctas_out) *ctas_out = ctas;
+  return cnt;
+}
+constexpr int kSplitSms = 148;       // SMs of the GPU the split is sized for (a B200)
+constexpr int kSplitMinSlices = 3;   // below that a split does not pay for its second launch
+constexpr int kSplitMaxSlices = 16;
+constexpr int kSplitMinBlocks = 4;   // k-blocks (of 64) per slice at least
+}  // namespace
+
+int splitk_slices(int batch, int64_t m, int64_t k) {
+  static const bool off = [] {
+    const char* e = std::getenv("MUON_B200_SPLITK");
+    return e && (e[0] == '0' || e[0] == 'n' || e[0] == 'f');
+  }();
+  if (off || batch < 1 || m < 1 || k < 1) return 1;
+  int ctas = 1;
+  const long long tiles = (long long)tri_tile_count(m, &ctas) * batch;
+  const int units = kSplitSms / ctas;
+  const int k_blocks = (int)((k + BK - 1) / BK);
+  long long want = units / tiles;
+  if (want > k_blocks / kSplitMinBlocks) want = k_blocks / kSplitMinBlocks;
+  if (want > kSplitMaxSlices) want = kSplitMaxSlices;
+  if (want < kSplitMinSlices) return 1;
+  const int per = (k_blocks + (int)want - 1) / (int)want;
+  return (k_blocks + per - 1) / per;  // every slice has at least one k-block
+}
+
+int64_t splitk_scratch_bytes(int batch, int64_t m, int64_t k) {
+  const int s = splitk_slices(batch, m, k);
+  if (s <= 1) return 0;
+  int ctas = 1;
+  const long long tiles = (long long)tri_tile_count(m, &ctas) * batch;
+  return tiles * s * ctas * (int64_t)(BM * BN * 4);
+}
+
 bool update_fusable(const UpdateSpec& u, int batch) {
   if (!u.param || batch < 1 || batch > kMaxUpdateTensors || u.rows < 1 || u.cols < 1) return false;
   const bool tall = u.rows > u.cols;
@@ -1225,7 +1315,7 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
                    int64_t ldo, int64_t out_bs, int batch, int64_t M, int64_t N, int64_t K,
                    float alpha, float beta, int sym_add, cudaStream_t stream, const __nv_bfloat16* addend,
                    const float* row_scale, int64_t scale_bs, const Fp8Spec* f8, const UpdateSpec* upd,
-                   const float* batch_scale) {
+                   const float* batch_scale, const SplitK* split) {
   if (!opa || !opb || !out) return set_error(ERR_INVALID_ARG, "null pointer passed to NS GEMM");
   if (batch < 1 || M < 1 || N < 1 || K < 1)
     return set_error(ERR_INVALID_ARG, "NS GEMM needs batch, M, N, K >= 1 (got %d, %lld, %lld, %lld)",
@@ -1346,6 +1436,23 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
   // waits for: eight warps.
   // (with e4m3 operands a tile's main loop takes half as long: the threshold doubles)
   if (ew == 0) ew = K >= (f8_kind == F8_OPERANDS ? 2 * kLongK : kLongK) ? 4 : 8;
+  if (split && split->partial && mode == MODE_SYRK && f8_kind == F8_NONE) {
+    const int slices = splitk_slices(batch, M, K);
+    if (slices > 1 && split->bytes >= splitk_scratch_bytes(batch, M, K) &&
+        (reinterpret_cast<uintptr_t>(split->partial) & 15) == 0) {
+      const int k_blocks = (int)((K + BK - 1) / BK);
+      p.split_k = slices;
+      p.split_kb = (k_blocks + slices - 1) / slices;
+      p.partial = split->partial;
+      p.split_phase = 1;  // slices -> partial sums; a slice is short: eight epilogue warps
+      rc = ctas == 2 ? launch_epi<MODE_SYRK, false, 2>(8, f8_kind, dev, sms, ta, tb, p, stream)
+                     : launch_epi<MODE_SYRK, false, 1>(8, f8_kind, dev, sms, ta, tb, p, stream);
+      if (rc != OK) return rc;
+      p.split_phase = 2;  // partial sums -> bf16 blocks and their mirror images
+      return ctas == 2 ? launch_epi<MODE_SYRK, false, 2>(8, f8_kind, dev, sms, ta, tb, p, stream)
+                       : launch_epi<MODE_SYRK, false, 1>(8, f8_kind, dev, sms, ta, tb, p, stream);
+    }
+  }
   if (ctas == 2) {
     switch (mode) {
       case MODE_SYRK: return launch_epi<MODE_SYRK, false, 2>(ew, f8_kind, dev, sms, ta, tb, p, stream);

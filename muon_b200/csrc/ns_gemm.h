@@ -92,7 +92,26 @@ struct GemmParams {
   float upd_scale, upd_decay, upd_neg_lr;
   // V_BATCH_SCALE: one factor per matrix of the batch
   const float* batch_scale;
+  // Split-K of line 1 (see SplitK): 0 = none; 1 = every work item is one of split_k K-slices
+  // (split_kb k-blocks each) of a tile and leaves fp32 partial sums in `partial`; 2 = every work
+  // item is a 32-column chunk of a tile whose slices are added and stored.
+  int split_phase, split_k, split_kb;
+  float* partial;
 };
+
+// Scratch for split-K: a launch of line 1 whose tiles would occupy less than a third of the SMs
+// (one or a few small matrices with a long K) is cut along K into slices that run on different
+// SMs; a second launch of the same kernel adds the slices of every 32 x 32 block in slice order
+// (so the result does not depend on scheduling) and stores the block and its mirror image.
+struct SplitK {
+  float* partial = nullptr;  // 256-byte aligned
+  int64_t bytes = 0;
+};
+// Slices launch_ns_gemm would use for line 1 of `batch` m x m products with contraction length k
+// (1 = no split), and the scratch bytes that takes; both functions of the sizes only (sized for
+// the 148 SMs of a B200, so that layouts can be computed without a device).
+int splitk_slices(int batch, int64_t m, int64_t k);
+int64_t splitk_scratch_bytes(int batch, int64_t m, int64_t k);
 
 int device_sm_count(int* sm_count_out);
 // Whether kernels that support it are launched with programmatic stream serialization.
@@ -106,6 +125,6 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
                    float alpha, float beta, int sym_add, cudaStream_t stream,
                    const __nv_bfloat16* addend = nullptr, const float* row_scale = nullptr,
                    int64_t scale_bs = 0, const Fp8Spec* f8 = nullptr, const UpdateSpec* upd = nullptr,
-                   const float* batch_scale = nullptr);
+                   const float* batch_scale = nullptr, const SplitK* split = nullptr);
 
 }  // namespace mb

@@ -53,8 +53,13 @@ def ns_line_1(A: Tensor, *, out: Tensor = None) -> Tensor:
         assert out.size(-1) == M, "Output matrix has incorrect shape"
     buf, user = _out_3d(out, A, (batch, M, M))
     with torch.cuda.device(A.device):
-        check(lib.muon_b200_ns_line1(A3.data_ptr(), A3.stride(-2), A3.stride(0), buf.data_ptr(),
-                                     buf.stride(-2), buf.stride(0), batch, M, K, _stream_ptr(A.device)))
+        # a product with few output tiles and a long K is split along K: room for its partial sums
+        need = lib.muon_b200_ns_line1_scratch_bytes(batch, M, K)
+        backend = get_backend()
+        scratch = backend._aligned_ptr(backend.workspace(A.device, need, slot=4)) if need > 0 else None
+        check(lib.muon_b200_ns_line1_scratch(A3.data_ptr(), A3.stride(-2), A3.stride(0), buf.data_ptr(),
+                                             buf.stride(-2), buf.stride(0), batch, M, K, scratch, need,
+                                             _stream_ptr(A.device)))
     return _finish(buf, user, A.ndim, (M, M))
 
 

@@ -165,6 +165,55 @@ def test_newton_schulz_classic5(mb, shape):
     assert hi < 1.25
 
 
+@pytest.mark.parametrize("shape", [(768, 3072), (2, 512, 4096), (1024, 8192), (100, 2050), (136, 1000), (3, 200, 1288)])
+def test_line_1_split_along_k(mb, shape):
+    """A Gram product with few output tiles and a long K is cut into K-slices that run on different
+    SMs; a second launch adds the slices in order. Against the same product computed in one piece:
+    exactly symmetric, equal to one rounding of the fp32 sum (the slices only change the order of
+    the fp32 additions: a handful of entries may round the other way, by one bf16 ulp), and the
+    same result on every run."""
+    from muon_b200 import _lib
+    lib, check = _lib.lib, _lib.check
+    g = torch.Generator().manual_seed(77)
+    X = (torch.randn(shape, generator=g) / shape[-1] ** 0.5).bfloat16().to(DEV)
+    X3 = X if X.ndim == 3 else X[None]
+    batch, m, k = X3.shape
+    ld = (k + 7) // 8 * 8
+    if ld != k:
+        Xp = torch.zeros(batch, m, ld, dtype=torch.bfloat16, device=DEV)
+        Xp[:, :, :k] = X3
+        X3 = Xp[:, :, :k]
+    ldm = (m + 7) // 8 * 8
+    need = lib.muon_b200_ns_line1_scratch_bytes(batch, m, k)
+    assert need > 0, "these sizes are meant to be split"
+    scratch = torch.empty(need + 256, dtype=torch.uint8, device=DEV)
+    sptr = (scratch.data_ptr() + 255) // 256 * 256
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def run(with_scratch):
+        out = torch.full((batch, m, ldm), float("nan"), dtype=torch.bfloat16, device=DEV)
+        before = _lib.launch_counts()["ns_line1"]
+        check(lib.muon_b200_ns_line1_scratch(X3.data_ptr(), X3.stride(-2), X3.stride(0), out.data_ptr(), ldm, m * ldm,
+                                             batch, m, k, sptr if with_scratch else None, need if with_scratch else 0,
+                                             stream))
+        torch.cuda.synchronize()
+        return out[:, :, :m].float().cpu(), _lib.launch_counts()["ns_line1"] - before
+
+    whole, n_whole = run(False)
+    split, n_split = run(True)
+    again, _ = run(True)
+    assert (n_whole, n_split) == (1, 2)
+    assert mb.device_status() == 0
+    assert torch.equal(split, again)
+    assert torch.equal(split, split.transpose(-1, -2))
+    ref = orc.ns_line_1(X3.cpu()).float()
+    assert orc.rel_fro(split, ref) <= 2e-3 and orc.rel_fro(whole, ref) <= 2e-3
+    diff = (split - whole).abs()
+    assert (diff > 0).float().mean() <= 0.02                      # a few entries round the other way
+    # by one bf16 ulp at most (entries that cancel to almost nothing carry the fp32 sums' own error)
+    assert (diff <= 2.0 ** -7 * whole.abs() + 1e-6).all()
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(384, 1024), (1024, 384), (200, 328), (328, 200), (64, 32, 3, 3)])
 def test_update_left_in_memory_then_applied_by_rows(mb, shape, dtype):
