@@ -17,7 +17,9 @@ the gradients are restored from a device-resident pool (the Nesterov blend overw
 place, muon.py:10) and, for the small workloads, a buffer larger than L2 is written.
 
 At N = 1 the line also carries ``other_configs`` (the three small benchmark configurations: one
-768x3072 matrix, GPT-2-small hidden weights with aux Adam, batched conv filters; a few ms each) and
+768x3072 matrix, GPT-2-small hidden weights with aux Adam, batched conv filters, a few ms each;
+with the default workload also two layers of Llama-3-70B shapes and the default workload under the
+classic Frobenius-normalised iteration, three timed steps each) and
 ``reference_gpu``: step times of the unmodified reference (its torch.compile'd driver over its
 autotuned Triton kernels) on a B200, either measured in this run (``--reference-gpu live``, needs
 the reference installed under baseline/_ref and takes minutes to compile and autotune) or as
@@ -78,6 +80,14 @@ SMALL_CONFIGS = {
     "one-768x3072": ("one-768x3072", "SingleDeviceMuon", 0, 0.03),
     "gpt2-small-hidden": ("gpt2-small-hidden", "MuonWithAuxAdam", 25, 0.91),
     "conv-filters": ("conv-filters", "SingleDeviceMuon", 0, 0.28),
+}
+# Two more entries of `other_configs` when the default workload runs on one GPU, three timed steps
+# each: the Llama-3-70B shapes as far as one GPU holds them beside the main workload's leftovers
+# (2 of 80 layers), and the main workload with the classic Frobenius-normalised iteration
+# (name -> (workload, optimizer class, gain vectors, lower bound or None, NS mode or None = current)).
+LARGE_CONFIGS = {
+    "llama3-70b-2layers": ("llama3-70b-2layers", "SingleDeviceMuon", 0, None, None),
+    "llama3-8b-hidden/classic5": ("llama3-8b-hidden", "SingleDeviceMuon", 0, None, "classic5"),
 }
 # DRAM bytes (read + write) per matrix element that one launch of the line-3 kernel moved in an ncu
 # capture of that kernel on 8 matrices of 4096 x 14336: 2.120 GB read + 0.925 GB written (a later
@@ -211,12 +221,20 @@ def timed_steps(step, n_steps, device, barrier, outside=None, world=1):
 
 
 def run_small_config(name, device, ns_mode, steps=20, warmup=3):
-    """One of the three small benchmark configurations on one GPU: ms per step (device time, L2
+    """One of the other benchmark configurations on one GPU: ms per step (device time, L2
     flushed and gradients restored before every step), kernel launches per step, NS TFLOP/s over
     the step, and the host time it takes to issue a step."""
     import muon_b200
     from muon_b200 import _lib
-    workload, cls_name, n_gains, lower_ms = SMALL_CONFIGS[name]
+    if name in SMALL_CONFIGS:
+        workload, cls_name, n_gains, lower_ms = SMALL_CONFIGS[name]
+        own_mode = None
+    else:
+        workload, cls_name, n_gains, lower_ms, own_mode = LARGE_CONFIGS[name]
+    if own_mode is not None:
+        previous_mode = muon_b200.get_ns_mode()
+        muon_b200.set_ns_mode(own_mode)
+        ns_mode = own_mode
     shapes, dtype, grad_std, desc = WORKLOADS[workload]
     params = make_problem(shapes, dtype, device)
     gains = [torch.nn.Parameter(torch.ones(768, device=device)) for _ in range(n_gains)]
@@ -258,7 +276,11 @@ def run_small_config(name, device, ns_mode, steps=20, warmup=3):
            "gpu_launches_per_step": (sum(counts1.values()) - sum(counts0.values())) / steps,
            "ns_tflops_step": red / (ms * 1e-3) / 1e12, "host_issue_ms_per_step": host_ms,
            "lower_bound_ms": lower_ms, "l2_policy": "256 MB written between timed steps"}
+    if own_mode is not None:
+        out["ns_mode"] = own_mode
+        muon_b200.set_ns_mode(*previous_mode)
     del opt, params, gains, owned, pool, flush
+    muon_b200.get_backend().release_workspaces()
     torch.cuda.empty_cache()
     return out
 
@@ -421,6 +443,10 @@ def run_ours(args):
         torch.cuda.empty_cache()
         other_configs = {name: run_small_config(name, device, args.ns_mode) for name in SMALL_CONFIGS
                          if SMALL_CONFIGS[name][0] != args.workload}
+        if args.workload == "llama3-8b-hidden":
+            for name, cfg in LARGE_CONFIGS.items():
+                if cfg[4] is None or cfg[4] != args.ns_mode:
+                    other_configs[name] = run_small_config(name, device, args.ns_mode, steps=3, warmup=3)
         reference_gpu = live_reference_gpu(args.workload, device) if args.reference_gpu == "live" \
             else recorded_reference_gpu()
 

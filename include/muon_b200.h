@@ -149,7 +149,10 @@ int muon_b200_ns_line1(const void* x, int64_t ldx, int64_t x_bs, void* a_out, in
  * launch adds them in slice order and stores the result (deterministic; differs from the unsplit
  * product only by the order of the fp32 additions). scratch: 256-byte aligned, at least
  * muon_b200_ns_line1_scratch_bytes(batch, m, k) bytes (0 = this size is never split); NULL or too
- * small: same as muon_b200_ns_line1. The workspaces of muon_b200_ns_run include this area. */
+ * small: same as muon_b200_ns_line1. muon_b200_zeropower splits the same way inside its scratch
+ * area; muon_b200_ns_run, muon_b200_ns_run_update, muon_b200_muon_step and
+ * muon_b200_ns_run_static never split, so that what they compute for a matrix does not depend on
+ * how many matrices share the call. */
 int muon_b200_ns_line1_scratch(const void* x, int64_t ldx, int64_t x_bs, void* a_out, int64_t lda,
                                int64_t a_bs, int batch, int64_t m, int64_t k, void* scratch,
                                int64_t scratch_bytes, muon_b200_stream_t stream);
@@ -185,9 +188,6 @@ typedef struct muon_b200_ns_layout {
   /* MUON_B200_NS_CLASSIC5 only (0 otherwise): sumsq_bs floats per matrix, starting at
    * sumsq_offset_bytes, for the sums of squares that muon_b200_prologue_sumsq leaves */
   int64_t sumsq_offset_bytes, sumsq_bs;
-  /* fp32 partial sums of the Gram products that are split along K (only for launches with few
-   * tiles: one or a few small matrices; 0 bytes otherwise) */
-  int64_t splitk_offset_bytes, splitk_bytes;
 } muon_b200_ns_layout;
 
 /* Layout for MUON_B200_NS_AOL4; also enough for MUON_B200_NS_CLASSIC5 without

@@ -37,7 +37,7 @@ class NsLayout(ctypes.Structure):
     _fields_ = [(name, c_int64) for name in (
         "total_bytes", "x_offset_bytes", "c_offset_bytes", "a_offset_bytes", "b_offset_bytes",
         "partials_offset_bytes", "ldn", "x_bs", "ldm", "a_bs", "x8_offset_bytes", "e8_offset_bytes",
-        "ld8n", "ld8m", "sumsq_offset_bytes", "sumsq_bs", "splitk_offset_bytes", "splitk_bytes")]
+        "ld8n", "ld8m", "sumsq_offset_bytes", "sumsq_bs")]
 
 
 # name -> (restype, argtypes); mirrors include/muon_b200.h one to one.

@@ -189,10 +189,6 @@ int muon_b200_ns_workspace_layout_mode(int batch, int64_t m, int64_t n, int mode
     l.sumsq_bs = classic_tiles_max(m, n);
     l.total_bytes += ns_classic_extra_bytes(batch, m, n);
   }
-  // launches of line 1 with few tiles are split along K (any mode): room for their partial sums
-  l.splitk_bytes = splitk_scratch_bytes(batch, m, n);
-  l.splitk_offset_bytes = l.splitk_bytes > 0 ? l.total_bytes : 0;
-  l.total_bytes += round_up(l.splitk_bytes, 256);
   *out = l;
   return OK;
 }
@@ -230,10 +226,6 @@ int workspace_buffers(void* workspace, int batch, int64_t m, int64_t n, int mode
   buf.fscratch = reinterpret_cast<float*>(ws + l.partials_offset_bytes);
   buf.f_bs = l.ldm;
   buf.fro_scales = fro_scales_in(buf.fscratch, batch, l.ldm);
-  if (l.splitk_bytes > 0) {
-    buf.splitk = reinterpret_cast<float*>(ws + l.splitk_offset_bytes);
-    buf.splitk_bytes = l.splitk_bytes;
-  }
   *out = buf;
   if (layout) *layout = l;
   return OK;
@@ -313,7 +305,7 @@ int muon_b200_ns_run_update(void* workspace, int mode, int steps, const float* c
 }
 
 int64_t muon_b200_zeropower_scratch_bytes(int batch, int64_t rows, int64_t cols, int mode) {
-  return rows <= cols ? ns_scratch_bytes(batch, rows, cols, mode) : ns_scratch_bytes(batch, cols, rows, mode);
+  return rows <= cols ? ns_scratch_bytes(batch, rows, cols, mode, true) : ns_scratch_bytes(batch, cols, rows, mode, true);
 }
 
 int muon_b200_zeropower(const void* g, int dtype, int64_t rows, int64_t cols, int64_t ldg, int64_t g_bs,
@@ -334,13 +326,13 @@ int muon_b200_zeropower(const void* g, int dtype, int64_t rows, int64_t cols, in
     return set_error(ERR_INVALID_ARG, "zeropower: input pitch shorter than a row or a matrix");
   if (reinterpret_cast<uintptr_t>(scratch) & 255)
     return set_error(ERR_ALIGNMENT, "zeropower: scratch must be 256-byte aligned");
-  const int64_t need = ns_scratch_bytes(batch, m, n, mode);
+  const int64_t need = ns_scratch_bytes(batch, m, n, mode, true);
   if (scratch_bytes < need)
     return set_error(ERR_INVALID_ARG, "zeropower: scratch too small: %lld bytes given, %lld needed",
                      (long long)scratch_bytes, (long long)need);
   return ns_run_with_scratch(g, dtype, rows, cols, ldg, g_bs, bf(out), ldo, o_bs,
                              static_cast<unsigned char*>(scratch), batch, mode, steps, coeffs, eps,
-                             /*replay=*/true, as_stream(stream));
+                             /*replay=*/true, as_stream(stream), /*split_k=*/true);
 }
 
 int muon_b200_cast_bf16(const void* src, int dtype, int64_t rows, int64_t cols, int64_t ld_src,

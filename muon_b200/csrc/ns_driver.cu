@@ -176,7 +176,7 @@ int64_t ns_classic_extra_bytes(int batch, int64_t m, int64_t n) {
   return round_up_i64((int64_t)batch * classic_tiles_max(m, n) * 4, 256);
 }
 
-int64_t ns_scratch_bytes(int batch, int64_t m, int64_t n, int mode) {
+int64_t ns_scratch_bytes(int batch, int64_t m, int64_t n, int mode, bool split_k) {
   if (batch < 1 || m < 1 || n < m) return -1;
   const int64_t ldn = round_up_i64(n, 8), ldm = round_up_i64(m, 8);
   const int64_t xs = round_up_i64(batch * m * ldn * 2, 256);
@@ -184,13 +184,13 @@ int64_t ns_scratch_bytes(int batch, int64_t m, int64_t n, int mode) {
   const int64_t per_matrix = ldm > kFroChunksMax ? ldm : kFroChunksMax;
   return xs + 3 * as + round_up_i64((int64_t)batch * per_matrix * 4, 256) +
          (mode == MUON_B200_NS_AOL4_FP8 ? ns_fp8_extra_bytes(batch, m, n) : 0) +
-         round_up_i64(splitk_scratch_bytes(batch, m, n), 256);
+         (split_k ? round_up_i64(splitk_scratch_bytes(batch, m, n), 256) : 0);
 }
 
 int ns_run_with_scratch(const void* src, int dtype, int64_t rows, int64_t cols, int64_t ld_src,
                         int64_t src_bs, __nv_bfloat16* out, int64_t ldo, int64_t o_bs,
                         unsigned char* scratch, int batch, int mode, int steps, const float* coeffs,
-                        float eps, bool replay, cudaStream_t st) {
+                        float eps, bool replay, cudaStream_t st, bool split_k) {
   const bool tall = rows > cols;
   const int64_t m = tall ? cols : rows, n = tall ? rows : cols;
   const int64_t ldn = round_up_i64(n, 8), ldm = round_up_i64(m, 8);
@@ -226,7 +226,7 @@ int ns_run_with_scratch(const void* src, int dtype, int64_t rows, int64_t cols, 
   // (classic iteration: the caller's matrices arrive through the cast kernel, so the driver sums
   // over X itself; tile_sumsq stays null)
   buf.fro_scales = fro_scales_in(buf.fscratch, batch, ldm);
-  buf.splitk_bytes = splitk_scratch_bytes(batch, m, n);
+  buf.splitk_bytes = split_k ? splitk_scratch_bytes(batch, m, n) : 0;
   if (buf.splitk_bytes > 0) {
     const int64_t per_matrix = ldm > kFroChunksMax ? ldm : kFroChunksMax;
     buf.splitk = reinterpret_cast<float*>(scratch + xs + 3 * as + round_up_i64((int64_t)batch * per_matrix * 4, 256) +

@@ -47,7 +47,7 @@ struct NsBuffers {
   int64_t tile_bs;
   int64_t tile_count;
   // fp32 partial sums of a line 1 that is split along K (launches with few tiles; see SplitK in
-  // ns_gemm.h), splitk_bytes of them; null: never split.
+  // ns_gemm.h), splitk_bytes of them; null (every caller but the functional zeropower): never split.
   float* splitk;
   int64_t splitk_bytes;
 };
@@ -91,18 +91,23 @@ void set_graph_replay(bool on);
 bool graph_replay_enabled();
 
 // Bytes of scratch ns_run_with_scratch needs for `batch` matrices of m x n (m <= n): one
-// [batch, m, ldn] iterate buffer, three [batch, m, ldm] squares and the fp32 area. -1 on bad sizes.
-int64_t ns_scratch_bytes(int batch, int64_t m, int64_t n, int mode = 0);
+// [batch, m, ldn] iterate buffer, three [batch, m, ldm] squares, the fp32 area and, with
+// `split_k`, room for the partial sums of a Gram product that is split along K. -1 on bad sizes.
+int64_t ns_scratch_bytes(int batch, int64_t m, int64_t n, int mode = 0, bool split_k = false);
 
 // Newton-Schulz with caller-owned input and output and a scratch area of ns_scratch_bytes():
 // `src` ([batch, rows, cols], element type `dtype` (a DType), pitches in elements) is cast to bf16,
 // transposed when rows > cols, into whichever iterate buffer makes the result land in `out`
 // ([batch, m, n] bf16, m = min(rows, cols)); the iteration ping-pongs between `out` and the
-// scratch. `replay` allows graph replay (see ns_iterate_replayed).
+// scratch. `replay` allows graph replay (see ns_iterate_replayed). `split_k` allows line 1 to be
+// split along K when the launch has few tiles (SplitK in ns_gemm.h; the scratch must then have been
+// sized with split_k): a matrix's result then depends, in the order of its fp32 additions, on how
+// many matrices share the call, which is why only the functional entry point asks for it — the
+// optimizer step and the entry points that promise its arithmetic never do.
 int ns_run_with_scratch(const void* src, int dtype, int64_t rows, int64_t cols, int64_t ld_src,
                         int64_t src_bs, __nv_bfloat16* out, int64_t ldo, int64_t o_bs,
                         unsigned char* scratch, int batch, int mode, int steps, const float* coeffs,
-                        float eps, bool replay, cudaStream_t stream);
+                        float eps, bool replay, cudaStream_t stream, bool split_k = false);
 
 // Argument checks shared by both entry points: fills in the default step count.
 int ns_check_mode(int mode, int* steps, const float* coeffs);

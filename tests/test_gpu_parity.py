@@ -317,7 +317,9 @@ def test_newton_schulz_aol4_fp8(mb, shape):
     finally:
         mb.set_ns_mode("aol4")
     after = mb._lib.launch_counts()
-    assert after["ns_line1"] - before["ns_line1"] == 4 and after["ns_line3"] - before["ns_line3"] == 4
+    # four Gram products and four line 3; the first Gram product (bf16) is two launches when this
+    # functional call splits it along K
+    assert after["ns_line1"] - before["ns_line1"] in (4, 5) and after["ns_line3"] - before["ns_line3"] == 4
     assert U.shape == G.shape and U.dtype == torch.bfloat16 and torch.isfinite(U.float()).all()
     sim = orc.zeropower_aol4_fp8(G)
     ref = orc.zeropower_via_newtonschulz5(G)
