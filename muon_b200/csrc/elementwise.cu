@@ -24,7 +24,12 @@ template <>
 struct Vec<float> {
   static constexpr int N = 4;
   using Raw = float4;
-  __device__ static Raw load_raw(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  // (streaming loads and stores: the data is touched once and must not push the operands of GEMMs
+  // that run beside these kernels out of L2)
+  __device__ static Raw load_raw(const float* p) { return __ldcs(reinterpret_cast<const float4*>(p)); }
+  __device__ static void store_stream(float* p, const float (&v)[4]) {
+    __stcs(reinterpret_cast<float4*>(p), make_float4(v[0], v[1], v[2], v[3]));
+  }
   __device__ static void unpack(const Raw& r, float (&v)[4]) {
     v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
   }
@@ -40,7 +45,11 @@ template <>
 struct Vec<__nv_bfloat16> {
   static constexpr int N = 8;
   using Raw = uint4;
-  __device__ static Raw load_raw(const __nv_bfloat16* p) { return *reinterpret_cast<const uint4*>(p); }
+  __device__ static Raw load_raw(const __nv_bfloat16* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
+  __device__ static void store_stream(__nv_bfloat16* p, const float (&v)[8]) {
+    __stcs(reinterpret_cast<uint4*>(p), make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
+                                                   pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7])));
+  }
   __device__ static void unpack(const Raw& r, float (&v)[8]) {
     const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
@@ -211,8 +220,8 @@ prologue_kernel(const PrologueArgs a) {
           ss = fmaf(xv[j + 1], xv[j + 1], ss);
         }
         if (full) {
-          Vec<T>::store(m + off, mv);
-          if (a.nesterov) Vec<T>::store(g + off, gv);
+          Vec<T>::store_stream(m + off, mv);
+          if (a.nesterov) Vec<T>::store_stream(g + off, gv);
         } else {
 #pragma unroll
           for (int j = 0; j < V; ++j)

@@ -255,6 +255,26 @@ __device__ __forceinline__ void block_store_coal(__nv_bfloat16* base, long long 
     *reinterpret_cast<uint4*>(ptr + 8 * i * ld) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
 }
 
+// The same two for data that is touched exactly once by the launch (the parameters a fused update
+// reads and rewrites): streaming accesses, so that they do not push the operand matrices, which
+// every tile re-reads, out of L2.
+__device__ __forceinline__ void block_load_stream(const __nv_bfloat16* base, long long ld, int row0,
+                                                  int col0, int lane, uint32_t (&w)[16]) {
+  const __nv_bfloat16* ptr = base + (row0 + (lane >> 2)) * ld + col0 + (lane & 3) * 8;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint4 q = __ldcs(reinterpret_cast<const uint4*>(ptr + 8 * i * ld));
+    w[4 * i] = q.x; w[4 * i + 1] = q.y; w[4 * i + 2] = q.z; w[4 * i + 3] = q.w;
+  }
+}
+__device__ __forceinline__ void block_store_stream(__nv_bfloat16* base, long long ld, int row0, int col0,
+                                                   int lane, const uint32_t (&w)[16]) {
+  __nv_bfloat16* ptr = base + (row0 + (lane >> 2)) * ld + col0 + (lane & 3) * 8;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    __stcs(reinterpret_cast<uint4*>(ptr + 8 * i * ld), make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]));
+}
+
 // ---------------------------------------------------------------------------
 // e4m3 copies of an output block (see Fp8Spec in ns_gemm.h).
 // ---------------------------------------------------------------------------
@@ -315,7 +335,7 @@ __device__ __forceinline__ void block_load_coal_f32(const float* base, long long
   const float* ptr = base + (row0 + (lane >> 2)) * ld + col0 + (lane & 3) * 4;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const uint4 q = *reinterpret_cast<const uint4*>(ptr + 8 * i * ld);
+    const uint4 q = __ldcs(reinterpret_cast<const uint4*>(ptr + 8 * i * ld));
     w[4 * i] = q.x; w[4 * i + 1] = q.y; w[4 * i + 2] = q.z; w[4 * i + 3] = q.w;
   }
 }
@@ -324,7 +344,7 @@ __device__ __forceinline__ void block_store_coal_f32(float* base, long long ld, 
   float* ptr = base + (row0 + (lane >> 2)) * ld + col0 + (lane & 3) * 4;
 #pragma unroll
   for (int i = 0; i < 4; ++i)
-    *reinterpret_cast<uint4*>(ptr + 8 * i * ld) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+    __stcs(reinterpret_cast<uint4*>(ptr + 8 * i * ld), make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]));
 }
 
 // ADD: how line 2's addend is formed (AddendMode); the other two lines pass ADD_SYMMETRIC.
@@ -744,7 +764,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             __nv_bfloat16* pb = static_cast<__nv_bfloat16*>(p.upd_param[tc.batch]);
             if (full) {
               uint32_t pw[16], own[16];
-              block_load_coal(pb, p.N, row_base, col0, lane, pw);
+              block_load_stream(pb, p.N, row_base, col0, lane, pw);
               stage_put_coal(stage, lane, pw);
               __syncwarp();
               stage_get_row(stage, lane, own);
@@ -763,7 +783,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               __syncwarp();
               stage_get_coal(stage, lane, pw);
               __syncwarp();
-              block_store_coal(pb, p.N, row_base, col0, lane, pw);
+              block_store_stream(pb, p.N, row_base, col0, lane, pw);
             } else if (row_ok) {
               __nv_bfloat16* prow = pb + static_cast<long long>(r) * p.N;
 #pragma unroll
@@ -781,7 +801,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             __nv_bfloat16* pb = static_cast<__nv_bfloat16*>(p.upd_param[tc.batch]);
             if (full) {
               uint32_t pw[16], np[16];
-              block_load_coal(pb, p.M, col0, row_base, lane, pw);
+              block_load_stream(pb, p.M, col0, row_base, lane, pw);
               stage_put_coal(stage, lane, pw);
               __syncwarp();
               // this thread's tile row r is column `lane` of the staged block: read it down the rows
@@ -807,7 +827,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               __syncwarp();
               stage_get_coal(stage, lane, pw);
               __syncwarp();
-              block_store_coal(pb, p.M, col0, row_base, lane, pw);
+              block_store_stream(pb, p.M, col0, row_base, lane, pw);
             } else if (row_ok) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
