@@ -17,6 +17,10 @@ same-shape parameters:
    receives its rows of every update;
 4. every rank applies ``p = p*(1 - lr*wd) - lr*u`` to its own rows with the update kernel.
 
+Sets are cut into units of at most 32 parameters and the units are pipelined: the gradients of
+unit k+1 and the updates of unit k-1 are exchanged (asynchronous collectives) while unit k is
+orthogonalised.
+
 Every element goes through the same arithmetic as in ``SingleDeviceMuon`` on the full parameter,
 so the shards are bit-identical to the corresponding rows of a single-device run.
 """
@@ -82,6 +86,7 @@ class ShardedMuon(torch.optim.Optimizer):
             if len(self._full_shape[id(p)]) < 2:
                 raise ValueError("Muon is for parameters with at least two dimensions")
         self._group = group
+        self.max_per_unit = 32  # parameters per exchange/orthogonalise unit (rounded to the world size)
         # the largest first, like the reference's sort (muon.py:42), on the unsharded shapes
         order = sorted(range(len(params)), key=lambda i: self._full_shape[id(params[i])], reverse=True)
         super().__init__([params[i] for i in order], defaults)
@@ -97,63 +102,111 @@ class ShardedMuon(torch.optim.Optimizer):
             with torch.enable_grad():
                 loss = closure()
         world, rank = self._world()
+        # Work units: same-shape parameters, at most `max_per_unit` at a time, so that the exchanges
+        # of one unit run while another unit is being orthogonalised.
+        units = []
         for group in self.param_groups:
             sets: "OrderedDict[tuple, list]" = OrderedDict()
             for p in group["params"]:
                 sets.setdefault((self._full_shape[id(p)], p.dtype), []).append(p)
             for (shape, _), plist in sets.items():
-                self._step_set(plist, shape, group, world, rank)
+                per = max(world, self.max_per_unit // world * world)
+                for start in range(0, len(plist), per):
+                    units.append(_Unit(plist[start:start + per], shape, group, world, rank))
+        # Pipeline: gradients of unit k+1 travel while unit k is orthogonalised; the updates of unit k
+        # travel back while unit k+1 is orthogonalised and are applied after that.
+        if units:
+            units[0].send_gradients(self._group)
+        previous = None
+        for k, unit in enumerate(units):
+            if k + 1 < len(units):
+                units[k + 1].send_gradients(self._group)
+            unit.orthogonalize(self)
+            unit.send_updates(self._group)
+            if previous is not None:
+                previous.apply()
+            previous = unit
+        if previous is not None:
+            previous.apply()
         return loss
 
-    def _step_set(self, plist, shape, group, world, rank) -> None:
-        backend = get_backend()
-        rows, cols = view_2d(shape)
-        chunk, mine_rows = shard_rows(rows, world, rank)
-        ld = (cols + 7) // 8 * 8  # pitch of the update blocks: rows of 16-byte multiples
+
+class _Unit:
+    """One exchange -> orthogonalise -> exchange -> apply unit of ShardedMuon.step (same-shape
+    parameters; parameter j of the unit is owned by rank j mod W)."""
+
+    def __init__(self, plist, shape, group, world, rank):
+        self.plist, self.shape, self.group, self.world, self.rank = plist, shape, group, world, rank
+        self.rows, self.cols = view_2d(shape)
+        self.chunk, self.mine_rows = shard_rows(self.rows, world, rank)
+        self.ld = (self.cols + 7) // 8 * 8  # pitch of the update blocks: rows of 16-byte multiples
         n = len(plist)
-        locals_ = []
+        self.locals = []
         for p in plist:
             lp = _local(p)
-            if lp.numel() != mine_rows * cols:
-                raise ValueError(f"rank {rank} should hold {mine_rows} rows of a {tuple(shape)} parameter, "
+            if lp.numel() != self.mine_rows * self.cols:
+                raise ValueError(f"rank {rank} should hold {self.mine_rows} rows of a {tuple(shape)} parameter, "
                                  f"got a shard of shape {tuple(lp.shape)}")
-            locals_.append(lp)
-        dev, dtype = locals_[0].device, locals_[0].dtype
-        # parameter j of the set is owned by rank j mod W; blocks are ordered by owner
-        by_owner = [list(range(d, n, world)) for d in range(world)]
-        counts = [len(ix) for ix in by_owner]
-        order = [j for ix in by_owner for j in ix]
-        n_mine = counts[rank]
+            if not lp.is_contiguous():
+                raise ValueError("ShardedMuon needs contiguous local shards")
+            self.locals.append(lp)
+        # blocks are ordered by owner
+        self.by_owner = [list(range(d, n, world)) for d in range(world)]
+        self.counts = [len(ix) for ix in self.by_owner]
+        self.order = [j for ix in self.by_owner for j in ix]
+        self.n_mine = self.counts[rank]
+        self.grad_work = self.upd_work = None
 
-        # 1. gradients to their owners (a missing gradient counts as zeros, muon.py:59-61)
+    def send_gradients(self, pg) -> None:
+        """1. gradient rows to their owners (a missing gradient counts as zeros, muon.py:59-61)."""
+        n, chunk, cols, world = len(self.plist), self.chunk, self.cols, self.world
+        dev, dtype = self.locals[0].device, self.locals[0].dtype
         send = torch.zeros(n, chunk, cols, dtype=dtype, device=dev)
-        for slot, j in enumerate(order):
-            g = plist[j].grad
-            if g is not None and mine_rows:
-                send[slot, :mine_rows].copy_(_local(g).reshape(mine_rows, cols))
-        recv = torch.empty(world, n_mine, chunk, cols, dtype=dtype, device=dev)
-        dist.all_to_all_single(recv.view(world * n_mine, chunk * cols), send.view(n, chunk * cols),
-                               output_split_sizes=[n_mine] * world, input_split_sizes=counts, group=self._group)
+        for slot, j in enumerate(self.order):
+            g = self.plist[j].grad
+            if g is not None and self.mine_rows:
+                send[slot, :self.mine_rows].copy_(_local(g).reshape(self.mine_rows, cols))
+        self.recv = torch.empty(world, self.n_mine, chunk, cols, dtype=dtype, device=dev)
+        self.grad_work = dist.all_to_all_single(
+            self.recv.view(world * self.n_mine, chunk * cols), send.view(n, chunk * cols),
+            output_split_sizes=[self.n_mine] * world, input_split_sizes=self.counts, group=pg, async_op=True)
+        self._send = send  # stays alive until the exchange has completed
 
-        # 2. the owner's share: full gradients -> scaled orthogonal updates
-        upd = torch.zeros(n_mine, world * chunk, ld, dtype=torch.bfloat16, device=dev)
-        if n_mine:
-            full = recv.transpose(0, 1).contiguous().view(n_mine, world * chunk, cols)
-            grads = [full[k, :rows] for k in range(n_mine)]
+    def orthogonalize(self, optimizer) -> None:
+        """2. the owner's share: full gradients -> scaled orthogonal updates."""
+        world, chunk, cols = self.world, self.chunk, self.cols
+        dev, dtype = self.locals[0].device, self.locals[0].dtype
+        self.grad_work.wait()
+        self._send = None
+        self.upd = torch.zeros(self.n_mine, world * chunk, self.ld, dtype=torch.bfloat16, device=dev)
+        if self.n_mine:
+            full = self.recv.transpose(0, 1).contiguous().view(self.n_mine, world * chunk, cols)
+            grads = [full[k, :self.rows] for k in range(self.n_mine)]
             moms = []
-            for j in by_owner[rank]:
-                state = self.state[plist[j]]
+            for j in self.by_owner[self.rank]:
+                state = optimizer.state[self.plist[j]]
                 if len(state) == 0:
-                    state["momentum_buffer"] = torch.zeros(rows, cols, dtype=dtype, device=dev)
+                    state["momentum_buffer"] = torch.zeros(self.rows, cols, dtype=dtype, device=dev)
                 moms.append(state["momentum_buffer"])
-            backend.muon_orthogonalize(grads, moms, shape, group["momentum"], True, upd)
+            get_backend().muon_orthogonalize(grads, moms, self.shape, self.group["momentum"], True, self.upd)
+        self.recv = None
 
-        # 3. updates back to the rows' holders, bf16
-        back_send = upd.view(n_mine, world, chunk, ld).transpose(0, 1).contiguous()
-        back = torch.empty(n, chunk, ld, dtype=torch.bfloat16, device=dev)
-        dist.all_to_all_single(back.view(n, chunk * ld), back_send.view(world * n_mine, chunk * ld),
-                               output_split_sizes=counts, input_split_sizes=[n_mine] * world, group=self._group)
+    def send_updates(self, pg) -> None:
+        """3. update rows back to their holders, bf16."""
+        n, world, chunk, ld = len(self.plist), self.world, self.chunk, self.ld
+        back_send = self.upd.view(self.n_mine, world, chunk, ld).transpose(0, 1).contiguous()
+        self.back = torch.empty(n, chunk, ld, dtype=torch.bfloat16, device=self.upd.device)
+        self.upd_work = dist.all_to_all_single(
+            self.back.view(n, chunk * ld), back_send.view(world * self.n_mine, chunk * ld),
+            output_split_sizes=self.counts, input_split_sizes=[self.n_mine] * world, group=pg, async_op=True)
+        self._send = back_send
+        self.upd = None
 
-        # 4. every rank updates its own rows (block `slot` of `back` belongs to parameter order[slot])
-        if mine_rows:
-            backend.apply_update([locals_[j] for j in order], back, mine_rows, cols, group["lr"], group["weight_decay"])
+    def apply(self) -> None:
+        """4. every rank updates its own rows (block `slot` of `back` belongs to parameter order[slot])."""
+        self.upd_work.wait()
+        self._send = None
+        if self.mine_rows:
+            get_backend().apply_update([self.locals[j] for j in self.order], self.back, self.mine_rows, self.cols,
+                                       self.group["lr"], self.group["weight_decay"])
+        self.back = None
