@@ -573,22 +573,6 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const TileCoord tc = decode_tile<TILE_M>(t / work_per_tile, p);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1u;
-      int ok = 1;
-      if (split_phase != 2)  // (phase 2 reads partial sums from memory: no accumulator to wait for)
-        ok = (CTAS == 2 ? mbar_wait_bounded_cluster(tfull_bar(acc), acc_phase, &s_abort)
-                        : mbar_wait_bounded(tfull_bar(acc), acc_phase, &s_abort))
-                 ? 1
-                 : 0;
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) {
-        if (lane == 0) {
-          atomicCAS(&g_device_status, 0, 4);
-          s_abort = 1;
-        }
-        break;
-      }
-      tc_fence_after();
-
       const int row_base = tc.tm * TILE_M + (int)cta_rank * BM + q * 32;
       const int r = row_base + lane;  // output row of this thread
       const int r_warp_max = row_base + 31;
@@ -615,8 +599,9 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const uint32_t stage = stage_area + (warp - 2) * STAGING_BYTES_PER_WARP;
 
       // Addend of the chunk about to be processed, fetched one chunk ahead ("coal" pattern for
-      // a full chunk, this thread's own row otherwise). (Two buffers taking turns instead of the
-      // copy below were measured: no faster, and 25 registers more.)
+      // a full chunk, this thread's own row otherwise); the first one before the accumulator is
+      // waited for, so that its latency passes under the tile's last MMAs. (Two buffers taking
+      // turns instead of the copy below were measured: no faster, and 25 registers more.)
       uint32_t add_raw[MODE == MODE_SYRK ? 1 : 16] = {};
       if constexpr (MODE != MODE_SYRK) {
         if (chunk_live(c_begin)) {
@@ -625,6 +610,22 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           else if (row_ok) load_row32_raw(add_row, col0, p.N, add_raw);
         }
       }
+
+      int ok = 1;
+      if (split_phase != 2)  // (phase 2 reads partial sums from memory: no accumulator to wait for)
+        ok = (CTAS == 2 ? mbar_wait_bounded_cluster(tfull_bar(acc), acc_phase, &s_abort)
+                        : mbar_wait_bounded(tfull_bar(acc), acc_phase, &s_abort))
+                 ? 1
+                 : 0;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) {
+          atomicCAS(&g_device_status, 0, 4);
+          s_abort = 1;
+        }
+        break;
+      }
+      tc_fence_after();
 
 #pragma unroll 1
       for (int c = c_begin; c < c_begin + CHUNKS; ++c) {
