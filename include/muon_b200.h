@@ -32,10 +32,11 @@ extern "C" {
 #define MUON_B200_ERR_DEVICE_TIMEOUT (-5)
 
 /* Element types. Parameters, gradients and optimizer state (prologue, epilogue, muon_step, adam)
- * are float32 or bfloat16; the reference's elementwise code would also run on float16 and
- * float64 parameters (muon.py:9-10, :66-67, :105-109), which this library does not implement.
- * The input of muon_b200_zeropower and muon_b200_cast_bf16 may be any of the four, like the
- * cast at muon.py:760. */
+ * are float32, bfloat16 or float16 (the update is fused into the last GEMM for the first two; a
+ * float16 parameter gets the update kernel). The reference's elementwise code would also run on
+ * float64 parameters (muon.py:9-10, :66-67, :105-109); this library computes in float32 registers
+ * and does not take them. The input of muon_b200_zeropower and muon_b200_cast_bf16 may be any of
+ * the four, like the cast at muon.py:760. */
 #define MUON_B200_F32 0
 #define MUON_B200_BF16 1
 #define MUON_B200_F16 2

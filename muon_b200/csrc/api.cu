@@ -37,8 +37,8 @@ inline __nv_bfloat16* bf(void* p) { return static_cast<__nv_bfloat16*>(p); }
 inline const __nv_bfloat16* bf(const void* p) { return static_cast<const __nv_bfloat16*>(p); }
 
 int check_dtype(int dtype) {
-  if (dtype != DT_F32 && dtype != DT_BF16)
-    return set_error(ERR_INVALID_ARG, "dtype must be MUON_B200_F32 or MUON_B200_BF16 (got %d)",
+  if (dtype != DT_F32 && dtype != DT_BF16 && dtype != DT_F16)
+    return set_error(ERR_INVALID_ARG, "dtype must be MUON_B200_F32, MUON_B200_BF16 or MUON_B200_F16 (got %d)",
                      dtype);
   return OK;
 }

@@ -19,6 +19,11 @@ constexpr int kTileRows = 64;
 constexpr int kRowsInFlight = 2;  // rows of a tile whose loads a thread issues back to back
 
 template <typename T>
+constexpr bool kIsBf16 = false;
+template <>
+constexpr bool kIsBf16<__nv_bfloat16> = true;
+
+template <typename T>
 struct Vec;
 template <>
 struct Vec<float> {
@@ -73,8 +78,40 @@ struct Vec<__nv_bfloat16> {
   }
 };
 
+template <>
+struct Vec<__half> {
+  static constexpr int N = 8;
+  using Raw = uint4;
+  __device__ static Raw load_raw(const __half* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
+  __device__ static void unpack(const Raw& r, float (&v)[8]) {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+      v[2 * j] = f.x;
+      v[2 * j + 1] = f.y;
+    }
+  }
+  __device__ static void load(const __half* p, float (&v)[8]) {
+    unpack(*reinterpret_cast<const uint4*>(p), v);
+  }
+  __device__ static uint4 pack(const float (&v)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+      w[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  __device__ static void store(__half* p, const float (&v)[8]) { *reinterpret_cast<uint4*>(p) = pack(v); }
+  __device__ static void store_stream(__half* p, const float (&v)[8]) { __stcs(reinterpret_cast<uint4*>(p), pack(v)); }
+};
+
 template <typename T>
 __device__ __forceinline__ float to_f(T v);
+template <>
+__device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
 template <>
 __device__ __forceinline__ float to_f<float>(float v) { return v; }
 template <>
@@ -90,6 +127,8 @@ template <>
 __device__ __forceinline__ float round_to<__nv_bfloat16>(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
 }
+template <>
+__device__ __forceinline__ float round_to<__half>(float v) { return __half2float(__float2half_rn(v)); }
 // Same for two values at once: for bf16 one packed conversion instead of two scalar ones.
 template <typename T>
 __device__ __forceinline__ void round_pair_to(float& a, float& b);
@@ -101,8 +140,16 @@ __device__ __forceinline__ void round_pair_to<__nv_bfloat16>(float& a, float& b)
   a = bf16_bits_to_float(w & 0xffffu);
   b = bf16_bits_to_float(w >> 16);
 }
+template <>
+__device__ __forceinline__ void round_pair_to<__half>(float& a, float& b) {
+  const float2 f = __half22float2(__floats2half2_rn(a, b));
+  a = f.x;
+  b = f.y;
+}
 template <typename T>
 __device__ __forceinline__ T from_f(float v);
+template <>
+__device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
 template <>
 __device__ __forceinline__ float from_f<float>(float v) { return v; }
 template <>
@@ -215,7 +262,7 @@ prologue_kernel(const PrologueArgs a) {
             xv[j] = mv[j];
             xv[j + 1] = mv[j + 1];
           }
-          if (sizeof(T) == 4) round_pair_to<__nv_bfloat16>(xv[j], xv[j + 1]);  // fp32 state -> bf16 X
+          if (!kIsBf16<T>) round_pair_to<__nv_bfloat16>(xv[j], xv[j + 1]);  // fp32 / fp16 state -> bf16 X
           ss = fmaf(xv[j], xv[j], ss);  // elements outside the matrix are zero
           ss = fmaf(xv[j + 1], xv[j + 1], ss);
         }
@@ -721,6 +768,9 @@ int launch_prologue(const PrologueArgs& a, int dtype, int transpose, cudaStream_
   if (dtype == DT_F32) {
     if (transpose) prologue_kernel<float, true><<<grid, kThreads, 0, stream>>>(a);
     else prologue_kernel<float, false><<<grid, kThreads, 0, stream>>>(a);
+  } else if (dtype == DT_F16) {
+    if (transpose) prologue_kernel<__half, true><<<grid, kThreads, 0, stream>>>(a);
+    else prologue_kernel<__half, false><<<grid, kThreads, 0, stream>>>(a);
   } else {
     if (transpose) prologue_kernel<__nv_bfloat16, true><<<grid, kThreads, 0, stream>>>(a);
     else prologue_kernel<__nv_bfloat16, false><<<grid, kThreads, 0, stream>>>(a);
@@ -752,6 +802,9 @@ int launch_epilogue(const EpilogueArgs& a, int dtype, int transpose, cudaStream_
   if (dtype == DT_F32) {
     if (transpose) launch_epilogue_variant<float, true>(grid, a, peers, stream);
     else launch_epilogue_variant<float, false>(grid, a, peers, stream);
+  } else if (dtype == DT_F16) {
+    if (transpose) launch_epilogue_variant<__half, true>(grid, a, peers, stream);
+    else launch_epilogue_variant<__half, false>(grid, a, peers, stream);
   } else {
     if (transpose) launch_epilogue_variant<__nv_bfloat16, true>(grid, a, peers, stream);
     else launch_epilogue_variant<__nv_bfloat16, false>(grid, a, peers, stream);
@@ -832,6 +885,7 @@ int launch_adam(const AdamArgs& a, int dtype, cudaStream_t stream) {
   for (int i = 0; i < a.count; ++i) elems += (double)a.numel[i];
   LaunchScope scope(K_ADAM, elems * 7 * (dtype == DT_F32 ? 4 : 2), stream);  // read p,g,m,v; write p,m,v
   if (dtype == DT_F32) adam_kernel<float><<<blocks, kThreads, 0, stream>>>(a);
+  else if (dtype == DT_F16) adam_kernel<__half><<<blocks, kThreads, 0, stream>>>(a);
   else adam_kernel<__nv_bfloat16><<<blocks, kThreads, 0, stream>>>(a);
   MB_CUDA_CHECK(cudaGetLastError());
   return OK;

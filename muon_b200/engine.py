@@ -21,7 +21,7 @@ from torch import Tensor
 from . import _lib
 from ._lib import BF16, F16, F32, F64, NS_AOL4, NS_AOL4_FP8, NS_CLASSIC5, NS_HAVE_SUMSQ, check, i64_array, lib, ptr_array
 
-_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 # element types the cast at the entry of Newton-Schulz accepts (muon.py:760 takes any float dtype)
 _NS_INPUT_CODE = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16, torch.float64: F64}
 _NS_MODES = {"aol4": NS_AOL4, "classic5": NS_CLASSIC5, "aol4_fp8": NS_AOL4_FP8}
@@ -108,7 +108,7 @@ def dtype_code(t: Tensor) -> int:
     try:
         return _DTYPE_CODE[t.dtype]
     except KeyError:
-        raise ValueError(f"muon_b200 supports float32 and bfloat16 tensors, got {t.dtype}") from None
+        raise ValueError(f"muon_b200 supports float32, bfloat16 and float16 tensors, got {t.dtype}") from None
 
 
 def view_2d(shape: Sequence[int]) -> tuple[int, int]:

@@ -488,6 +488,54 @@ def test_update_fused_into_the_last_gemm_on_ragged_shapes(mb, dtype):
         assert orc.rel_fro(p.detach().cpu(), r) <= tol, p.shape
 
 
+def test_float16_parameters(mb):
+    """float16 parameters, gradients and state (the reference's eager ops take them, muon.py:9-10,
+    :66-67, :105-109): Muon parameters of both orientations and a 4-D filter plus Adam vectors,
+    two steps, against the oracle run on float16 CPU tensors. The momentum after the first step is
+    one rounding of an fp32 expression on both sides; parameters within the bounds of the fp32 case
+    plus float16's own 2^-11 rounding; the update is a kernel of its own for this dtype."""
+    g = torch.Generator().manual_seed(29)
+    shapes = [(128, 384)] * 2 + [(384, 128)] + [(64, 32, 3, 3)] + [(100, 250)]
+    p0 = [(torch.randn(s, generator=g) * 0.02).half() for s in shapes]
+    gains0 = [torch.ones(96).half() for _ in range(3)]
+    params = [torch.nn.Parameter(p.clone().to(DEV)) for p in p0]
+    gains = [torch.nn.Parameter(p.clone().to(DEV)) for p in gains0]
+    opt = mb.SingleDeviceMuonWithAuxAdam([dict(params=params, use_muon=True, lr=0.02, weight_decay=0.01),
+                                          dict(params=gains, use_muon=False, lr=1e-3)])
+    ref_p, ref_g = [p.clone() for p in p0], [p.clone() for p in gains0]
+    mom = [torch.zeros_like(p) for p in p0]
+    ea, es = [torch.zeros_like(p) for p in gains0], [torch.zeros_like(p) for p in gains0]
+    before = dict(mb._lib.launch_counts())
+    for step in (1, 2):
+        gh = [torch.randn(s, generator=g).half() for s in shapes]
+        # (|g| >= 0.05: a smaller Adam gradient squares to zero in float16 and the reference's own
+        # arithmetic then divides by zero)
+        gg = [((0.05 + 0.1 * torch.rand(96, generator=g)) * torch.sign(torch.randn(96, generator=g))).half()
+              for _ in gains0]
+        for p, gr in zip(params + gains, gh + gg):
+            p.grad = gr.clone().to(DEV)
+        opt.step()
+        for p, gr, m in zip(ref_p, gh, mom):
+            orc.muon_param_step(p, gr.clone(), m, 0.02, 0.01, 0.95)
+        for p, gr, m, v in zip(ref_g, gg, ea, es):
+            orc.adam_param_step(p, gr.clone(), m, v, step, 1e-3, 0, (0.9, 0.95), 1e-10)
+        if step == 1:
+            for p, m in zip(params, mom):
+                got = opt.state[p]["momentum_buffer"].float().cpu()
+                assert ((got - m.float()).abs() <= m.float().abs() * 2 ** -10 + 1e-8).all()
+    torch.cuda.synchronize()
+    assert mb.device_status() == 0
+    after = mb._lib.launch_counts()
+    assert after["epilogue"] - before["epilogue"] >= 2  # no fused update for float16
+    for p, r in zip(params, ref_p):
+        assert p.dtype == torch.float16
+        assert orc.rel_fro(p.detach().float().cpu(), r.float()) <= 1.5e-3, p.shape
+    for p, r, m, v in zip(gains, ref_g, ea, es):
+        assert orc.rel_fro(p.detach().float().cpu(), r.float()) <= 1e-3
+        assert orc.rel_fro(opt.state[p]["exp_avg"].float().cpu(), m.float()) <= 2e-3
+        assert orc.rel_fro(opt.state[p]["exp_avg_sq"].float().cpu(), v.float()) <= 4e-3
+
+
 def test_grad_none_becomes_zero_and_state_keys(mb):
     p = torch.nn.Parameter(torch.randn(64, 96, device=DEV))
     before = p.detach().clone()
