@@ -61,6 +61,26 @@ def test_argument_errors_are_reported_without_a_gpu():
     assert rc == -1 and b"dtype" in L.lib.muon_b200_last_error()
 
 
+def test_split_along_k_is_sized_without_a_gpu():
+    """Scratch of the functional line 1 / Newton-Schulz for a Gram product that is split along K: a
+    function of the sizes alone (no device needed). One or a few small matrices with a long K are
+    split; launches that fill the GPU, and short contractions, are not."""
+    import muon_b200._lib as L
+    tile_bytes = 256 * 256 * 4
+    one = L.lib.muon_b200_ns_line1_scratch_bytes(1, 768, 3072)
+    assert one > 0 and one % (6 * tile_bytes) == 0          # 6 lower-triangle tiles x slices
+    assert 3 <= one // (6 * tile_bytes) <= 16
+    assert L.lib.muon_b200_ns_line1_scratch_bytes(1, 1024, 8192) > 0
+    assert L.lib.muon_b200_ns_line1_scratch_bytes(12, 768, 3072) == 0    # 72 tiles: one wave of CTA pairs
+    assert L.lib.muon_b200_ns_line1_scratch_bytes(1, 4096, 14336) == 0
+    assert L.lib.muon_b200_ns_line1_scratch_bytes(1, 768, 512) == 0      # too few k-blocks per slice
+    assert L.lib.muon_b200_ns_line1_scratch_bytes(1, 100, 2050) > 0      # one single-CTA tile
+    # the functional Newton-Schulz includes that room, the optimizer's workspace does not
+    assert L.lib.muon_b200_zeropower_scratch_bytes(1, 768, 3072, L.NS_AOL4) >= one
+    lay = L.ns_layout(1, 768, 3072, L.NS_AOL4)
+    assert lay.total_bytes < L.lib.muon_b200_zeropower_scratch_bytes(1, 768, 3072, L.NS_AOL4) + 768 * 3072 * 2
+
+
 def test_ramped_launch_groups():
     """Slowly growing groups at the start of a set whose gradients are still arriving (a group may
     hold one more than a quarter of everything before it); every parameter stays in exactly one

@@ -83,6 +83,20 @@ def test_balanced_ownership(shapes, world):
     assert ownership.ns_cost(shapes[0]) == m * (m + 1) * n + m * m * (m + 1) + 2 * m * m * n
 
 
+@settings(max_examples=200, deadline=None)
+@given(rows=st.integers(1, 5000), world=st.integers(1, 64))
+def test_row_shards_partition_the_rows(rows, world):
+    """The row split of ShardedMuon is torch.chunk's (= DTensor Shard(0)): chunks of ceil(rows/W),
+    consecutive, covering every row once; the last ranks may be short or empty."""
+    from muon_b200.sharded import shard_rows
+    pieces = [shard_rows(rows, world, r) for r in range(world)]
+    chunk = pieces[0][0]
+    assert all(c == chunk for c, _ in pieces) and chunk == -(-rows // world)
+    assert sum(n for _, n in pieces) == rows
+    assert [n for _, n in pieces] == [len(t) for t in torch.arange(rows).chunk(world)] + \
+        [0] * (world - len(torch.arange(rows).chunk(world)))
+
+
 @settings(max_examples=40, deadline=None)
 @given(m=st.integers(1, 70), seed=st.integers(0, 2 ** 16), tile=st.sampled_from([8, 16, 64]))
 def test_mirror_rules(m, seed, tile):
