@@ -7,7 +7,8 @@
 
 namespace mb {
 
-// DT_F16 and DT_F64 are accepted by the cast kernel only (inputs of the functional Newton-Schulz).
+// DT_F64 is accepted by the cast kernel only (inputs of the functional Newton-Schulz); parameters,
+// gradients and optimizer state are DT_F32, DT_BF16 or DT_F16.
 enum DType : int { DT_F32 = 0, DT_BF16 = 1, DT_F16 = 2, DT_F64 = 3 };
 
 constexpr int kMaxTensors = 32;  // tensors per multi-tensor launch

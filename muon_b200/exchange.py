@@ -80,7 +80,7 @@ class PeerPush:
         gathered = [None] * self.world
         dist.all_gather_object(gathered, (exported, errors))
         errors = [e for g in gathered for e in g[1]]
-        # Every rank must hold the same parameters in the same order, or ownership (index % world)
+        # Every rank must hold the same parameters in the same order, or ownership (a function of the position in the list)
         # and the pushes would pair up different tensors: compare the byte sizes rank by rank.
         sizes = [[item[2] for item in g[0]] for g in gathered]
         if not errors and any(s != sizes[0] for s in sizes):
