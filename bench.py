@@ -174,6 +174,28 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------------- ours
+def cpus_near_gpu(index):
+    """CPUs of the NUMA node the GPU hangs off (from sysfs), or None when that cannot be told.
+    Pinned host buffers allocated by a thread running there are local to the GPU's PCIe root, so
+    host-to-device copies do not cross the socket interconnect."""
+    try:
+        props = torch.cuda.get_device_properties(index)
+        bdf = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            text = f.read().strip()
+        cpus = set()
+        for part in text.split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        return (node, cpus) if cpus else None
+    except Exception:
+        return None
+
+
 def make_problem(shapes, dtype, device):
     """Parameters for every matrix (replicated on every rank). Seeds depend on the matrix index
     only, so the data does not depend on the world size."""
@@ -409,7 +431,17 @@ def run_ours(args):
     per_kind = _lib.timing_collect()
 
     # ---- end to end: gradients arrive from pinned host memory, a scalar goes back ----
-    pinned = [g.to("cpu").pin_memory() for g in pool]  # one pinned buffer per gradient
+    # one pinned buffer per gradient, allocated from a CPU of the GPU's NUMA node where that is known
+    allowed = os.sched_getaffinity(0)
+    near = cpus_near_gpu(local_rank)
+    numa_note = "NUMA node of the GPU unknown: buffers allocated wherever the process ran"
+    if near is not None and near[1] & allowed:
+        os.sched_setaffinity(0, near[1] & allowed)
+        numa_note = f"buffers allocated on NUMA node {near[0]}, the GPU's"
+    try:
+        pinned = [g.to("cpu").pin_memory() for g in pool]
+    finally:
+        os.sched_setaffinity(0, allowed)
     h2d_bytes = sum(g.numel() * g.element_size() for g in pool)
     result_host = torch.zeros(1, dtype=torch.float32).pin_memory()
     probe = sorted_params[0]
@@ -484,7 +516,8 @@ def run_ours(args):
             "ns_tflops_kernels": ns_work / (ns_ms * 1e-3) / 1e12 if ns_ms > 0 else None,
             "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": int(h2d.item()),
                     "d2h_bytes_per_step": 4,
-                    "note": "one pinned host buffer per gradient; copies on a copy stream, each gradient marked ready"},
+                    "note": "one pinned host buffer per gradient (" + numa_note + "); copies on a copy stream, "
+                            "each gradient marked ready"},
             "gpu_launches": int(launches),
             "roofline": {"bound": "tensor", "kernel": "ns_gemm_kernel<MODE_BX> (line 3: a*X + B*X)",
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
