@@ -643,9 +643,23 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             float sum[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) sum[j] = 0.f;
-            for (int sl = 0; sl < p.split_k; ++sl) {
-              const float* src = p.partial +
-                  ((((tile_index * p.split_k + sl) * CTAS + cta_rank) * 4 + q) * (BN / 32) + c) * 1024 + lane;
+            // Two slices per round: their 64 loads are in flight together, the additions keep the
+            // slice order. (One slice per round made this phase wait for L2 twelve times in a row.)
+            const long long slice_pitch = static_cast<long long>(CTAS) * 4 * (BN / 32) * 1024;
+            const float* src = p.partial +
+                (((tile_index * p.split_k * CTAS + cta_rank) * 4 + q) * (BN / 32) + c) * 1024 + lane;
+            int sl = 0;
+            for (; sl + 1 < p.split_k; sl += 2) {
+              float first[32], second[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) first[j] = __ldcg(src + j * 32);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) second[j] = __ldcg(src + slice_pitch + j * 32);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) sum[j] = (sum[j] + first[j]) + second[j];
+              src += 2 * slice_pitch;
+            }
+            if (sl < p.split_k) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) sum[j] += __ldcg(src + j * 32);
             }
