@@ -63,8 +63,11 @@ def ns_line_1(A: Tensor, *, out: Tensor = None) -> Tensor:
     return _finish(buf, user, A.ndim, (M, M))
 
 
-def ns_line_2(A: Tensor, alpha: float, beta: float, *, out: Tensor = None) -> Tensor:
-    """C = alpha * A @ A.T + beta * A for square bf16 A (muon.py:547-588)."""
+def ns_line_2(A: Tensor, alpha: float, beta: float, *, out: Tensor = None, symmetric: bool = False) -> Tensor:
+    """C = alpha * A @ A.T + beta * A for square bf16 A (muon.py:547-588). ``symmetric=True``
+    (not in the reference's signature) promises that A equals its transpose bit for bit, as the
+    output of ``ns_line_1`` does: the kernel then mirrors finished values instead of reading
+    A[col, row] for the mirrored element (same result for such an A, less traffic)."""
     if A.ndim > 3 or A.ndim < 2:
         raise ValueError(f"Input tensor must be 2D or 3D, but got {A.ndim}D tensor.")
     M, K = A.shape[-2:]
@@ -78,12 +81,12 @@ def ns_line_2(A: Tensor, alpha: float, beta: float, *, out: Tensor = None) -> Te
     if buf.data_ptr() == A3.data_ptr():
         buf, user = _out_3d(None, A, (batch, M, M))[0], out
     with torch.cuda.device(A.device):
-        # The reference's kernel takes any square A (muon.py:483-486); nothing here knows whether this
-        # one is symmetric bit for bit, so the general addend path is used (for such an A it gives
-        # the same result as the symmetric one).
+        # The reference's kernel takes any square A (muon.py:483-486); unless the caller says that
+        # this one is symmetric bit for bit, the general addend path is used (for such an A it
+        # gives the same result as the symmetric one).
         check(lib.muon_b200_ns_line2(A3.data_ptr(), A3.stride(-2), A3.stride(0), buf.data_ptr(),
-                                     buf.stride(-2), buf.stride(0), batch, M, float(alpha), float(beta), 0,
-                                     _stream_ptr(A.device)))
+                                     buf.stride(-2), buf.stride(0), batch, M, float(alpha), float(beta),
+                                     1 if symmetric else 0, _stream_ptr(A.device)))
     return _finish(buf, user, A.ndim, (M, M))
 
 

@@ -60,6 +60,8 @@ def test_ns_line_2(mb, m, symmetric):
     assert orc.rel_fro(B, ref) <= 2e-3
     if symmetric:
         assert torch.equal(B, B.T)
+        # told that A is symmetric, the kernel mirrors finished values: same result
+        assert torch.equal(mb.ns_line_2(A.to(DEV), 2.4635, -7.0585, symmetric=True).cpu(), B)
 
 
 @pytest.mark.parametrize("m,n", [(128, 256), (128, 64), (256, 512), (200, 328), (768, 3072), (40, 72)])
