@@ -549,7 +549,8 @@ def test_grad_none_becomes_zero_and_state_keys(mb):
 
 
 def test_degenerate_parameters_are_rejected_loudly(mb):
-    """Empty matrices and 1-D / 3-D tensors have no orthogonalisation: clear errors, no silent skip."""
+    """Empty matrices and 1-D / 3-D tensors have no orthogonalisation, float64 parameters no kernels:
+    clear errors, no silent skip."""
     empty = torch.nn.Parameter(torch.zeros(0, 8, device=DEV))
     empty.grad = torch.zeros(0, 8, device=DEV)
     with pytest.raises(mb.MuonB200Error):
@@ -558,10 +559,10 @@ def test_degenerate_parameters_are_rejected_loudly(mb):
     vec.grad = torch.zeros(8, device=DEV)
     with pytest.raises(ValueError, match="2-D or 4-D"):
         mb.SingleDeviceMuon([vec]).step()
-    half = torch.nn.Parameter(torch.zeros(8, 8, device=DEV, dtype=torch.float16))
-    half.grad = torch.zeros_like(half)
-    with pytest.raises(ValueError, match="float32 and bfloat16"):
-        mb.SingleDeviceMuon([half]).step()
+    double = torch.nn.Parameter(torch.zeros(8, 8, device=DEV, dtype=torch.float64))
+    double.grad = torch.zeros_like(double)
+    with pytest.raises(ValueError, match="float32, bfloat16 and float16"):
+        mb.SingleDeviceMuon([double]).step()
     # a 1 x n and an n x 1 matrix are legal: the update is the normalised row / column
     row = torch.nn.Parameter(torch.ones(1, 64, device=DEV))
     row.grad = torch.full((1, 64), 2.0, device=DEV)
