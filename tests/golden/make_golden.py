@@ -279,7 +279,8 @@ def gen_ns_oracle():
         G = torch.randn(shape)
         U = orc.zeropower_via_newtonschulz5(G)
         Uc = orc.zeropower_classic5(G)
-        cases.append(dict(G=G, aol4=U.clone(), classic5=Uc.clone()))
+        Uf = orc.zeropower_classic5(G, folded=True)  # the arithmetic of the CUDA path
+        cases.append(dict(G=G, aol4=U.clone(), classic5=Uc.clone(), classic5_folded=Uf.clone()))
     return {"cases": cases}
 
 

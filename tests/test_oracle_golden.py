@@ -165,6 +165,7 @@ def test_newton_schulz_restatement_is_stable(golden):
         # iteration amplifies like any other change of rounding (1.3e-2 .. 1.7e-2 here); the folded
         # form is as far from the literal text as the fused one (3.1e-2 .. 3.5e-2).
         folded = orc.zeropower_classic5(c["G"], folded=True)
+        assert torch.equal(folded, c["classic5_folded"])
         assert orc.rel_fro(folded, fused) < 2.5e-2
         assert orc.rel_fro(folded, Uc) < 5e-2
 
