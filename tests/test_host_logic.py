@@ -33,6 +33,30 @@ def test_library_exports_every_declared_symbol():
     assert L.lib.muon_b200_last_error() is not None
 
 
+def test_public_header_is_plain_c(tmp_path):
+    """include/muon_b200.h is the drop-in boundary: it must compile as C99 and as C++ on its own
+    (plain pointers and sizes, no torch or CUDA types), and a C program that only includes it and
+    takes the address of an entry point must link against the library."""
+    import shutil
+    import subprocess
+    header = os.path.join(ROOT, "include", "muon_b200.h")
+    gcc, gxx = shutil.which("gcc"), shutil.which("g++")
+    if not gcc or not gxx:
+        pytest.skip("no host compiler")
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-Werror", "-fsyntax-only", "-x", "c", header], check=True)
+    subprocess.run([gxx, "-std=c++11", "-fsyntax-only", "-x", "c++", header], check=True)
+    src = tmp_path / "use.c"
+    src.write_text('#include "muon_b200.h"\n#include <stdio.h>\n'
+                   'int main(void) { muon_b200_ns_layout l; int rc = muon_b200_ns_workspace_layout(2, 64, 96, &l);\n'
+                   '  printf("%d %lld %d\\n", rc, (long long)l.total_bytes, muon_b200_version()); return rc; }\n')
+    exe = tmp_path / "use"
+    libdir = os.path.join(ROOT, "muon_b200")
+    subprocess.run([gcc, "-std=c99", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe),
+                    "-L", libdir, "-lmuon_b200", f"-Wl,-rpath,{libdir}"], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    assert out[0] == "0" and int(out[1]) > 0 and int(out[2]) >= 100
+
+
 def test_workspace_layout_is_host_only_and_consistent():
     import muon_b200._lib as L
     lay = L.ns_layout(3, 200, 330)
