@@ -418,12 +418,11 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   constexpr int KSTEP = VAR == F8_OPERANDS ? 2 * BK : BK;
   const int k_blocks = (p.K + KSTEP - 1) / KSTEP;
   // Split-K (line 1 of launches with far fewer tiles than SMs, see launch_ns_gemm): a work item is
-  // then one K-slice of a tile (phase 1: fp32 partial sums go to p.partial) or one 32-column chunk
-  // of a tile (phase 2: the slices of the chunk are added in order and stored like a finished
-  // accumulator). Otherwise a work item is a tile.
+  // then one K-slice of a tile and its fp32 partial sums go to p.partial, where
+  // splitk_reduce_kernel finds them. Otherwise a work item is a tile.
   constexpr bool kCanSplit = MODE == MODE_SYRK && VAR == F8_NONE;
   const int split_phase = kCanSplit ? p.split_phase : 0;
-  const int work_per_tile = split_phase == 1 ? p.split_k : (split_phase == 2 ? BN / 32 : 1);
+  const int work_per_tile = split_phase == 1 ? p.split_k : 1;
   const int total_tiles = p.tiles_per_batch * p.batch * work_per_tile;
   const int work0 = blockIdx.x / CTAS;
   const int work_stride = gridDim.x / CTAS;
@@ -434,7 +433,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = work0; t < total_tiles && ok && split_phase != 2; t += work_stride) {
+      for (int t = work0; t < total_tiles && ok; t += work_stride) {
         const TileCoord tc = decode_tile<TILE_M>(t / work_per_tile, p);
         const int a_row = tc.tm * TILE_M + (int)cta_rank * BM;
         const int b_row = tc.tn * BN + (int)cta_rank * C::B_ROWS;
@@ -496,7 +495,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
-      for (int t = work0; t < total_tiles && ok && split_phase != 2; t += work_stride, ++local) {
+      for (int t = work0; t < total_tiles && ok; t += work_stride, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1u;
         const int kb_first = split_phase == 1 ? (t % work_per_tile) * p.split_kb : 0;
@@ -611,12 +610,10 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
       }
 
-      int ok = 1;
-      if (split_phase != 2)  // (phase 2 reads partial sums from memory: no accumulator to wait for)
-        ok = (CTAS == 2 ? mbar_wait_bounded_cluster(tfull_bar(acc), acc_phase, &s_abort)
-                        : mbar_wait_bounded(tfull_bar(acc), acc_phase, &s_abort))
-                 ? 1
-                 : 0;
+      int ok = (CTAS == 2 ? mbar_wait_bounded_cluster(tfull_bar(acc), acc_phase, &s_abort)
+                          : mbar_wait_bounded(tfull_bar(acc), acc_phase, &s_abort))
+                   ? 1
+                   : 0;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         if (lane == 0) {
@@ -634,43 +631,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const bool full = chunk_full(c);
         uint32_t v[32];
         __syncwarp();  // tcgen05.ld is warp-collective: reconverge after the predicated stores
-        if constexpr (kCanSplit) {
-          if (split_phase == 2) {
-            // Work item = chunk (t % 8) of the tile: add its K-slices in slice order. A chunk of a
-            // slice is 32 columns x 32 rows of fp32 with the rows (lanes) contiguous.
-            if (c != t % work_per_tile) continue;
-            const long long tile_index = t / work_per_tile;
-            float sum[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) sum[j] = 0.f;
-            // Two slices per round: their 64 loads are in flight together, the additions keep the
-            // slice order. (One slice per round made this phase wait for L2 twelve times in a row.)
-            const long long slice_pitch = static_cast<long long>(CTAS) * 4 * (BN / 32) * 1024;
-            const float* src = p.partial +
-                (((tile_index * p.split_k * CTAS + cta_rank) * 4 + q) * (BN / 32) + c) * 1024 + lane;
-            int sl = 0;
-            for (; sl + 1 < p.split_k; sl += 2) {
-              float first[32], second[32];
-#pragma unroll
-              for (int j = 0; j < 32; ++j) first[j] = __ldcg(src + j * 32);
-#pragma unroll
-              for (int j = 0; j < 32; ++j) second[j] = __ldcg(src + slice_pitch + j * 32);
-#pragma unroll
-              for (int j = 0; j < 32; ++j) sum[j] = (sum[j] + first[j]) + second[j];
-              src += 2 * slice_pitch;
-            }
-            if (sl < p.split_k) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) sum[j] += __ldcg(src + j * 32);
-            }
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(sum[j]);
-          } else {
-            tmem_ld_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, v);
-          }
-        } else {
-          tmem_ld_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, v);
-        }
+        tmem_ld_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, v);
         uint32_t add_next[MODE == MODE_SYRK ? 1 : 16] = {};
         const bool more = MODE != MODE_SYRK && c + 1 < c_begin + CHUNKS && chunk_live(c + 1);
         if constexpr (MODE != MODE_SYRK) {
@@ -686,7 +647,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
         if constexpr (kCanSplit) {
           if (split_phase == 1) {
-            // this slice's share of the chunk, as it is: phase 2 adds the slices and stores
+            // this slice's share of the chunk, as it is: splitk_reduce_kernel adds the slices
             float* dst = p.partial +
                 (((static_cast<long long>(t) * CTAS + cta_rank) * 4 + q) * (BN / 32) + c) * 1024 + lane;
 #pragma unroll
@@ -1031,7 +992,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       // Accumulator drained: hand it back to the MMA warp (of the pair's leader).
       tc_fence_before();
       __syncwarp();
-      if (lane == 0 && split_phase != 2) {
+      if (lane == 0) {
         if (CTAS == 2) mbar_arrive_remote(map_to_cta(tempty_bar(acc), 0));
         else mbar_arrive(tempty_bar(acc));
       }
@@ -1047,6 +1008,89 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (warp == 1) {
     if (CTAS == 2) tmem_dealloc_pair(tmem_base, TMEM_COLS);
     else tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Second launch of a line 1 that was split along K: one warp per 32-row x 8-column piece of the
+// output adds the piece's K-slices in slice order (lane = row, so every load and every mirrored
+// store is contiguous across the warp), rounds once and stores the piece and its mirror image
+// with the rules of the GEMM epilogue: positions with col <= row from their own value, positions
+// above the diagonal from the mirrored one. Pieces this narrow because the launches that are
+// split have few tiles: four warps per 32 x 32 block put enough loads in flight on the few SMs
+// that get work.
+// ---------------------------------------------------------------------------
+template <int CTAS>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const GemmParams p) {
+  constexpr int TILE_M = BM * CTAS;
+  constexpr int PIECES_PER_TILE = CTAS * 4 * (BN / 32) * 4;
+  griddep_launch_dependents();
+  griddep_wait();  // the partial sums come from the launch before this one
+  const int lane = threadIdx.x & 31;
+  const long long warp_global = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long total = static_cast<long long>(p.tiles_per_batch) * p.batch * PIECES_PER_TILE;
+  if (warp_global >= total) return;
+  const int tile = static_cast<int>(warp_global / PIECES_PER_TILE);
+  int within = static_cast<int>(warp_global - static_cast<long long>(tile) * PIECES_PER_TILE);
+  const int j0 = (within & 3) * 8;  // first of the piece's 8 columns inside its 32-column chunk
+  within >>= 2;
+  const int c = within % (BN / 32);
+  const int q = (within / (BN / 32)) & 3;
+  const int rank = within / (4 * (BN / 32));
+  const TileCoord tc = decode_tile<TILE_M>(tile, p);
+  const int row_base = tc.tm * TILE_M + rank * BM + q * 32;
+  const int col0 = tc.tn * BN + c * 32 + j0;
+  if (col0 >= p.N || col0 > row_base + 31 || row_base >= p.M) return;  // outside, or above the diagonal
+
+  // Two slices per round: their 16 loads are in flight together, the additions keep slice order.
+  const long long slice_pitch = static_cast<long long>(CTAS) * 4 * (BN / 32) * 1024;
+  const float* src = p.partial +
+      (((static_cast<long long>(tile) * p.split_k * CTAS + rank) * 4 + q) * (BN / 32) + c) * 1024 + j0 * 32 + lane;
+  float sum[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sum[j] = 0.f;
+  int sl = 0;
+  for (; sl + 1 < p.split_k; sl += 2) {
+    float first[8], second[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) first[j] = __ldcg(src + j * 32);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) second[j] = __ldcg(src + slice_pitch + j * 32);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sum[j] = (sum[j] + first[j]) + second[j];
+    src += 2 * slice_pitch;
+  }
+  if (sl < p.split_k) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sum[j] += __ldcg(src + j * 32);
+  }
+
+  const int r = row_base + lane;
+  if (r >= p.M) return;
+  unsigned short* out_s = reinterpret_cast<unsigned short*>(p.out + static_cast<long long>(tc.batch) * p.out_bs);
+  uint32_t packed[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) packed[j] = pack_bf16x2(sum[2 * j], sum[2 * j + 1]);
+  if (col0 + 8 <= row_base && col0 + 8 <= p.N) {
+    // strictly below the diagonal and inside the matrix: the row's 16 bytes in one piece
+    *reinterpret_cast<uint4*>(out_s + static_cast<long long>(r) * p.ldo + col0) =
+        make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int col = col0 + j;
+      if (col <= r && col < p.N)
+        out_s[static_cast<long long>(r) * p.ldo + col] =
+            static_cast<unsigned short>((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xffffu));
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int col = col0 + j;
+    if (col < r && col < p.N)
+      out_s[static_cast<long long>(col) * p.ldo + r] =
+          static_cast<unsigned short>((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xffffu));
   }
 }
 
@@ -1152,8 +1196,7 @@ int launch_instance(int dev, int sms, const CUtensorMap& ta, const CUtensorMap& 
   using C = Cfg<CTAS>;
   auto kern = ns_gemm_kernel<MODE, B_MN, CTAS, EW, ADD, F8>;
   const int slot = (((MODE * 2 + (CTAS - 1)) * 2 + (EW == 4 ? 0 : 1)) * 3 + ADD) * 7 + F8;
-  const long long total = (long long)p.tiles_per_batch * p.batch *
-                          (p.split_phase == 1 ? p.split_k : p.split_phase == 2 ? BN / 32 : 1);
+  const long long total = (long long)p.tiles_per_batch * p.batch * (p.split_phase == 1 ? p.split_k : 1);
 
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(num_threads(EW));
@@ -1198,7 +1241,7 @@ int launch_instance(int dev, int sms, const CUtensorMap& ta, const CUtensorMap& 
   cfg.gridDim = dim3(units * CTAS);
   {
     const double m = p.M, n = p.N, k = p.K, b = p.batch;
-    const double flops = p.split_phase == 2 ? 0.0 : MODE == MODE_BX ? 2.0 * m * k * n * b : m * (m + 1.0) * k * b;
+    const double flops = MODE == MODE_BX ? 2.0 * m * k * n * b : m * (m + 1.0) * k * b;
     const int64_t tag = ((int64_t)p.M << 40) | ((int64_t)(MODE == MODE_BX ? p.N : p.K) << 16) | ((int64_t)(p.batch & 0xfff) << 4) |
                         (p.sym_add == ADD_SYMMETRIC ? 1 : 0) | (CTAS == 2 ? 2 : 0) |
                         (p.sym_add == ADD_ROW_SCALED ? 4 : 0) | (EW >= 8 ? 8 : 0);
@@ -1483,9 +1526,22 @@ int launch_ns_gemm(int mode, const __nv_bfloat16* opa, int64_t lda, int64_t a_bs
       rc = ctas == 2 ? launch_epi<MODE_SYRK, false, 2>(8, f8_kind, dev, sms, ta, tb, p, stream)
                      : launch_epi<MODE_SYRK, false, 1>(8, f8_kind, dev, sms, ta, tb, p, stream);
       if (rc != OK) return rc;
-      p.split_phase = 2;  // partial sums -> bf16 blocks and their mirror images
-      return ctas == 2 ? launch_epi<MODE_SYRK, false, 2>(8, f8_kind, dev, sms, ta, tb, p, stream)
-                       : launch_epi<MODE_SYRK, false, 1>(8, f8_kind, dev, sms, ta, tb, p, stream);
+      // partial sums -> bf16 pieces and their mirror images, one warp per 32 rows x 8 columns
+      const long long warps = (long long)p.tiles_per_batch * batch * ctas * 4 * (BN / 32) * 4;
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3((unsigned)((warps + 7) / 8));
+      cfg.blockDim = dim3(256);
+      cfg.stream = stream;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = dependent_launch_enabled() ? 1 : 0;
+      LaunchScope scope(K_NS_LINE1, 0.0, stream);
+      if (ctas == 2) MB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, splitk_reduce_kernel<2>, p));
+      else MB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, splitk_reduce_kernel<1>, p));
+      MB_CUDA_CHECK(cudaGetLastError());
+      return OK;
     }
   }
   if (ctas == 2) {

@@ -93,16 +93,15 @@ struct GemmParams {
   // V_BATCH_SCALE: one factor per matrix of the batch
   const float* batch_scale;
   // Split-K of line 1 (see SplitK): 0 = none; 1 = every work item is one of split_k K-slices
-  // (split_kb k-blocks each) of a tile and leaves fp32 partial sums in `partial`; 2 = every work
-  // item is a 32-column chunk of a tile whose slices are added and stored.
+  // (split_kb k-blocks each) of a tile and leaves fp32 partial sums in `partial`.
   int split_phase, split_k, split_kb;
   float* partial;
 };
 
 // Scratch for split-K: a launch of line 1 whose tiles would occupy less than a third of the SMs
 // (one or a few small matrices with a long K) is cut along K into slices that run on different
-// SMs; a second launch of the same kernel adds the slices of every 32 x 32 block in slice order
-// (so the result does not depend on scheduling) and stores the block and its mirror image.
+// SMs; a second, small kernel adds the slices of every 32 x 32 block in slice order (so the
+// result does not depend on scheduling) and stores the block and its mirror image.
 struct SplitK {
   float* partial = nullptr;  // 256-byte aligned
   int64_t bytes = 0;
