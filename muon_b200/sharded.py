@@ -40,7 +40,14 @@ except Exception:  # pragma: no cover
 
 
 def _local(t):
-    return t.to_local() if DTensor is not None and isinstance(t, DTensor) else t
+    """This rank's rows of `t`: the local shard of a DTensor (redistributed to Shard(0) first when
+    it arrives in another placement, e.g. a gradient that is still Partial), or `t` itself."""
+    if DTensor is None or not isinstance(t, DTensor):
+        return t
+    if len(t.placements) != 1 or not t.placements[0].is_shard(0):
+        from torch.distributed.tensor import Shard
+        t = t.redistribute(placements=[Shard(0)])
+    return t.to_local()
 
 
 def shard_rows(rows: int, world: int, rank: int) -> tuple[int, int]:
